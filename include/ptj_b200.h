@@ -1,0 +1,207 @@
+/*
+ * ptj_b200.h — C ABI of the B200 (sm_100a) implementation of pre-tjax's GPT-2 training operators.
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and a CUDA stream handle (void* = cudaStream_t),
+ *   - returns 0 (PTJ_OK) or a negative ptj_status; it never throws, never synchronises the device and,
+ *     unless stated otherwise, never allocates (scratch buffers are passed in by the caller),
+ *   - reads its inputs and writes only its outputs; outputs need no zero-initialisation.
+ *
+ * "Replaces" comments cite the operator of the reference project (file:line inside pre-tjax) whose role
+ * the entry point takes. Element types: `dtype` is PTJ_F32 or PTJ_BF16 for activations; LayerNorm scale/shift,
+ * biases, optimizer state and gradients of parameters are always float.
+ *
+ * Dropout everywhere follows the reference semantics (model_torch_func.py:98-102): in training the value is
+ * multiplied by a 0/1 mask with keep probability 1-p and is NOT rescaled; in evaluation it is multiplied by 1-p.
+ * Masks come from Philox4x32-10 keyed by `seed`, counter = (element index / 4, stream id), so forward and
+ * backward regenerate identical masks from (seed, stream id) without storing them.
+ */
+#ifndef PTJ_B200_H_
+#define PTJ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  PTJ_OK = 0,
+  PTJ_ERR_BAD_SHAPE = -1,   /* a size is non-positive, too large, or violates a divisibility rule      */
+  PTJ_ERR_MISALIGNED = -2,  /* a pointer or leading dimension breaks the stated alignment              */
+  PTJ_ERR_DTYPE = -3,       /* dtype is not supported by this entry point                              */
+  PTJ_ERR_LAUNCH = -4,      /* the CUDA launch (or a driver call preparing it) reported an error       */
+  PTJ_ERR_WORKSPACE = -5,   /* the scratch buffer passed in is too small or NULL                       */
+  PTJ_ERR_UNSUPPORTED = -6, /* combination of options not implemented                                  */
+  PTJ_ERR_DEVICE = -7,      /* current device is not an sm_100 part / driver entry point missing       */
+  PTJ_ERR_TIMEOUT = -8      /* a bounded wait inside a kernel ran out (reported via ptj_last_kernel_fault) */
+} ptj_status;
+
+enum { PTJ_F32 = 0, PTJ_BF16 = 1 };
+
+/* ---- library ---------------------------------------------------------------------------------------- */
+int ptj_version(void);
+const char* ptj_status_string(int status);
+/* PTJ_OK when the current device has compute capability 10.x, else PTJ_ERR_DEVICE. */
+int ptj_device_check(void);
+/* Number of kernels this library has launched since load (all entry points, all threads). */
+int64_t ptj_launch_count(void);
+/* Tensor-core kernels poll their barriers with a bounded number of attempts. When a wait runs out the kernel
+ * records a non-zero code in a device word and returns early. This reads and clears that word (synchronises
+ * `stream`). 0 means no fault was recorded. */
+int ptj_last_kernel_fault(void* stream, unsigned int* code_out);
+
+/* ---- LayerNorm: y = gamma * (x - mean) / std_unbiased + beta, no epsilon ------------------------------ */
+/* Replaces t_layernorm_fwd_t (model_triton.py:1625-1637; math model_torch_func.py:104-108). */
+int ptj_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y,
+                      int64_t rows, int64_t dim, int dtype, void* stream);
+/* Replaces t_layernorm_bkwd2_x_t (model_triton.py:1853-1867) and t_layernorm_bkwd2_p_t (:1710-1726) in one
+ * pass. dx and/or (dgamma,dbeta) may be NULL to skip that result. dx_add (may be NULL, may alias dx) is added
+ * to dx: the gradient that arrives over the residual connection around the normalised branch
+ * (model_triton.py:2036, 2190). `scratch` holds per-block partial column sums (needed only when dgamma/dbeta
+ * are requested): ptj_layernorm_bwd_scratch_floats(rows, dim) floats.
+ * Results are bit-reproducible (two-stage reduction, no atomics). */
+size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim);
+int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                      float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
+                      int64_t dim, int dtype, void* stream);
+
+/* ---- GELU (tanh form) ------------------------------------------------------------------------------- */
+/* Replaces t_gelu_fwd_t (model_triton.py:254-260) and t_gelu_bkwd2_t (:296-304). */
+int ptj_gelu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream);
+int ptj_gelu_bwd(const void* dy, const void* x_preact, void* dx, int64_t n, int dtype, void* stream);
+
+/* ---- Dropout ---------------------------------------------------------------------------------------- */
+/* Replaces t_dropout_fwd_t (model_triton.py:1496-1506) and t_dropout_bkwd2_t (:1562-1572): the backward is the
+ * same map applied to the gradient. residual may be NULL; when given, y = residual + dropout(x). */
+int ptj_dropout(const void* x, const void* residual, void* y, int64_t n, float p, int train,
+                uint64_t seed, uint32_t stream_id, int dtype, void* stream);
+
+/* ---- log-softmax over the last dimension ------------------------------------------------------------- */
+/* Replaces t_log_softmax_fwd_t (model_triton.py:62-72) and t_log_softmax_bkwd2_t (:153-164).
+ * ld = elements between consecutive rows (>= cols). Rows of any length (chunked online max/sum). */
+int ptj_log_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int64_t ld_x, int64_t ld_y,
+                        int dtype, void* stream);
+int ptj_log_softmax_bwd(const void* dy, const void* x, void* dx, int64_t rows, int64_t cols, int64_t ld,
+                        int dtype, void* stream);
+
+/* ---- cross entropy --------------------------------------------------------------------------------- */
+/* Replaces t_avg_cross_entropy_loss_bkwd3_t (loss_and_optimizer_triton.py:176-197), t_avg_cross_entropy_loss
+ * (:23-32) and accuracy (:199-200). Label 0 is padding: such rows add nothing to the loss, the accuracy or the
+ * token count, and get a zero gradient row.
+ *   labels      int32[rows]
+ *   logits      [rows, ld] (cols valid)
+ *   dlogits     same layout, may alias logits (in place), or NULL for forward only
+ *   row_stats   float[2*rows] scratch: per-row loss and per-row hit
+ *   n_valid     float[1]: number of rows with label != 0. If count_in_kernel != 0 it is computed here from
+ *               labels, otherwise it is read (lets data-parallel callers supply the global count).
+ *   out3        float[3]: mean loss, accuracy, n_valid / rows   (deterministic single-block reduction)
+ */
+int ptj_cross_entropy(const int32_t* labels, const void* logits, void* dlogits, float* row_stats,
+                      float* n_valid, int count_in_kernel, float* out3, int64_t rows, int64_t cols,
+                      int64_t ld, int dtype, void* stream);
+
+/* ---- embedding -------------------------------------------------------------------------------------- */
+/* Replaces t_embed_fwd + positional add + dropout (model_triton.py:166-167, 2338-2341):
+ * y[b,s,:] = dropout(w_emb[ids[b,s],:] * sqrt(dim) + w_pos[s,:]). Weights are `wdtype`, output `dtype`. */
+int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* w_pos, void* y, int64_t batch,
+                  int64_t seq, int64_t dim, int64_t vocab, float p, int train, uint64_t seed,
+                  uint32_t stream_id, int wdtype, int dtype, void* stream);
+/* Replaces t_embed_bkwd2 / t_indexing_bkwd2 (model_triton.py:183-185, 205-213, 2513-2518) without atomics.
+ * dy is the gradient AFTER the embedding dropout (this entry point applies the mask itself).
+ *   sorted_pos int32[batch*seq]: token positions (b*seq+s) stably sorted by token id
+ *   d_w_emb    float[vocab, dim]: accumulate != 0 adds onto existing contents (tied LM-head gradient)
+ *   d_w_pos    float[seq, dim]  : overwritten
+ */
+int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb,
+                  float* d_w_pos, int accumulate, int64_t batch, int64_t seq, int64_t dim, int64_t vocab,
+                  float p, int train, uint64_t seed, uint32_t stream_id, int dtype, void* stream);
+
+/* ---- column sums (bias gradients) --------------------------------------------------------------------- */
+/* out[c] = sum_r x[r, c]; replaces the dloss_dx.sum(dim=0) of t_linear_bkwd2_p (model_triton.py:423-428).
+ * scratch: ptj_colsum_scratch_floats(rows, cols) floats. Deterministic. */
+size_t ptj_colsum_scratch_floats(int64_t rows, int64_t cols);
+int ptj_colsum(const void* x, float* out, float* scratch, size_t scratch_floats, int64_t rows,
+               int64_t cols, int64_t ld, int dtype, void* stream);
+
+/* ---- GEMM ------------------------------------------------------------------------------------------ */
+/* C[M,N] = op(A) * op(B) with an elementwise epilogue. Replaces t_matmul_t / the linear variant of t_matmul_k
+ * (model_triton.py:314-398) and every torch.matmul / einsum of the training path (t_linear_fwd :306,
+ * t_proj_fwd :436, t_proj_bkwd2_p :460-472, t_proj_bkwd2_x :495-508).
+ *   a_kmajor != 0: A is stored [M, K] (K contiguous, leading dim lda); else A is stored [K, M] (M contiguous)
+ *   b_kmajor != 0: B is stored [N, K] (K contiguous, leading dim ldb); else B is stored [K, N] (N contiguous)
+ *   in_dtype   PTJ_BF16: tcgen05 tensor-core kernel (TMA-fed, fp32 accumulate in TMEM); pointers 16-byte aligned,
+ *              leading dimensions multiples of 8 elements.
+ *              PTJ_F32 : exact-fp32 SIMT kernel, any shape (the "fp32 path").
+ *   out_dtype  PTJ_F32 or PTJ_BF16, C row-major with leading dim ldc
+ *   epilogue   PTJ_EPI_*; aux / aux_out meaning depends on it (same dtype and ld as C unless noted)
+ *   split_k    >1 splits K over that many work items; partial tiles go to `workspace`
+ *              (split_k*M*N floats) and are summed in a fixed order (bf16 kernel only; epilogue NONE/ACCUM).
+ */
+enum {
+  PTJ_EPI_NONE = 0,         /* C = acc (+ bias[n] if bias != NULL)                                        */
+  PTJ_EPI_GELU = 1,         /* aux_out = acc + bias (pre-activation, may be NULL); C = gelu(acc + bias)   */
+  PTJ_EPI_GELU_BWD = 2,     /* C = acc * gelu'(aux[m,n])          (aux = saved pre-activation)            */
+  PTJ_EPI_DROPOUT_RESID = 3,/* C = aux[m,n] + dropout(acc + bias) (aux = residual stream)                 */
+  PTJ_EPI_ACCUM = 4         /* C += acc (out_dtype float only)                                            */
+};
+typedef struct {
+  float p;            /* dropout probability (PTJ_EPI_DROPOUT_RESID) */
+  int train;
+  uint64_t seed;
+  uint32_t stream_id;
+} ptj_dropout_args;
+int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const void* aux, void* aux_out,
+             int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int a_kmajor,
+             int b_kmajor, int in_dtype, int out_dtype, int epilogue, const ptj_dropout_args* dropout,
+             int split_k, float* workspace, size_t workspace_floats, void* stream);
+
+/* ---- causal scaled-dot-product attention ----------------------------------------------------------- */
+/* Replaces t_scaled_dot_prod_attn_fwd3_t (model_triton.py:706-754) and t_scaled_dot_prod_attn_bkwd3_t
+ * (:951-1003): O = dropout(softmax(causal(Q K^T / sqrt(d)))) V with the dropout applied to the probabilities.
+ * q, k, v, o (and dq, dk, dv, d_o) are 4-D views [batch, heads, seq, d_head] described by element strides
+ * (d_head contiguous), so both the reference's [B,H,3,N,D] tensor and a fused [B*N, H*3*D] projection
+ * output are addressed without copies. row_max / row_sum are float[batch*heads*seq] (the reference's acts0 /
+ * acts1: running maximum of the scaled scores and sum of exp(score - max)).
+ *   dtype PTJ_BF16 with d_head == 64 and seq % 128 == 0 runs the tcgen05 kernels; everything else runs the
+ *   exact-fp32 SIMT kernels.
+ * Backward recomputes the probabilities; it is deterministic (no atomics).
+ */
+typedef struct {
+  int64_t batch, heads, seq, d_head;
+  int64_t q_strides[3], k_strides[3], v_strides[3], o_strides[3]; /* batch, head, row (elements) */
+} ptj_attn_shape;
+int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
+                 const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
+                 int dtype, void* stream);
+/* dq/dk/dv use q/k/v strides of `dshape`; d_o and o use o_strides of `shape`. */
+int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                 const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
+                 const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
+                 uint64_t seed, uint32_t stream_id, int dtype, void* stream);
+
+/* ---- optimizer -------------------------------------------------------------------------------------- */
+/* sum of squares of a float vector -> out[0] (deterministic two-stage). Replaces grads_l2norm
+ * (loss_and_optimizer_triton.py:411-416) on a flat buffer. scratch: ptj_sumsq_scratch_floats(n). */
+size_t ptj_sumsq_scratch_floats(int64_t n);
+int ptj_sumsq(const float* x, float* out, float* scratch, size_t scratch_floats, int64_t n, void* stream);
+/* Replaces adam_w_in_place (loss_and_optimizer_triton.py:376-401) over a flat range, in place:
+ *   g' = g * grad_scale * clip,  clip = min(1, max_norm / (sqrt(*sumsq) * grad_scale + 1e-6)) when sumsq != NULL
+ *   m = b1 m + (1-b1) g' ; v = b2 v + (1-b2) g'^2 ; p -= lr * ( (m/(1-b1^t)) / (sqrt(v/(1-b2^t)) + eps) + wd_i p )
+ * Segments (device arrays): seg_start int64[nseg+1] (ascending element offsets, multiples of 4, seg_start[0]=0,
+ * last = n), seg_decay uint8[nseg] says whether weight decay applies to that segment (nseg <= 1024).
+ * nseg == 0: wd applies everywhere. sumsq is a device scalar (see ptj_sumsq).
+ * shadow (may be NULL): bf16 copy of the updated parameters.
+ */
+int ptj_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16, int64_t n,
+              const int64_t* seg_start, const uint8_t* seg_decay, int nseg, float lr, float beta1,
+              float beta2, float eps, float weight_decay, int64_t t, float grad_scale,
+              const float* sumsq, float max_norm, void* stream);
+/* dst_bf16[i] = (bf16) src[i] */
+int ptj_cast_f32_to_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PTJ_B200_H_ */

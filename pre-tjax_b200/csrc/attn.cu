@@ -1,0 +1,63 @@
+// C entry points of causal attention: validate, then route to the tcgen05 kernels (bf16, d_head 64, seq % 128 == 0)
+// or to the exact-fp32 CUDA-core kernels (everything else).
+#include <cstdlib>
+
+#include "attn_common.cuh"
+
+using namespace ptj;
+
+namespace {
+bool shape_ok(const ptj_attn_shape* s) {
+  return s && s->batch >= 1 && s->heads >= 1 && s->seq >= 1 && s->d_head >= 1 &&
+         s->batch * s->heads * s->seq < (1LL << 40);
+}
+AttnDropout make_dropout(float p, int train, uint64_t seed, uint32_t stream_id) {
+  AttnDropout d;
+  d.thr = dropout_threshold(p);
+  d.eval_scale = 1.f - p;
+  d.train = train;
+  d.seed = seed;
+  d.stream_id = stream_id;
+  return d;
+}
+bool force_simt() {
+  static const bool v = [] {
+    const char* e = std::getenv("PTJ_ATTN_SIMT");
+    return e != nullptr && e[0] == '1';
+  }();
+  return v;
+}
+}  // namespace
+
+extern "C" int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
+                            const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
+                            int dtype, void* stream) {
+  if (!shape_ok(shape) || !q || !k || !v || !o || !row_max || !row_sum || !(p >= 0.f && p <= 1.f))
+    return PTJ_ERR_BAD_SHAPE;
+  if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const AttnDropout dr = make_dropout(p, train, seed, stream_id);
+  const void* ptrs[4] = {q, k, v, o};
+  if (dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, ptrs, 4))
+    return attn_fwd_tc(q, k, v, o, row_max, row_sum, *shape, dr, st);
+  return attn_fwd_simt(q, k, v, o, row_max, row_sum, *shape, dr, dtype, st);
+}
+
+extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                            const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
+                            const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
+                            uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
+  if (!shape_ok(shape) || !shape_ok(dshape) || !d_o || !q || !k || !v || !o || !row_max || !row_sum || !dq || !dk ||
+      !dv || !(p >= 0.f && p <= 1.f))
+    return PTJ_ERR_BAD_SHAPE;
+  if (dshape->batch != shape->batch || dshape->heads != shape->heads || dshape->seq != shape->seq ||
+      dshape->d_head != shape->d_head)
+    return PTJ_ERR_BAD_SHAPE;
+  if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const AttnDropout dr = make_dropout(p, train, seed, stream_id);
+  const void* ptrs[8] = {d_o, q, k, v, o, dq, dk, dv};
+  if (dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, ptrs, 8) && attn_tc_supported(*dshape, ptrs, 0))
+    return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, st);
+  return attn_bwd_simt(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, dtype, st);
+}

@@ -1,0 +1,36 @@
+// Declarations shared by the attention translation units.
+#pragma once
+#include "common.cuh"
+
+namespace ptj {
+
+// Dropout on attention probabilities: element (b*H+h, i, j) of the [B*H, S, S] probability tensor.
+struct AttnDropout {
+  uint32_t thr;
+  float eval_scale;  // 1 - p
+  int train;
+  uint64_t seed;
+  uint32_t stream_id;
+  __device__ __forceinline__ float factor(int64_t bh, int64_t S, int64_t i, int64_t j) const {
+    if (!train) return eval_scale;
+    if (thr == 0u) return 1.f;
+    const uint64_t idx = (static_cast<uint64_t>(bh) * S + i) * S + j;
+    return dropout_keep(seed, stream_id, idx, thr) ? 1.f : 0.f;
+  }
+};
+
+int attn_fwd_simt(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
+                  const ptj_attn_shape& sh, const AttnDropout& dr, int dtype, cudaStream_t st);
+int attn_bwd_simt(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
+                  const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
+                  const ptj_attn_shape& dsh, const AttnDropout& dr, int dtype, cudaStream_t st);
+
+// tcgen05 kernels: bf16, d_head == 64, seq % 128 == 0, 16-byte aligned strides.
+bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs);
+int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
+                const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
+int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
+                const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
+                const ptj_attn_shape& dsh, const AttnDropout& dr, cudaStream_t st);
+
+}  // namespace ptj

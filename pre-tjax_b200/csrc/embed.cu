@@ -1,0 +1,224 @@
+// Token + position embedding forward (gather, scale by sqrt(dim), add positions, dropout) and its backward
+// (deterministic segmented scatter into the embedding table, batch-sum into the position table), and the
+// deterministic column sum used for bias gradients.
+#include "common.cuh"
+
+namespace ptj {
+namespace {
+
+// y[t, :] = dropout(w_emb[ids[t], :] * sqrt(dim) + w_pos[t % seq, :])   (model_triton.py:166-167, 2338-2341)
+template <typename TW, typename T>
+__global__ void __launch_bounds__(256)
+embed_fwd_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ w_emb, const TW* __restrict__ w_pos,
+                 T* __restrict__ y, int64_t tokens, int64_t seq, int dim, int64_t vocab, float scale, uint32_t thr,
+                 float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  const int64_t total = tokens * dim;
+  for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x * 4) {
+    // dim % 4 == 0 is checked on the host, so the 4 elements share a token
+    const int64_t t = i / dim;
+    const int c = static_cast<int>(i - t * dim);
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const TW* e = w_emb + id * dim + c;
+    const TW* p = w_pos + (t % seq) * dim + c;
+    float k[4] = {eval_scale, eval_scale, eval_scale, eval_scale};
+    if (train) {
+      const Philox4 r = philox4x32_10(seed, static_cast<uint64_t>(i) >> 2, stream_id);
+      k[0] = r.x >= thr ? 1.f : 0.f;
+      k[1] = r.y >= thr ? 1.f : 0.f;
+      k[2] = r.z >= thr ? 1.f : 0.f;
+      k[3] = r.w >= thr ? 1.f : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      Elem<T>::store(y + i + j, (Elem<TW>::load(e + j) * scale + Elem<TW>::load(p + j)) * k[j]);
+  }
+}
+
+// Gradient w.r.t. the position table: d_w_pos[s, c] = sum_b mask * dy[b, s, c]   (model_triton.py:2518)
+template <typename T>
+__global__ void __launch_bounds__(256)
+pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t batch, int64_t seq, int dim,
+               uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  const int64_t total = seq * dim;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    for (int64_t b = 0; b < batch; ++b) {
+      const int64_t idx = b * total + i;
+      const float k = train ? (dropout_keep(seed, stream_id, static_cast<uint64_t>(idx), thr) ? 1.f : 0.f) : eval_scale;
+      s += Elem<T>::load(dy + idx) * k;
+    }
+    d_w_pos[i] = s;
+  }
+}
+
+// Gradient w.r.t. the embedding table (model_triton.py:183-185, 205-213). Token positions arrive stably sorted by
+// token id; the warp that sits on the first position of a run of equal ids walks the whole run in order, so every
+// table row is produced by one warp with a fixed summation order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
+                 float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
+                 uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t j = warp; j < tokens; j += nwarps) {
+    const int32_t id = ids[sorted_pos[j]];
+    if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run
+    if (id < 0 || id >= vocab) continue;
+    int64_t end = j + 1;
+    while (end < tokens && ids[sorted_pos[end]] == id) ++end;
+    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
+    for (int c = lane; c < dim; c += 32) {
+      float s = 0.f;
+      for (int64_t q = j; q < end; ++q) {
+        const int64_t idx = static_cast<int64_t>(sorted_pos[q]) * dim + c;
+        const float k =
+            train ? (dropout_keep(seed, stream_id, static_cast<uint64_t>(idx), thr) ? 1.f : 0.f) : eval_scale;
+        s += Elem<T>::load(dy + idx) * k;
+      }
+      s *= scale;
+      out[c] = accumulate ? out[c] + s : s;
+    }
+  }
+}
+
+// rows of the table that no token hit are zeroed when not accumulating
+__global__ void zero_kernel(float* __restrict__ p, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    p[i] = 0.f;
+}
+
+// stage 1: block (bx, by) sums rows [by*chunk, (by+1)*chunk) of columns bx*256 + tid
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_stage1_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols, int64_t ld,
+                     int64_t chunk) {
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * chunk;
+  const int64_t r1 = r0 + chunk < rows ? r0 + chunk : rows;
+  float s = 0.f;
+  for (int64_t r = r0; r < r1; ++r) s += Elem<T>::load(x + r * ld + c);
+  partial[static_cast<int64_t>(blockIdx.y) * cols + c] = s;
+}
+__global__ void __launch_bounds__(256)
+colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t cols, int nchunks) {
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int k = 0; k < nchunks; ++k) s += partial[static_cast<int64_t>(k) * cols + c];
+  out[c] = s;
+}
+
+inline int colsum_chunks(int64_t rows, int64_t cols) {
+  // enough row chunks to fill the machine: (cols/256) * chunks >= ~4 blocks per SM
+  const int64_t strips = ceil_div(cols, 256);
+  int64_t want = ceil_div(static_cast<int64_t>(kNumSMs) * 4, strips);
+  if (want < 1) want = 1;
+  const int64_t max_chunks = ceil_div(rows, 16);
+  if (want > max_chunks) want = max_chunks;
+  if (want > 1024) want = 1024;
+  return static_cast<int>(want);
+}
+
+inline int flat_grid(int64_t work, int per_block) {
+  int64_t b = ceil_div(work, per_block);
+  const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
+  if (b < 1) b = 1;
+  return static_cast<int>(b < cap ? b : cap);
+}
+
+}  // namespace
+}  // namespace ptj
+
+using namespace ptj;
+
+extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* w_pos, void* y, int64_t batch,
+                             int64_t seq, int64_t dim, int64_t vocab, float p, int train, uint64_t seed,
+                             uint32_t stream_id, int wdtype, int dtype, void* stream) {
+  if (batch < 0 || seq < 1 || dim < 4 || dim % 4 != 0 || vocab < 1 || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+  if (batch == 0) return PTJ_OK;
+  if (!ids || !w_emb || !w_pos || !y) return PTJ_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t tokens = batch * seq;
+  const int grid = flat_grid(tokens * dim / 4, 256);
+  const float scale = sqrtf(static_cast<float>(dim));
+  const uint32_t thr = dropout_threshold(p);
+#define PTJ_EMBED(TW, T)                                                                                      \
+  embed_fwd_kernel<TW, T><<<grid, 256, 0, st>>>(ids, static_cast<const TW*>(w_emb), static_cast<const TW*>(w_pos), \
+                                                static_cast<T*>(y), tokens, seq, (int)dim, vocab, scale, thr,  \
+                                                1.f - p, train, seed, stream_id)
+  if (wdtype == PTJ_F32 && dtype == PTJ_F32) PTJ_EMBED(float, float);
+  else if (wdtype == PTJ_F32 && dtype == PTJ_BF16) PTJ_EMBED(float, __nv_bfloat16);
+  else if (wdtype == PTJ_BF16 && dtype == PTJ_BF16) PTJ_EMBED(__nv_bfloat16, __nv_bfloat16);
+  else return PTJ_ERR_DTYPE;
+#undef PTJ_EMBED
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb,
+                             float* d_w_pos, int accumulate, int64_t batch, int64_t seq, int64_t dim, int64_t vocab,
+                             float p, int train, uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
+  if (batch < 1 || seq < 1 || dim < 1 || vocab < 1 || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+  if (batch * seq > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
+  if (!dy || !ids || !sorted_pos || !d_w_emb || !d_w_pos) return PTJ_ERR_BAD_SHAPE;
+  if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t tokens = batch * seq;
+  const float scale = sqrtf(static_cast<float>(dim));
+  const uint32_t thr = dropout_threshold(p);
+  if (!accumulate) {
+    zero_kernel<<<flat_grid(vocab * dim, 256 * 4), 256, 0, st>>>(d_w_emb, vocab * dim);
+    PTJ_CHECK_LAUNCH();
+  }
+  const int grid_e = flat_grid(tokens, 8);  // one warp per sorted position
+  const int grid_p = flat_grid(seq * dim, 256);
+  if (dtype == PTJ_F32) {
+    embed_bwd_kernel<float><<<grid_e, 256, 0, st>>>(static_cast<const float*>(dy), ids, sorted_pos, d_w_emb, 1, tokens,
+                                                    (int)dim, vocab, scale, thr, 1.f - p, train, seed, stream_id);
+    PTJ_CHECK_LAUNCH();
+    pos_bwd_kernel<float><<<grid_p, 256, 0, st>>>(static_cast<const float*>(dy), d_w_pos, batch, seq, (int)dim, thr,
+                                                  1.f - p, train, seed, stream_id);
+  } else {
+    embed_bwd_kernel<__nv_bfloat16><<<grid_e, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), ids, sorted_pos,
+                                                            d_w_emb, 1, tokens, (int)dim, vocab, scale, thr, 1.f - p,
+                                                            train, seed, stream_id);
+    PTJ_CHECK_LAUNCH();
+    pos_bwd_kernel<__nv_bfloat16><<<grid_p, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), d_w_pos, batch, seq,
+                                                          (int)dim, thr, 1.f - p, train, seed, stream_id);
+  }
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+extern "C" size_t ptj_colsum_scratch_floats(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>(colsum_chunks(rows, cols)) * static_cast<size_t>(cols);
+}
+
+extern "C" int ptj_colsum(const void* x, float* out, float* scratch, size_t scratch_floats, int64_t rows,
+                          int64_t cols, int64_t ld, int dtype, void* stream) {
+  if (rows < 1 || cols < 1 || ld < cols) return PTJ_ERR_BAD_SHAPE;
+  if (!x || !out) return PTJ_ERR_BAD_SHAPE;
+  if (!scratch || scratch_floats < ptj_colsum_scratch_floats(rows, cols)) return PTJ_ERR_WORKSPACE;
+  if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nchunks = colsum_chunks(rows, cols);
+  const int64_t chunk = ceil_div(rows, nchunks);
+  dim3 grid(static_cast<unsigned>(ceil_div(cols, 256)), static_cast<unsigned>(nchunks));
+  if (dtype == PTJ_F32)
+    colsum_stage1_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+  else
+    colsum_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols,
+                                                              ld, chunk);
+  PTJ_CHECK_LAUNCH();
+  colsum_stage2_kernel<<<static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st>>>(scratch, out, cols, nchunks);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}

@@ -1,0 +1,427 @@
+// GEMM for the training path.
+//
+// bf16 inputs: persistent, warp-specialised tcgen05 kernel. One warp issues TMA tensor copies into a ring of
+// 128-byte-swizzled shared-memory stages, one thread issues tcgen05.mma (128 x BN x 16 per instruction, fp32
+// accumulators in tensor memory, two accumulator buffers), four warps drain finished accumulators with tcgen05.ld
+// and run the elementwise epilogue while the next tile is already being multiplied. Either operand may be K-major
+// or MN-major, which covers forward (x W^T), input-gradient (dy W) and weight-gradient (dy^T x) products without
+// any transposed copy. Work items = output tiles x K splits, walked by a static persistent schedule.
+//
+// fp32 inputs: plain shared-memory tiled FMA kernel (exact fp32, any shape) for the fp32 parity path.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include "tc_common.cuh"
+#include "tc_runtime.h"
+
+namespace ptj {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+struct GemmParams {
+  EpilogueParams ep;
+  int64_t M, N, K;
+  int num_m, num_n, num_kb, split_k;
+  float* workspace;  // [split_k, M, N] partial sums when split_k > 1
+  int out_bf16;
+  unsigned int* fault;
+};
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const AbortCtx ctx{abort_flag, p.fault};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.num_m * p.num_n;
+  const int total = tiles * p.split_k;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        const int split = item / tiles, tile = item - split * tiles;
+        const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0101u)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          if (A_KMAJOR) {
+            tma_load_2d(sa, &tmap_a, &full[stage], kb * BK, m_blk * BM);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BM / 64; ++h)
+              tma_load_2d(sa + h * 8192, &tmap_a, &full[stage], m_blk * BM + h * 64, kb * BK);
+          }
+          if (B_KMAJOR) {
+            tma_load_2d(sb, &tmap_b, &full[stage], kb * BK, n_blk * BN);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h)
+              tma_load_2d(sb + h * 8192, &tmap_b, &full[stage], n_blk * BN + h * 64, kb * BK);
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN, !A_KMAJOR, !B_KMAJOR);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
+        const int split = item / tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty[buf], aphase ^ 1u, ctx, 0x0201u)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, ctx, 0x0202u)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t adesc = A_KMAJOR ? smem_desc_sw128(sa + k4 * 32, 16, 1024)
+                                            : smem_desc_sw128(sa + k4 * 2048, 8192, 1024);
+            const uint64_t bdesc = B_KMAJOR ? smem_desc_sw128(sb + k4 * 32, 16, 1024)
+                                            : smem_desc_sw128(sb + k4 * 2048, 8192, 1024);
+            mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+          }
+          mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
+    int it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
+      const int split = item / tiles, tile = item - split * tiles;
+      const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1u;
+      if (!mbar_wait(&tmem_full[buf], aphase, ctx, 0x0301u)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int64_t row = static_cast<int64_t>(m_blk) * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + chunk * 32, r);
+        tmem_ld_wait();
+        float acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + chunk * 32;
+        if (p.split_k > 1) {
+          if (row < p.M) {
+            float* w = p.workspace + (static_cast<int64_t>(split) * p.M + row) * p.N;
+            if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(w + n0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) w[n0 + j] = acc[j];
+            }
+          }
+        } else if (p.out_bf16) {
+          epilogue_row_segment<__nv_bfloat16, 32>(p.ep, row, n0, acc);
+        } else {
+          epilogue_row_segment<float, 32>(p.ep, row, n0, acc);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies still in flight time to land before shared memory is handed back
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// c[m, n] = (accumulate ? c : 0) + bias[n] + sum_s ws[s, m, n]
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restrict__ c, const float* __restrict__ bias, int64_t M,
+                     int64_t N, int64_t ldc, int split_k, int accumulate) {
+  const int64_t total = M * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / N, n = i - m * N;
+    float s = 0.f;
+    for (int k = 0; k < split_k; ++k) s += ws[static_cast<int64_t>(k) * total + i];
+    if (bias != nullptr) s += bias[n];
+    TOut* dst = c + m * ldc + n;
+    if (accumulate) s += Elem<TOut>::load(dst);
+    Elem<TOut>::store(dst, s);
+  }
+}
+
+// ---- exact fp32 kernel -----------------------------------------------------------------------------------------
+constexpr int SM_BM = 64, SM_BN = 64, SM_BK = 16;
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t sam, int64_t sak, int64_t sbn,
+                 int64_t sbk, int64_t M, int64_t N, int64_t K, const EpilogueParams ep) {
+  __shared__ float As[SM_BK][SM_BM + 4];
+  __shared__ float Bs[SM_BK][SM_BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 7, ty = tid >> 3;  // 8 column groups of 8, 16 row groups of 4
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * SM_BM, n0 = static_cast<int64_t>(blockIdx.x) * SM_BN;
+  float acc[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int64_t k0 = 0; k0 < K; k0 += SM_BK) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = tid + i * 128;
+      int mm, kk;
+      if (sak == 1) { mm = idx / SM_BK; kk = idx % SM_BK; } else { kk = idx / SM_BM; mm = idx % SM_BM; }
+      const int64_t gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < M && gk < K) ? A[gm * sam + gk * sak] : 0.f;
+      int nn, kb;
+      if (sbk == 1) { nn = idx / SM_BK; kb = idx % SM_BK; } else { kb = idx / SM_BN; nn = idx % SM_BN; }
+      const int64_t gn = n0 + nn, gkb = k0 + kb;
+      Bs[kb][nn] = (gn < N && gkb < K) ? B[gn * sbn + gkb * sbk] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < SM_BK; ++kk) {
+      float a[4], b[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) b[j] = Bs[kk][tx * 8 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) epilogue_row_segment<TOut, 8>(ep, m0 + ty * 4 + i, n0 + tx * 8, acc[i]);
+}
+
+template <int BN, bool AK, bool BK_>
+int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_tc_kernel<BN, AK, BK_>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return PTJ_ERR_LAUNCH;
+  }
+  const int total = p.num_m * p.num_n * p.split_k;
+  const int grid = total < kNumSMs ? total : kNumSMs;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+}  // namespace
+}  // namespace ptj
+
+using namespace ptj;
+
+extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const void* aux, void* aux_out,
+                        int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int a_kmajor,
+                        int b_kmajor, int in_dtype, int out_dtype, int epilogue, const ptj_dropout_args* dropout,
+                        int split_k, float* workspace, size_t workspace_floats, void* stream) {
+  if (M < 1 || N < 1 || K < 1 || M > (1LL << 30) || N > (1LL << 30) || K > (1LL << 30)) return PTJ_ERR_BAD_SHAPE;
+  if (!a || !b || !c) return PTJ_ERR_BAD_SHAPE;
+  if (lda < (a_kmajor ? K : M) || ldb < (b_kmajor ? K : N) || ldc < N) return PTJ_ERR_BAD_SHAPE;
+  if (out_dtype != PTJ_F32 && out_dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  if (epilogue < PTJ_EPI_NONE || epilogue > PTJ_EPI_ACCUM) return PTJ_ERR_UNSUPPORTED;
+  if ((epilogue == PTJ_EPI_GELU_BWD || epilogue == PTJ_EPI_DROPOUT_RESID) && aux == nullptr) return PTJ_ERR_BAD_SHAPE;
+  if (epilogue == PTJ_EPI_DROPOUT_RESID && dropout == nullptr) return PTJ_ERR_BAD_SHAPE;
+  if (epilogue == PTJ_EPI_ACCUM && out_dtype != PTJ_F32) return PTJ_ERR_UNSUPPORTED;
+  if (split_k < 1) split_k = 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  EpilogueParams ep{};
+  ep.c = c;
+  ep.bias = bias;
+  ep.aux = aux;
+  ep.aux_out = aux_out;
+  ep.M = M;
+  ep.N = N;
+  ep.ldc = ldc;
+  ep.mode = epilogue;
+  const size_t osz = dtype_size(out_dtype);
+  ep.vec_ok = aligned16(c) && (ldc * osz) % 16 == 0 && (aux == nullptr || aligned16(aux)) &&
+              (aux_out == nullptr || aligned16(aux_out));
+  if (dropout != nullptr) {
+    if (!(dropout->p >= 0.f && dropout->p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+    ep.drop_thr = dropout_threshold(dropout->p);
+    ep.eval_scale = 1.f - dropout->p;
+    ep.train = dropout->train;
+    ep.seed = dropout->seed;
+    ep.stream_id = dropout->stream_id;
+  }
+
+  if (in_dtype == PTJ_F32) {
+    if (split_k != 1) return PTJ_ERR_UNSUPPORTED;
+    const int64_t sam = a_kmajor ? lda : 1, sak = a_kmajor ? 1 : lda;
+    const int64_t sbn = b_kmajor ? ldb : 1, sbk = b_kmajor ? 1 : ldb;
+    dim3 grid(static_cast<unsigned>(ceil_div(N, SM_BN)), static_cast<unsigned>(ceil_div(M, SM_BM)));
+    if (grid.y > 65535) return PTJ_ERR_BAD_SHAPE;
+    if (out_dtype == PTJ_F32)
+      gemm_simt_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b), sam, sak,
+                                                    sbn, sbk, M, N, K, ep);
+    else
+      gemm_simt_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b),
+                                                            sam, sak, sbn, sbk, M, N, K, ep);
+    PTJ_CHECK_LAUNCH();
+    return PTJ_OK;
+  }
+  if (in_dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+
+  if (!aligned16(a) || !aligned16(b) || lda % 8 != 0 || ldb % 8 != 0) return PTJ_ERR_MISALIGNED;
+  if (ptj_device_check() != PTJ_OK) return PTJ_ERR_DEVICE;
+  const int num_kb = static_cast<int>(ceil_div(K, BK));
+  if (split_k > num_kb) split_k = num_kb;
+  if (split_k > 1) {
+    if (epilogue != PTJ_EPI_NONE && epilogue != PTJ_EPI_ACCUM) return PTJ_ERR_UNSUPPORTED;
+    if (!workspace || workspace_floats < static_cast<size_t>(split_k) * M * N || !aligned16(workspace))
+      return PTJ_ERR_WORKSPACE;
+  }
+  GemmParams p{};
+  p.ep = ep;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_m = static_cast<int>(ceil_div(M, BM));
+  p.num_kb = num_kb;
+  p.split_k = split_k;
+  p.workspace = workspace;
+  p.out_bf16 = out_dtype == PTJ_BF16;
+  p.fault = tc::fault_word();
+  if (p.fault == nullptr) return PTJ_ERR_DEVICE;
+
+  // tile width: fewer, fatter tiles unless that leaves SMs idle in the last wave
+  auto waves_cost = [&](int bn) {
+    const int64_t items = static_cast<int64_t>(p.num_m) * ceil_div(N, bn) * split_k;
+    return ceil_div(items, kNumSMs) * bn;
+  };
+  const int bn = waves_cost(128) < waves_cost(256) ? 128 : 256;
+  p.num_n = static_cast<int>(ceil_div(N, bn));
+  if (static_cast<int64_t>(p.num_m) * p.num_n * split_k > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t dims_mn[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
+    const uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    const uint32_t box_k[2] = {64, 128}, box_mn[2] = {64, 64};
+    if (!make_tmap_bf16(&ta, a, 2, a_kmajor ? dims_k : dims_mn, str, a_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
+  }
+  {
+    const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t dims_mn[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    const uint32_t box_k[2] = {64, static_cast<uint32_t>(bn)}, box_mn[2] = {64, 64};
+    if (!make_tmap_bf16(&tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
+  }
+
+  int rc;
+#define PTJ_TC(BN_)                                                              \
+  (a_kmajor ? (b_kmajor ? launch_tc<BN_, true, true>(ta, tb, p, st)              \
+                        : launch_tc<BN_, true, false>(ta, tb, p, st))            \
+            : (b_kmajor ? launch_tc<BN_, false, true>(ta, tb, p, st)             \
+                        : launch_tc<BN_, false, false>(ta, tb, p, st)))
+  rc = bn == 128 ? PTJ_TC(128) : PTJ_TC(256);
+#undef PTJ_TC
+  if (rc != PTJ_OK) return rc;
+
+  if (split_k > 1) {
+    const int64_t total = M * N;
+    int64_t blocks = ceil_div(total, 256);
+    if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+    if (out_dtype == PTJ_F32)
+      splitk_reduce_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N,
+                                                                            ldc, split_k, epilogue == PTJ_EPI_ACCUM);
+    else
+      splitk_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+          workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    PTJ_CHECK_LAUNCH();
+  }
+  return PTJ_OK;
+}

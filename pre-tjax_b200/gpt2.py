@@ -1,0 +1,323 @@
+"""GPT-2 forward + hand-written backward on the sm_100a kernels.
+
+Mirrors the composition functions of the reference's Triton path — ``t_gpt2_forward_with_acts_t``
+(model_triton.py:2535-2539), ``t_gpt2_bkwd3_p_t`` (:2583-2593) and ``t_loss_bkwd3_t``
+(loss_and_optimizer_triton.py:279-289) — with the same parameter pytree (model_torch_func.py:36-43):
+
+    [[W_emb(V,D), b_head(V)], [W_pos(S,D)],
+     L x [g1, b1, W_qkv(H,3,dh,D), W_o(D,D), g2, b2, W1(F,D), b1f(F), W2(D,F), b2f(D)],
+     [g_f, b_f]]
+
+Differences in HOW (not in what is computed): the three head projections are ONE GEMM whose output columns are
+ordered (head, q/k/v, d_head) so W_qkv keeps the reference layout; attention reads/writes strided views (no stack,
+transpose or concat copies); bias, GELU, dropout and the residual add run in GEMM epilogues; the causal mask is
+analytic; QKV and the FFN pre-activation are saved instead of recomputed in backward; the cross entropy overwrites
+the logits with their gradient; nothing uses atomics, so results are bit-reproducible.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from . import _lib, operators as ops
+
+LAYER_TENSORS = ("g1", "b1", "w_qkv", "w_o", "g2", "b2", "w1", "b1f", "w2", "b2f")
+# which tensors take part in the tensor-core GEMMs and therefore live in the compute dtype
+MATRIX_TENSORS = {"w_emb", "w_pos", "w_qkv", "w_o", "w1", "w2"}
+
+
+@dataclass(frozen=True)
+class GPT2Config:
+    vocab: int
+    dim: int
+    layers: int
+    heads: int
+    ffn: int
+    seq: int
+    dropout: float = 0.1
+
+    @property
+    def d_head(self) -> int:
+        return self.dim // self.heads
+
+    def param_shapes(self):
+        """[(name, shape)] in the order of the flattened reference pytree."""
+        V, D, H, F, S = self.vocab, self.dim, self.heads, self.ffn, self.seq
+        out = [("w_emb", (V, D)), ("b_head", (V,)), ("w_pos", (S, D))]
+        for l in range(self.layers):
+            out += [(f"l{l}.g1", (D,)), (f"l{l}.b1", (D,)), (f"l{l}.w_qkv", (H, 3, D // H, D)), (f"l{l}.w_o", (D, D)),
+                    (f"l{l}.g2", (D,)), (f"l{l}.b2", (D,)), (f"l{l}.w1", (F, D)), (f"l{l}.b1f", (F,)),
+                    (f"l{l}.w2", (D, F)), (f"l{l}.b2f", (D,))]
+        out += [("g_f", (D,)), ("b_f", (D,))]
+        return out
+
+    def num_params(self) -> int:
+        return sum(math.prod(s) for _, s in self.param_shapes())
+
+
+PRESETS = {
+    "tiny": GPT2Config(vocab=1024, dim=128, layers=2, heads=4, ffn=512, seq=128, dropout=0.0),
+    "gpt2-small": GPT2Config(vocab=50257, dim=768, layers=12, heads=12, ffn=3072, seq=1024, dropout=0.1),
+    "gpt2-medium": GPT2Config(vocab=50257, dim=1024, layers=24, heads=16, ffn=4096, seq=1024, dropout=0.1),
+}
+
+
+def base_name(name: str) -> str:
+    return name.split(".")[-1]
+
+
+def is_decayed(name: str) -> bool:
+    """Weight-decay rule of the reference (train_gpt2_triton.py:69-71): everything except 1-D tensors that start as
+    zeros, i.e. biases and LayerNorm shifts are exempt while LayerNorm scales (initialised to one) are decayed."""
+    return base_name(name) not in ("b_head", "b1", "b2", "b1f", "b2f", "b_f")
+
+
+def flatten_pytree(tree) -> List[torch.Tensor]:
+    return [t for grp in tree for t in grp]
+
+
+def unflatten_like(flat: Sequence[torch.Tensor], cfg: GPT2Config):
+    """Regroup a flat list into the reference's [[2], [1], L x [10], [2]] nesting."""
+    it = iter(flat)
+    tree = [[next(it), next(it)], [next(it)]]
+    for _ in range(cfg.layers):
+        tree.append([next(it) for _ in range(10)])
+    tree.append([next(it), next(it)])
+    return tree
+
+
+def config_from_params(params, dropout: float) -> GPT2Config:
+    V, D = params[0][0].shape
+    S = params[1][0].shape[0]
+    L = len(params) - 3
+    H = params[2][2].shape[0]
+    F = params[2][6].shape[0]
+    return GPT2Config(vocab=V, dim=D, layers=L, heads=H, ffn=F, seq=S, dropout=dropout)
+
+
+class Weights:
+    """Named views of the parameters: matrices in the compute dtype, vectors (LayerNorm, biases) in float32."""
+
+    def __init__(self, cfg: GPT2Config, tensors: dict):
+        self.cfg = cfg
+        self.t = tensors
+
+    def __getitem__(self, name):
+        return self.t[name]
+
+    @staticmethod
+    def from_pytree(params, cfg: GPT2Config, compute_dtype: torch.dtype) -> "Weights":
+        flat = flatten_pytree(params)
+        names = [n for n, _ in cfg.param_shapes()]
+        assert len(flat) == len(names), "parameter pytree does not match the configuration"
+        t = {}
+        for n, p in zip(names, flat):
+            if not p.is_cuda:
+                raise RuntimeError("parameters must live on a CUDA device: there is no CPU implementation")
+            want = compute_dtype if base_name(n) in MATRIX_TENSORS else torch.float32
+            p = p.contiguous()
+            t[n] = p if p.dtype == want else p.to(want)
+        return Weights(cfg, t)
+
+
+def split_k_for(m_tiles: int, n_tiles: int, k_blocks: int) -> int:
+    """K split of a weight-gradient GEMM: aim for about two waves of work items over 148 SMs."""
+    tiles = max(1, m_tiles * n_tiles)
+    s = max(1, round(2 * 148 / tiles))
+    return int(min(s, 8, max(1, k_blocks // 4)))
+
+
+class Gpt2Step:
+    """One forward + backward pass. Gradients are written into caller-provided float32 tensors (``grads[name]``),
+    so a trainer can hand in views of one flat buffer and overlap their reduction with the rest of backward."""
+
+    def __init__(self, cfg: GPT2Config, compute_dtype: torch.dtype = torch.bfloat16):
+        self.cfg = cfg
+        self.dtype = compute_dtype
+        # logits rows are padded so that every row starts on a 16-byte boundary
+        self.vocab_ld = (cfg.vocab + 127) // 128 * 128
+        self._ws = None
+
+    # -- helpers --
+    def _wgrad(self, dy2d, x2d, out, accumulate=False):
+        """out[N_out, N_in] = dy^T x : both operands are read 'MN-major' (tokens are the reduction dimension)."""
+        T = dy2d.shape[0]
+        M, N = out.shape[0], x2d.shape[1]
+        split = 1
+        if dy2d.dtype == torch.bfloat16:
+            split = split_k_for((M + 127) // 128, (N + 255) // 256, (T + 63) // 64)
+            need = split * M * N
+            if split > 1 and (self._ws is None or self._ws.numel() < need):
+                self._ws = torch.empty(need, device=out.device, dtype=torch.float32)
+        ops.gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, M=M, N=N, K=T, lda=dy2d.stride(0), ldb=x2d.stride(0),
+                 out=out.view(M, N), epilogue=_lib.EPI_ACCUM if accumulate else _lib.EPI_NONE, split_k=split,
+                 workspace=self._ws)
+
+    def _dgrad(self, dy2d, w2d, cols=None, **kw):
+        """dx[T, N_in] = dy[T, N_out] w[N_out, N_in]: w is the 'MN-major' B operand."""
+        T = dy2d.shape[0]
+        K = w2d.shape[0] if cols is None else cols
+        return ops.gemm(dy2d, w2d, a_kmajor=True, b_kmajor=False, M=T, N=w2d.shape[1], K=K, lda=dy2d.stride(0),
+                        ldb=w2d.stride(0), out_dtype=self.dtype, **kw)
+
+    # -- forward --
+    def forward(self, w: Weights, ids_in: torch.Tensor, train: bool, seeds: Sequence[int]):
+        """Returns (logits [B*S, vocab_ld] (first `vocab` columns valid), saved activations)."""
+        cfg, p = self.cfg, self.cfg.dropout
+        B, S = ids_in.shape
+        assert S == cfg.seq, "the positional table is added without slicing: sequence length must equal cfg.seq"
+        D, H, dh, T = cfg.dim, cfg.heads, cfg.d_head, B * S
+        if not train:
+            seeds = [0] * (1 + 3 * cfg.layers)
+        x = ops.embed_fwd(ids_in, w["w_emb"], w["w_pos"], train, seeds[0], out_dtype=self.dtype, p=p).view(T, D)
+        acts = {"layers": []}
+        for l in range(cfg.layers):
+            s_attn, s_res1, s_res2 = seeds[1 + 3 * l: 4 + 3 * l]
+            g = lambda n: w[f"l{l}.{n}"]
+            a = {"x": x}
+            a["ln1"] = ops.t_layernorm_fwd_t((g("g1"), g("b1")), x)
+            a["qkv"] = ops.gemm(a["ln1"], g("w_qkv").view(3 * D, D))  # columns ordered (head, q/k/v, d_head)
+            qkv5 = a["qkv"].view(B, S, H, 3, dh)
+            q, k, v = (qkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
+            a["attn"] = torch.empty((T, D), device=x.device, dtype=self.dtype)
+            o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
+            a["m"], a["l"] = ops.attn_fwd(q, k, v, o4, train, s_attn, p=p)
+            a["x_mid"] = ops.gemm(a["attn"], g("w_o"), epilogue=_lib.EPI_DROPOUT_RESID, aux=x,
+                                  dropout_args=(p, train, s_res1, 0))
+            a["ln2"] = ops.t_layernorm_fwd_t((g("g2"), g("b2")), a["x_mid"])
+            a["h_pre"] = torch.empty((T, cfg.ffn), device=x.device, dtype=self.dtype)
+            a["h_act"] = ops.gemm(a["ln2"], g("w1"), bias=g("b1f"), epilogue=_lib.EPI_GELU, aux_out=a["h_pre"])
+            x = ops.gemm(a["h_act"], g("w2"), bias=g("b2f"), epilogue=_lib.EPI_DROPOUT_RESID, aux=a["x_mid"],
+                         dropout_args=(p, train, s_res2, 0))
+            acts["layers"].append(a)
+        acts["x_last"] = x
+        acts["x_f"] = ops.t_layernorm_fwd_t((w["g_f"], w["b_f"]), x)
+        logits = torch.empty((T, self.vocab_ld), device=x.device, dtype=self.dtype)
+        ops.gemm(acts["x_f"], w["w_emb"], bias=w["b_head"], out=logits, N=cfg.vocab, ldc=self.vocab_ld)
+        return logits, acts
+
+    # -- backward --
+    def backward(self, w: Weights, grads: dict, dlogits: torch.Tensor, acts: dict, ids_in: torch.Tensor, train: bool,
+                 seeds: Sequence[int], on_ready: Optional[Callable[[List[str]], None]] = None):
+        """dlogits: [B*S, vocab_ld]. Fills grads[name] (float32) for every parameter; calls on_ready(names) as soon as
+        the kernels producing those gradients have been enqueued."""
+        cfg, p = self.cfg, self.cfg.dropout
+        B, S = ids_in.shape
+        D, H, dh, T, F, V = cfg.dim, cfg.heads, cfg.d_head, B * S, cfg.ffn, cfg.vocab
+        if not train:
+            seeds = [0] * (1 + 3 * cfg.layers)
+        ready = on_ready or (lambda names: None)
+
+        # LM head (tied to the embedding): bias, weight (the embedding scatter is added at the very end), input
+        ops.colsum(dlogits, cols=V, out=grads["b_head"])
+        self._head_wgrad(dlogits, acts["x_f"], grads["w_emb"])
+        ready(["b_head"])
+        d = self._dgrad(dlogits, w["w_emb"], cols=V)
+        dx = self._ln_bwd(d, w["g_f"], acts["x_last"], grads["g_f"], grads["b_f"])
+        ready(["g_f", "b_f"])
+
+        for l in reversed(range(cfg.layers)):
+            s_attn, s_res1, s_res2 = seeds[1 + 3 * l: 4 + 3 * l]
+            a = acts["layers"][l]
+            g = lambda n: w[f"l{l}.{n}"]
+            G = lambda n: grads[f"l{l}.{n}"]
+            # x_next = x_mid + dropout(W2 gelu(W1 ln2(x_mid) + b1f) + b2f)
+            dy = ops.dropout(dx, train, s_res2, p=p)
+            ops.colsum(dy, out=G("b2f"))
+            self._wgrad(dy, a["h_act"], G("w2"))
+            dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
+            ops.colsum(dh_pre, out=G("b1f"))
+            self._wgrad(dh_pre, a["ln2"], G("w1"))
+            d_ln2 = self._dgrad(dh_pre, g("w1"))
+            dx = self._ln_bwd(d_ln2, g("g2"), a["x_mid"], G("g2"), G("b2"), dx_add=dx)
+            ready([f"l{l}.{n}" for n in ("b2f", "w2", "b1f", "w1", "g2", "b2")])
+            # x_mid = x + dropout(attn(ln1(x)) W_o^T)
+            dy = ops.dropout(dx, train, s_res1, p=p)
+            self._wgrad(dy, a["attn"], G("w_o"))
+            d_attn = self._dgrad(dy, g("w_o"))
+            dqkv = torch.empty((T, 3 * D), device=dy.device, dtype=self.dtype)
+            qkv5, dqkv5 = a["qkv"].view(B, S, H, 3, dh), dqkv.view(B, S, H, 3, dh)
+            q, k, v = (qkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
+            dq, dk, dv = (dqkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
+            o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
+            do4 = d_attn.view(B, S, H, dh).permute(0, 2, 1, 3)
+            ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p)
+            self._wgrad(dqkv, a["ln1"], G("w_qkv").view(3 * D, D))
+            d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
+            dx = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx)
+            ready([f"l{l}.{n}" for n in ("w_o", "w_qkv", "g1", "b1")])
+
+        # embedding + positions; the scatter accumulates onto the LM-head weight gradient (tied weights)
+        ops.embed_bwd(dx, ids_in, grads["w_emb"], grads["w_pos"], accumulate=True, train=train, seed=seeds[0], p=p,
+                      sorted_pos=acts.get("sorted_pos"))
+        ready(["w_emb", "w_pos"])
+
+    def _head_wgrad(self, dlogits, x_f, out):
+        V = self.cfg.vocab
+        T = dlogits.shape[0]
+        ops.gemm(dlogits, x_f, a_kmajor=False, b_kmajor=False, M=V, N=x_f.shape[1], K=T, lda=dlogits.stride(0),
+                 ldb=x_f.stride(0), out=out)
+
+    def _ln_bwd(self, dy, gamma, x, dgamma_out, dbeta_out, dx_add=None):
+        dx, _, _ = ops.layernorm_bwd(dy, (gamma, None), x, want_dx=True, want_dp=True, dx_add=dx_add,
+                                     dgamma_out=dgamma_out, dbeta_out=dbeta_out)
+        return dx
+
+    # -- loss + gradients --
+    def loss_and_grads(self, w: Weights, grads: dict, y: torch.Tensor, train: bool, seeds: Sequence[int],
+                       n_valid: Optional[torch.Tensor] = None, on_ready=None, sorted_pos=None):
+        """y: [B, S+1] token ids; inputs y[:, :-1], labels y[:, 1:] (loss_and_optimizer_triton.py:280-281).
+        Returns float32[3] = (mean loss over labels != 0, accuracy, fraction of labels != 0)."""
+        ids_in = y[:, :-1].contiguous().to(torch.int32)
+        labels = y[:, 1:].contiguous().to(torch.int32)
+        logits, acts = self.forward(w, ids_in, train, seeds)
+        if sorted_pos is not None:
+            acts["sorted_pos"] = sorted_pos
+        stats, _, dlogits = ops.cross_entropy(labels, logits, cols=self.cfg.vocab, want_grad=True, in_place=True,
+                                              n_valid=n_valid)
+        self.backward(w, grads, dlogits, acts, ids_in, train, seeds, on_ready)
+        return stats
+
+
+# ---- reference-shaped entry points ------------------------------------------------------------------------------------
+def _seeds_or_zero(p_gen_aux, cfg):
+    return list(p_gen_aux) if p_gen_aux is not None else [0] * (1 + 3 * cfg.layers)
+
+
+def t_gpt2_forward_with_acts_t(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
+    """(logits [B,S,V], acts) (model_triton.py:2535-2539). y_mask must be causal and y_indices are ignored, as in the
+    reference's Triton path. The activations object is opaque: pass it to t_gpt2_bkwd3_p_t."""
+    cfg = config_from_params(params, ops.DROPOUT_RATE)
+    step = Gpt2Step(cfg, params[0][0].dtype)
+    w = Weights.from_pytree(params, cfg, step.dtype)
+    ids = y.to(torch.int32).contiguous()
+    logits, acts = step.forward(w, ids, train, _seeds_or_zero(p_gen_aux, cfg))
+    B, S = ids.shape
+    acts["_step"], acts["_w"], acts["_logits_padded"] = step, w, logits
+    return logits.view(B, S, -1)[:, :, :cfg.vocab], acts
+
+
+def t_gpt2_bkwd3_p_t(dloss_dx, acts, params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
+    """Gradient pytree from dloss/dlogits [B,S,V] (model_triton.py:2583-2593)."""
+    step, w = acts["_step"], acts["_w"]
+    cfg = step.cfg
+    ids = y.to(torch.int32).contiguous()
+    T = ids.numel()
+    d = torch.zeros((T, step.vocab_ld), device=dloss_dx.device, dtype=step.dtype)
+    d[:, :cfg.vocab] = dloss_dx.reshape(T, cfg.vocab)
+    grads = {n: torch.empty(s, device=d.device, dtype=torch.float32) for n, s in cfg.param_shapes()}
+    step.backward(w, grads, d, acts, ids, train, _seeds_or_zero(p_gen_aux, cfg))
+    return unflatten_like([grads[n] for n, _ in cfg.param_shapes()], cfg)
+
+
+def t_loss_bkwd3_t(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
+    """(grads pytree, (loss, accuracy, valid fraction)) for y[B, S+1] (loss_and_optimizer_triton.py:279-289)."""
+    cfg = config_from_params(params, ops.DROPOUT_RATE)
+    step = Gpt2Step(cfg, params[0][0].dtype)
+    w = Weights.from_pytree(params, cfg, step.dtype)
+    grads = {n: torch.empty(s, device=y.device, dtype=torch.float32) for n, s in cfg.param_shapes()}
+    stats = step.loss_and_grads(w, grads, y, train, _seeds_or_zero(p_gen_aux, cfg))
+    return unflatten_like([grads[n] for n, _ in cfg.param_shapes()], cfg), (stats[0], stats[1], stats[2])

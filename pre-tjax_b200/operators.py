@@ -1,0 +1,378 @@
+"""Drop-in operator surface: the launcher functions of the reference's Triton path, backed by the sm_100a library.
+
+Names, argument order and return structure follow pre-tjax's ``model_triton.py`` / ``loss_and_optimizer_triton.py``
+(cited per function). Tensors are CUDA tensors, float32 or bfloat16; results are fresh tensors, inputs are never
+modified. Unlike the reference, no output needs zero-initialisation and nothing uses atomics.
+
+The dropout rate is a module constant, as in the reference (model_torch_func.py:2, model_triton.py:21):
+set ``operators.DROPOUT_RATE`` before calling.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import AttnShape, DropoutArgs, PTJ_BF16, PTJ_F32
+
+DROPOUT_RATE = 0.1
+
+
+# ---- plumbing -------------------------------------------------------------------------------------------------------
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return PTJ_F32
+    if t.dtype == torch.bfloat16:
+        return PTJ_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}: the kernels take float32 or bfloat16")
+
+
+def _cuda(t: torch.Tensor, name: str = "tensor") -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must live on a CUDA device: there is no CPU implementation")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    t = _cuda(t)
+    return t if t.dtype == torch.float32 else t.float()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _seed(p_gen_aux) -> int:
+    return 0 if p_gen_aux is None else int(p_gen_aux) & 0xFFFFFFFFFFFFFFFF
+
+
+# ---- LayerNorm ------------------------------------------------------------------------------------------------------
+def t_layernorm_fwd_t(layer_params, x: torch.Tensor) -> torch.Tensor:
+    """gamma * (x - mean) / unbiased_std + beta over the last dim (model_triton.py:1625-1637)."""
+    x = _cuda(x, "x")
+    gamma, beta = _f32(layer_params[0]), _f32(layer_params[1])
+    y = torch.empty_like(x)
+    dim = x.shape[-1]
+    rows = x.numel() // dim if dim else 0
+    _lib.check(_lib.lib().ptj_layernorm_fwd(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), rows, dim, _dt(x), _stream()),
+               "ptj_layernorm_fwd")
+    return y
+
+
+def layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=True, dx_add=None, dgamma_out=None,
+                  dbeta_out=None):
+    """Fused LayerNorm backward: (dx or None, dgamma or None, dbeta or None); dx_add is added onto dx.
+    dgamma_out / dbeta_out: optional float32 destinations (e.g. views of a flat gradient buffer)."""
+    x = _cuda(x, "x")
+    dy = _cuda(dloss_dx, "dloss_dx")
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    gamma = _f32(layer_params[0])
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    dx = torch.empty_like(x) if want_dx else None
+    dg = db = scratch = None
+    n_scratch = 0
+    if want_dp:
+        dg = dgamma_out if dgamma_out is not None else torch.empty(dim, device=x.device, dtype=torch.float32)
+        db = dbeta_out if dbeta_out is not None else torch.empty(dim, device=x.device, dtype=torch.float32)
+        n_scratch = _lib.lib().ptj_layernorm_bwd_scratch_floats(rows, dim)
+        scratch = torch.empty(max(n_scratch, 1), device=x.device, dtype=torch.float32)
+    if dx_add is not None:
+        dx_add = _cuda(dx_add, "dx_add")
+    _lib.check(
+        _lib.lib().ptj_layernorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx_add), _ptr(dx), _ptr(dg), _ptr(db),
+                                     _ptr(scratch), n_scratch, rows, dim, _dt(x), _stream()),
+        "ptj_layernorm_bwd")
+    return dx, dg, db
+
+
+def t_layernorm_bkwd2_p_t(dloss_dx, layer_params, x):
+    """(dgamma, dbeta) (model_triton.py:1710-1726)."""
+    _, dg, db = layernorm_bwd(dloss_dx, layer_params, x, want_dx=False, want_dp=True)
+    return dg, db
+
+
+def t_layernorm_bkwd2_x_t(dloss_dx, layer_params, x):
+    """dx (model_triton.py:1853-1867)."""
+    dx, _, _ = layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=False)
+    return dx.reshape(dloss_dx.shape)
+
+
+# ---- GELU -----------------------------------------------------------------------------------------------------------
+def t_gelu_fwd_t(x: torch.Tensor) -> torch.Tensor:
+    """tanh-GELU (model_triton.py:254-260)."""
+    x = _cuda(x, "x")
+    y = torch.empty_like(x)
+    _lib.check(_lib.lib().ptj_gelu_fwd(_ptr(x), _ptr(y), x.numel(), _dt(x), _stream()), "ptj_gelu_fwd")
+    return y
+
+
+def t_gelu_bkwd2_t(dloss_dx: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """dloss_dx * gelu'(x) (model_triton.py:296-304)."""
+    x = _cuda(x, "x")
+    dy = _cuda(dloss_dx, "dloss_dx").to(x.dtype)
+    out = torch.empty_like(x)
+    _lib.check(_lib.lib().ptj_gelu_bwd(_ptr(dy), _ptr(x), _ptr(out), x.numel(), _dt(x), _stream()), "ptj_gelu_bwd")
+    return out
+
+
+# ---- dropout --------------------------------------------------------------------------------------------------------
+def dropout(x, train, seed, stream_id=0, residual=None, p=None):
+    x = _cuda(x, "x")
+    if residual is not None:
+        residual = _cuda(residual, "residual").to(x.dtype)
+    y = torch.empty_like(x)
+    p = DROPOUT_RATE if p is None else p
+    _lib.check(_lib.lib().ptj_dropout(_ptr(x), _ptr(residual), _ptr(y), x.numel(), p, int(bool(train)), _seed(seed),
+                                      stream_id, _dt(x), _stream()), "ptj_dropout")
+    return y
+
+
+def t_dropout_fwd_t(x: torch.Tensor, train=True, p_gen_aux=None) -> torch.Tensor:
+    """x * mask in training (keep probability 1 - DROPOUT_RATE, no rescale), x * (1 - DROPOUT_RATE) otherwise
+    (model_triton.py:1496-1506). The mask is a pure function of (p_gen_aux, element index)."""
+    return dropout(x, train, p_gen_aux)
+
+
+def t_dropout_bkwd2_t(dloss_dx: torch.Tensor, x: torch.Tensor, train=True, p_gen_aux=None) -> torch.Tensor:
+    """The same mask applied to the gradient (model_triton.py:1562-1572); x only fixes the shape."""
+    return dropout(dloss_dx, train, p_gen_aux)
+
+
+# ---- log-softmax ------------------------------------------------------------------------------------------------------
+def t_log_softmax_fwd_t(x: torch.Tensor) -> torch.Tensor:
+    """log-softmax over the last dim, any row length (model_triton.py:62-72)."""
+    x = _cuda(x, "x")
+    y = torch.empty_like(x)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    _lib.check(_lib.lib().ptj_log_softmax_fwd(_ptr(x), _ptr(y), rows, cols, cols, cols, _dt(x), _stream()),
+               "ptj_log_softmax_fwd")
+    return y
+
+
+def t_log_softmax_bkwd2_t(dloss_dx: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """dloss_dx - softmax(x) * sum(dloss_dx) (model_triton.py:153-164)."""
+    x = _cuda(x, "x")
+    dy = _cuda(dloss_dx, "dloss_dx").to(x.dtype)
+    dx = torch.empty_like(x)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    _lib.check(_lib.lib().ptj_log_softmax_bwd(_ptr(dy), _ptr(x), _ptr(dx), rows, cols, cols, _dt(x), _stream()),
+               "ptj_log_softmax_bwd")
+    return dx.reshape(dloss_dx.shape)
+
+
+# ---- GEMM -----------------------------------------------------------------------------------------------------------
+def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None, ldb=None, out=None, out_dtype=None,
+         ldc=None, bias=None, epilogue=_lib.EPI_NONE, aux=None, aux_out=None, dropout_args=None, split_k=1,
+         workspace=None):
+    """C[M,N] = op(A) op(B) through ptj_gemm. a_kmajor: A stored [M,K]; else [K,M]. b_kmajor: B stored [N,K]; else [K,N]."""
+    if a.dtype != b.dtype:
+        raise TypeError("operands of a GEMM must share a dtype")
+    if M is None:
+        M, K = (a.shape[0], a.shape[1]) if a_kmajor else (a.shape[1], a.shape[0])
+    if N is None:
+        N = b.shape[0] if b_kmajor else b.shape[1]
+    lda = a.stride(0) if lda is None else lda
+    ldb = b.stride(0) if ldb is None else ldb
+    if out is None:
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    ldc = out.stride(0) if ldc is None else ldc
+    ws_n = 0
+    if split_k > 1:
+        if a.dtype != torch.bfloat16:
+            split_k = 1
+        else:
+            ws_n = split_k * M * N
+            if workspace is None or workspace.numel() < ws_n:
+                workspace = torch.empty(ws_n, device=a.device, dtype=torch.float32)
+    dargs = None
+    if dropout_args is not None:
+        p, train, seed, sid = dropout_args
+        dargs = ctypes.byref(DropoutArgs(p, int(bool(train)), _seed(seed), sid))
+    _lib.check(
+        _lib.lib().ptj_gemm(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(aux), _ptr(aux_out), M, N, K, lda, ldb, ldc,
+                            int(a_kmajor), int(b_kmajor), _dt(a), _dt(out), epilogue, dargs, split_k, _ptr(workspace),
+                            ws_n, _stream()),
+        "ptj_gemm")
+    return out
+
+
+def t_matmul_t(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a[N,K] @ b[K,M] (model_triton.py:373-398). No tile-divisibility restrictions."""
+    a, b = _cuda(a, "a"), _cuda(b, "b")
+    assert a.shape[1] == b.shape[0]
+    return gemm(a, b, a_kmajor=True, b_kmajor=False)
+
+
+def t_linear_fwd_t(layer_params, x: torch.Tensor, activation=None) -> torch.Tensor:
+    """x @ W^T + b with W stored [out, in], optional fused tanh-GELU (the linear variant of t_matmul_k,
+    model_triton.py:314-321, 364-368; math t_linear_fwd :306-307)."""
+    w, bias = _cuda(layer_params[0], "weight"), _f32(layer_params[1])
+    x2 = _cuda(x, "x").reshape(-1, x.shape[-1])
+    out = gemm(x2, w, bias=bias, epilogue=_lib.EPI_GELU if activation == "gelu" else _lib.EPI_NONE)
+    return out.reshape(*x.shape[:-1], w.shape[0])
+
+
+def t_tlayer_ffn_fwd_t(layer_params, x: torch.Tensor, activation_fn=None) -> torch.Tensor:
+    """W2 gelu(W1 x + b1) + b2 with the GELU fused into the first GEMM's epilogue (model_triton.py:1258-1313)."""
+    h = t_linear_fwd_t((layer_params[0], layer_params[1]), x, activation="gelu")
+    return t_linear_fwd_t((layer_params[2], layer_params[3]), h)
+
+
+# ---- attention ------------------------------------------------------------------------------------------------------
+def _attn_shape(B, H, N, D, q, k, v, o_strides):
+    s = AttnShape()
+    s.batch, s.heads, s.seq, s.d_head = B, H, N, D
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v)):
+        assert t.stride(3) == 1, "d_head must be contiguous"
+        setattr(s, name, (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
+    s.o_strides = (ctypes.c_int64 * 3)(*o_strides)
+    return s
+
+
+def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None):
+    """q,k,v,out: [B,H,N,D] strided views (D contiguous). Returns (row_max, row_sum) float32 [B,H,N]."""
+    B, H, N, D = q.shape
+    m = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+    l = torch.empty_like(m)
+    sh = _attn_shape(B, H, N, D, q, k, v, out.stride()[:3])
+    p = DROPOUT_RATE if p is None else p
+    _lib.check(_lib.lib().ptj_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m), _ptr(l), ctypes.byref(sh), p,
+                                       int(bool(train)), _seed(seed), stream_id, _dt(q), _stream()), "ptj_attn_fwd")
+    return m, l
+
+
+def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None):
+    B, H, N, D = q.shape
+    assert d_o.stride() == o.stride(), "dO and O must share a layout"
+    sh = _attn_shape(B, H, N, D, q, k, v, o.stride()[:3])
+    dsh = _attn_shape(B, H, N, D, dq, dk, dv, o.stride()[:3])
+    p = DROPOUT_RATE if p is None else p
+    _lib.check(
+        _lib.lib().ptj_attn_bwd(_ptr(d_o), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(m), _ptr(l), _ptr(dq), _ptr(dk),
+                                _ptr(dv), ctypes.byref(sh), ctypes.byref(dsh), p, int(bool(train)), _seed(seed),
+                                stream_id, _dt(q), _stream()), "ptj_attn_bwd")
+
+
+def t_scaled_dot_prod_attn_fwd3_t(qkv: torch.Tensor, mask: torch.Tensor = None, train=True, p_gen_aux=None):
+    """Causal attention on qkv[B,H,3,N,D] -> (out[B,H,N,D], [row_max, row_sum, out]) (model_triton.py:706-754).
+    `mask` is accepted for signature compatibility and must be the causal mask (as the reference kernel assumes,
+    :728-731); it is never read."""
+    qkv = _cuda(qkv, "qkv")
+    q, k, v = qkv.unbind(dim=2)
+    out = torch.empty(q.shape, device=qkv.device, dtype=qkv.dtype)
+    m, l = attn_fwd(q, k, v, out, train, p_gen_aux)
+    return out, [m, l, out]
+
+
+def t_scaled_dot_prod_attn_bkwd3_t(dloss_dx, acts, qkv: torch.Tensor, mask: torch.Tensor = None, train=True,
+                                   p_gen_aux=None):
+    """(dq, dk, dv), each [B,H,N,D] (model_triton.py:951-1003). Deterministic: no atomics, no zero-filled outputs."""
+    qkv = _cuda(qkv, "qkv")
+    q, k, v = qkv.unbind(dim=2)
+    m, l, out = acts
+    d_o = _cuda(dloss_dx, "dloss_dx").to(qkv.dtype).reshape(out.shape)
+    out = _cuda(out)
+    dq, dk, dv = (torch.empty(q.shape, device=qkv.device, dtype=qkv.dtype) for _ in range(3))
+    attn_bwd(d_o, q, k, v, out, _cuda(m), _cuda(l), dq, dk, dv, train, p_gen_aux)
+    return dq, dk, dv
+
+
+# ---- cross entropy -----------------------------------------------------------------------------------------------------
+def cross_entropy(labels, logits, cols=None, want_grad=True, in_place=False, n_valid=None):
+    """Fused CE forward(+backward). logits [rows, ld]; returns (stats float[3] = loss, accuracy, valid fraction;
+    n_valid float[1]; dlogits or None)."""
+    ld = logits.shape[-1]
+    cols = ld if cols is None else cols
+    rows = logits.numel() // ld
+    labels = _cuda(labels, "labels").reshape(-1).to(torch.int32)
+    row_stats = torch.empty(2 * rows, device=logits.device, dtype=torch.float32)
+    out3 = torch.empty(3, device=logits.device, dtype=torch.float32)
+    count = n_valid is None
+    if count:
+        n_valid = torch.empty(1, device=logits.device, dtype=torch.float32)
+    dlogits = None
+    if want_grad:
+        dlogits = logits if in_place else torch.empty_like(logits)
+    _lib.check(
+        _lib.lib().ptj_cross_entropy(_ptr(labels), _ptr(logits), _ptr(dlogits), _ptr(row_stats), _ptr(n_valid),
+                                     int(count), _ptr(out3), rows, cols, ld, _dt(logits), _stream()),
+        "ptj_cross_entropy")
+    return out3, n_valid, dlogits
+
+
+def t_avg_cross_entropy_loss(y_labels: torch.Tensor, x_logits: torch.Tensor):
+    """(mean loss over labels != 0, number of such labels) (loss_and_optimizer_triton.py:23-32)."""
+    out3, n_valid, _ = cross_entropy(y_labels, _cuda(x_logits, "x_logits"), want_grad=False)
+    return out3[0], n_valid[0].to(torch.int64)
+
+
+def t_avg_cross_entropy_loss_bkwd3_t(y_labels: torch.Tensor, x_logits: torch.Tensor):
+    """(loss[1], n_valid, dlogits) (loss_and_optimizer_triton.py:176-197)."""
+    x = _cuda(x_logits, "x_logits")
+    out3, n_valid, dlogits = cross_entropy(y_labels, x, want_grad=True)
+    return out3[0:1], n_valid[0].to(torch.int64), dlogits.reshape(x_logits.shape)
+
+
+def accuracy_from_logits(y_labels: torch.Tensor, x_logits: torch.Tensor):
+    """Mean over labels != 0 of argmax == label (loss_and_optimizer_triton.py:199-200), from the same kernel."""
+    out3, _, _ = cross_entropy(y_labels, _cuda(x_logits, "x_logits"), want_grad=False)
+    return out3[1]
+
+
+# ---- embedding ------------------------------------------------------------------------------------------------------
+def embed_fwd(ids, w_emb, w_pos, train, seed, stream_id=0, out_dtype=None, p=None):
+    """dropout(w_emb[ids] * sqrt(D) + w_pos) -> [B, S, D] (model_triton.py:166-167, 2338-2341)."""
+    B, S = ids.shape
+    V, D = w_emb.shape
+    ids = _cuda(ids, "ids").to(torch.int32)
+    out_dtype = out_dtype or w_emb.dtype
+    y = torch.empty((B, S, D), device=w_emb.device, dtype=out_dtype)
+    p = DROPOUT_RATE if p is None else p
+    _lib.check(
+        _lib.lib().ptj_embed_fwd(_ptr(ids), _ptr(w_emb), _ptr(w_pos), _ptr(y), B, S, D, V, p, int(bool(train)),
+                                 _seed(seed), stream_id, _dt(w_emb), _dt(y), _stream()), "ptj_embed_fwd")
+    return y
+
+
+def embed_bwd(dy, ids, d_w_emb, d_w_pos, accumulate, train, seed, stream_id=0, sorted_pos=None, p=None):
+    """Scatter the (dropout-masked) gradient into d_w_emb [V,D] (optionally accumulating) and d_w_pos [S,D]."""
+    B, S = ids.shape
+    V, D = d_w_emb.shape
+    ids = _cuda(ids, "ids").to(torch.int32)
+    if sorted_pos is None:
+        sorted_pos = torch.sort(ids.reshape(-1), stable=True).indices.to(torch.int32)
+    p = DROPOUT_RATE if p is None else p
+    _lib.check(
+        _lib.lib().ptj_embed_bwd(_ptr(dy), _ptr(ids), _ptr(sorted_pos), _ptr(d_w_emb), _ptr(d_w_pos), int(accumulate), B,
+                                 S, D, V, p, int(bool(train)), _seed(seed), stream_id, _dt(dy), _stream()),
+        "ptj_embed_bwd")
+
+
+def colsum(x2d, cols=None, out=None):
+    """Column sums of a [rows, ld] matrix (first `cols` columns) in float32: bias gradients."""
+    rows, ld = x2d.shape
+    cols = ld if cols is None else cols
+    if out is None:
+        out = torch.empty(cols, device=x2d.device, dtype=torch.float32)
+    n = _lib.lib().ptj_colsum_scratch_floats(rows, cols)
+    scratch = torch.empty(max(n, 1), device=x2d.device, dtype=torch.float32)
+    _lib.check(_lib.lib().ptj_colsum(_ptr(x2d), _ptr(out), _ptr(scratch), n, rows, cols, ld, _dt(x2d), _stream()),
+               "ptj_colsum")
+    return out
+
+
+def last_kernel_fault() -> int:
+    code = ctypes.c_uint(0)
+    _lib.check(_lib.lib().ptj_last_kernel_fault(_stream(), ctypes.byref(code)), "ptj_last_kernel_fault")
+    return int(code.value)
+

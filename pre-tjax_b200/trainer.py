@@ -1,0 +1,289 @@
+"""Data-parallel GPT-2 training step on flat buffers.
+
+The reference trains on one GPU with gradient accumulation (train_gpt2_triton.py:261, 298-321); here every rank owns
+one GPU and one micro-batch, and the only collective is a sum-allreduce of the gradients:
+
+* parameters, gradients and both Adam moments live in four flat float32 buffers with identical layout, plus a bf16
+  shadow of the parameters that the tensor-core GEMMs read;
+* tensors are laid out in the order in which backward produces their gradients, so a bucket is a contiguous slice
+  that the GEMM epilogues write directly (no pack / unpack copies) and that the fused AdamW reads directly;
+* as soon as every gradient of a bucket has been enqueued, the bucket is all-reduced on a side stream while the
+  compute stream carries on with the rest of backward;
+* clipping uses the norm of the reduced buffer, so it is identical on every rank without another collective.
+
+Loss normalisation under data parallelism: each rank divides by its OWN number of non-padding labels and the ranks'
+gradients are averaged — the same "mean of per-micro-batch means" the reference's accumulation loop computes
+(train_gpt2_triton.py:315-318). With ``global_token_norm=True`` the label count is all-reduced first and the result
+equals the single-process gradient of the concatenated batch exactly.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .gpt2 import GPT2Config, Gpt2Step, MATRIX_TENSORS, Weights, base_name, is_decayed, unflatten_like
+
+ALIGN = 64  # elements; every tensor starts on a 256-byte boundary of the flat buffers
+
+
+def backward_order(cfg: GPT2Config) -> List[str]:
+    """Parameter names in the order their gradients become final during backward."""
+    names = ["b_head", "g_f", "b_f"]
+    for l in reversed(range(cfg.layers)):
+        names += [f"l{l}.{n}" for n in ("b2f", "w2", "b1f", "w1", "g2", "b2", "w_o", "w_qkv", "g1", "b1")]
+    names += ["w_emb", "w_pos"]
+    return names
+
+
+@dataclass
+class FlatLayout:
+    """Offsets of every parameter inside the flat buffers."""
+    names: List[str]
+    shapes: Dict[str, Tuple[int, ...]]
+    offsets: Dict[str, int]
+    total: int
+
+    @staticmethod
+    def build(cfg: GPT2Config) -> "FlatLayout":
+        shapes = dict(cfg.param_shapes())
+        offsets, off = {}, 0
+        names = backward_order(cfg)
+        assert sorted(names) == sorted(shapes), "layout must cover every parameter exactly once"
+        for n in names:
+            offsets[n] = off
+            off += (math.prod(shapes[n]) + ALIGN - 1) // ALIGN * ALIGN
+        return FlatLayout(names, shapes, offsets, off)
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        n = math.prod(self.shapes[name])
+        o = self.offsets[name]
+        return flat[o:o + n].view(self.shapes[name])
+
+    def views(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        return {n: self.view(flat, n) for n in self.names}
+
+    def decay_segments(self) -> Tuple[List[int], List[int]]:
+        """(segment starts incl. final end, decay flag per segment), consecutive equal flags merged."""
+        starts, flags = [], []
+        for n in self.names:
+            f = 1 if is_decayed(n) else 0
+            if not flags or flags[-1] != f:
+                starts.append(self.offsets[n])
+                flags.append(f)
+        starts.append(self.total)
+        return starts, flags
+
+
+@dataclass
+class Bucket:
+    start: int
+    end: int
+    names: List[str]
+    pending: int = 0
+    work: object = None
+    event: object = None
+
+
+def make_buckets(layout: FlatLayout, bucket_elems: int) -> List[Bucket]:
+    """Cut the flat gradient buffer into contiguous buckets at tensor boundaries, in backward order."""
+    buckets, cur = [], None
+    for n in layout.names:
+        size = (math.prod(layout.shapes[n]) + ALIGN - 1) // ALIGN * ALIGN
+        o = layout.offsets[n]
+        if cur is None or (cur.end - cur.start) + size > bucket_elems and cur.names:
+            cur = Bucket(o, o, [])
+            buckets.append(cur)
+        cur.names.append(n)
+        cur.end = o + size
+    return buckets
+
+
+class GradReducer:
+    """Bucketed sum-allreduce of a flat gradient buffer, overlapped with backward. Works with NCCL on CUDA tensors
+    (side stream + events) and with gloo on CPU tensors (synchronous), which is how the host logic is tested."""
+
+    def __init__(self, flat_grads: torch.Tensor, layout: FlatLayout, bucket_mb: float, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.flat = flat_grads
+        self.buckets = make_buckets(layout, max(1, int(bucket_mb * (1 << 20) / 4)))
+        self.owner = {n: i for i, b in enumerate(self.buckets) for n in b.names}
+        self.cuda = flat_grads.is_cuda
+        self.comm_stream = torch.cuda.Stream() if self.cuda else None
+        self.launched: List[int] = []
+        self.reset()
+
+    def reset(self):
+        for b in self.buckets:
+            b.pending = len(b.names)
+            b.work = None
+        self.launched = []
+
+    def mark_ready(self, names: Sequence[str]):
+        for n in names:
+            b = self.buckets[self.owner[n]]
+            b.pending -= 1
+            if b.pending < 0:
+                raise RuntimeError(f"gradient {n} reported ready twice in one step")
+            if b.pending == 0:
+                self._launch(self.owner[n])
+
+    def _launch(self, idx: int):
+        b = self.buckets[idx]
+        view = self.flat[b.start:b.end]
+        if self.cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                b.work = self.dist.all_reduce(view, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True)
+        else:
+            b.work = self.dist.all_reduce(view, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self.launched.append(idx)
+
+    def finish(self):
+        """Block the compute stream (not the host, on CUDA) until every bucket has been reduced."""
+        missing = [b.names for b in self.buckets if b.pending != 0]
+        if missing:
+            raise RuntimeError(f"backward never produced the gradients of {missing[0]}: bucket cannot be reduced")
+        for idx in self.launched:
+            w = self.buckets[idx].work
+            if w is not None:
+                w.wait()  # NCCL: makes the current stream wait for the collective; gloo: blocks the host
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+
+@dataclass
+class TrainConfig:
+    lr: float = 6e-4
+    betas: Tuple[float, float] = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    clip: Optional[float] = 1.0
+    bucket_mb: float = 48.0
+    seed: int = 0
+    global_token_norm: bool = False
+    compute_dtype: torch.dtype = torch.bfloat16
+
+
+def step_seeds(base_seed: int, step: int, rank: int, n: int) -> List[int]:
+    """Dropout seeds of one step, derived on the host (the reference draws them on the GPU and reads them back with
+    .item(), loss_and_optimizer_triton.py:319-325, which stalls the device every step). splitmix64 of
+    (base, step, rank, site): distinct sites, steps and ranks get unrelated Philox keys."""
+    out = []
+    for site in range(n):
+        z = (base_seed * 0x9E3779B97F4A7C15 + step * 0xBF58476D1CE4E5B9 + rank * 0x94D049BB133111EB + site + 1) & (2**64 - 1)
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & (2**64 - 1)
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & (2**64 - 1)
+        out.append(z ^ (z >> 31))
+    return out
+
+
+class Trainer:
+    """fwd + bwd + gradient allreduce + clip + AdamW for one micro-batch per rank."""
+
+    def __init__(self, cfg: GPT2Config, tc: TrainConfig = None, params=None, device="cuda", world: int = 1,
+                 rank: int = 0, group=None):
+        from .optimizer import init_from_config
+        self.cfg, self.tc = cfg, tc or TrainConfig()
+        self.world, self.rank = world, rank
+        self.device = torch.device(device)
+        self.layout = FlatLayout.build(cfg)
+        n = self.layout.total
+        z = lambda dt=torch.float32: torch.zeros(n, device=self.device, dtype=dt)
+        self.p, self.g, self.m, self.v = z(), z(), z(), z()
+        self.shadow = z(torch.bfloat16) if self.tc.compute_dtype == torch.bfloat16 else None
+        if params is None:
+            params = init_from_config(cfg, device="cpu", seed=self.tc.seed)
+        flat_params = [t for grp in params for t in grp]
+        for (name, _), t in zip(cfg.param_shapes(), flat_params):
+            self.layout.view(self.p, name).copy_(t.to(self.device, torch.float32))
+        self.pv, self.gv = self.layout.views(self.p), self.layout.views(self.g)
+        self._refresh_shadow()
+        starts, flags = self.layout.decay_segments()
+        self.seg_start = torch.tensor(starts, device=self.device, dtype=torch.int64)
+        self.seg_decay = torch.tensor(flags, device=self.device, dtype=torch.uint8)
+        self.nseg = len(flags)
+        self.engine = Gpt2Step(cfg, self.tc.compute_dtype)
+        self.sumsq = torch.zeros(1, device=self.device, dtype=torch.float32)
+        ns = _lib.lib().ptj_sumsq_scratch_floats(n)
+        self.sumsq_scratch = torch.empty(ns, device=self.device, dtype=torch.float32)
+        self.reducer = GradReducer(self.g, self.layout, self.tc.bucket_mb, group) if world > 1 else None
+        self.t = 0
+        self.ids_dev = None
+
+    # weights the kernels read: bf16 shadow for matrices, fp32 master for vectors
+    def _refresh_shadow(self):
+        if self.shadow is not None:
+            _lib.check(_lib.lib().ptj_cast_f32_to_bf16(self.p.data_ptr(), self.shadow.data_ptr(), self.p.numel(),
+                                                       torch.cuda.current_stream().cuda_stream), "ptj_cast_f32_to_bf16")
+            sv = self.layout.views(self.shadow)
+            self.w = Weights(self.cfg, {n: (sv[n] if base_name(n) in MATRIX_TENSORS else self.pv[n]) for n in self.layout.names})
+        else:
+            self.w = Weights(self.cfg, dict(self.pv))
+
+    def params_pytree(self):
+        return unflatten_like([self.pv[n] for n, _ in self.cfg.param_shapes()], self.cfg)
+
+    def grads_pytree(self):
+        return unflatten_like([self.gv[n] for n, _ in self.cfg.param_shapes()], self.cfg)
+
+    def step(self, y: torch.Tensor, lr: Optional[float] = None, train: bool = True) -> torch.Tensor:
+        """y: [B, S+1] int32 token ids (host, ideally pinned, or device). Returns float32[3] on the device:
+        mean loss, accuracy, fraction of non-padding labels (of this rank's micro-batch)."""
+        if not y.is_cuda:
+            if self.ids_dev is None or self.ids_dev.shape != y.shape:
+                self.ids_dev = torch.empty(y.shape, device=self.device, dtype=torch.int32)
+            self.ids_dev.copy_(y, non_blocking=True)
+            y = self.ids_dev
+        seeds = step_seeds(self.tc.seed, self.t, self.rank, 1 + 3 * self.cfg.layers)
+        sorted_pos = torch.sort(y[:, :-1].reshape(-1), stable=True).indices.to(torch.int32)
+        n_valid = None
+        if self.reducer is not None:
+            self.reducer.reset()
+            if self.tc.global_token_norm:
+                n_valid = (y[:, 1:] != 0).sum().to(torch.float32).reshape(1)
+                self.reducer.dist.all_reduce(n_valid, group=self.reducer.group)
+                n_valid = n_valid / self.world  # gradients are averaged over ranks afterwards
+        on_ready = self.reducer.mark_ready if self.reducer is not None else None
+        stats = self.engine.loss_and_grads(self.w, self.gv, y, train, seeds, n_valid=n_valid, on_ready=on_ready,
+                                           sorted_pos=sorted_pos)
+        if self.reducer is not None:
+            self.reducer.finish()
+        self.apply_update(lr if lr is not None else self.tc.lr)
+        return stats
+
+    def apply_update(self, lr: float):
+        """Clip by the global norm of the (reduced) gradient buffer and run the fused AdamW; t counts from 1."""
+        lib, st = _lib.lib(), torch.cuda.current_stream().cuda_stream
+        self.t += 1
+        scale = 1.0 / self.world
+        sumsq_ptr, max_norm = 0, 0.0
+        if self.tc.clip is not None:
+            _lib.check(lib.ptj_sumsq(self.g.data_ptr(), self.sumsq.data_ptr(), self.sumsq_scratch.data_ptr(),
+                                     self.sumsq_scratch.numel(), self.g.numel(), st), "ptj_sumsq")
+            sumsq_ptr, max_norm = self.sumsq.data_ptr(), float(self.tc.clip)
+        _lib.check(
+            lib.ptj_adamw(self.p.data_ptr(), self.g.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
+                          self.shadow.data_ptr() if self.shadow is not None else 0, self.p.numel(),
+                          self.seg_start.data_ptr(), self.seg_decay.data_ptr(), self.nseg, lr, self.tc.betas[0],
+                          self.tc.betas[1], self.tc.eps, self.tc.weight_decay, self.t, scale, sumsq_ptr, max_norm, st),
+            "ptj_adamw")
+
+    def grad_norm(self) -> float:
+        """Pre-clip global gradient norm of the last step (host sync; for logging)."""
+        return math.sqrt(float(self.sumsq.item())) / self.world
+
+    def state_dict(self):
+        return {"p": self.p.clone(), "m": self.m.clone(), "v": self.v.clone(), "t": self.t, "seed": self.tc.seed}
+
+    def load_state_dict(self, sd):
+        self.p.copy_(sd["p"]); self.m.copy_(sd["m"]); self.v.copy_(sd["v"])
+        self.t = int(sd["t"])
+        self._refresh_shadow()
