@@ -49,8 +49,10 @@ adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restri
              float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ sumsq, float max_norm) {
   __shared__ int64_t s_start[kMaxSegments + 1];
   __shared__ uint8_t s_decay[kMaxSegments];
-  for (int i = threadIdx.x; i <= nseg; i += blockDim.x) s_start[i] = seg_start[i];
-  for (int i = threadIdx.x; i < nseg; i += blockDim.x) s_decay[i] = seg_decay[i];
+  if (nseg > 0) {  // the segment tables may be null when there are no segments
+    for (int i = threadIdx.x; i <= nseg; i += blockDim.x) s_start[i] = seg_start[i];
+    for (int i = threadIdx.x; i < nseg; i += blockDim.x) s_decay[i] = seg_decay[i];
+  }
   __syncthreads();
   float gs = grad_scale;
   if (sumsq != nullptr) {

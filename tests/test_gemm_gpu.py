@@ -1,0 +1,123 @@
+"""tcgen05 GEMM through the C ABI against float64 products of the same bf16 inputs: every operand layout
+(K-major / MN-major for A and B), ragged edges, both tile widths, split-K, and every epilogue."""
+import math
+
+import pytest
+import torch
+
+from conftest import pkg, rel_err
+from oracle import gpt2_oracle as orc
+from oracle import philox
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2  # bf16 inputs, fp32 accumulate, bf16 or fp32 output
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return pkg("operators")
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(*shape, generator=g)).bfloat16()
+
+
+def no_fault(ops):
+    torch.cuda.synchronize()
+    assert ops.last_kernel_fault() == 0, "a bounded wait inside the kernel ran out"
+
+
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 512, 192), (200, 136, 72), (1024, 768, 768),
+                                   (384, 2304, 768), (8, 8, 8)])
+def test_layouts_and_edges(ops, a_k, b_k, M, N, K):
+    A, B = rnd(M, K, seed=1), rnd(N, K, seed=2)  # logical A[M,K], B[N,K]
+    ref = A.double() @ B.double().t()
+    a_dev = (A if a_k else A.t().contiguous()).cuda()
+    b_dev = (B if b_k else B.t().contiguous()).cuda()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        c = ops.gemm(a_dev, b_dev, a_kmajor=a_k, b_kmajor=b_k, M=M, N=N, K=K, out_dtype=out_dtype)
+        no_fault(ops)
+        assert rel_err(c.float(), ref) < (TOL if out_dtype == torch.bfloat16 else 1e-3)
+
+
+@pytest.mark.parametrize("split", [2, 3, 8])
+def test_split_k_weight_gradient_shape(ops, split):
+    """dW[N_out, N_in] = dY^T X with the token dimension as K: both operands MN-major, fp32 output, split-K."""
+    T, N_out, N_in = 1024, 200, 136
+    dY, X = rnd(T, N_out, seed=1), rnd(T, N_in, seed=2)
+    ref = dY.double().t() @ X.double()
+    out = torch.empty(N_out, N_in, device="cuda", dtype=torch.float32)
+    ops.gemm(dY.cuda(), X.cuda(), a_kmajor=False, b_kmajor=False, M=N_out, N=N_in, K=T, out=out, split_k=split)
+    no_fault(ops)
+    assert rel_err(out, ref) < 1e-3
+    out2 = torch.empty_like(out)
+    ops.gemm(dY.cuda(), X.cuda(), a_kmajor=False, b_kmajor=False, M=N_out, N=N_in, K=T, out=out2, split_k=split)
+    assert torch.equal(out, out2), "split-K must reduce in a fixed order"
+    # accumulate onto existing contents
+    lib = pkg("_lib")
+    base = torch.full_like(out, 0.25)
+    ops.gemm(dY.cuda(), X.cuda(), a_kmajor=False, b_kmajor=False, M=N_out, N=N_in, K=T, out=base, split_k=split,
+             epilogue=lib.EPI_ACCUM)
+    assert rel_err(base, ref + 0.25) < 1e-3
+
+
+def test_epilogues(ops):
+    lib = pkg("_lib")
+    M, N, K = 256, 384, 128
+    A, W = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.1)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(3))
+    acc = A.double() @ W.double().t() + bias.double()
+    a, w, b = A.cuda(), W.cuda(), bias.cuda()
+    # bias only
+    assert rel_err(ops.gemm(a, w, bias=b).float(), acc) < TOL
+    # bias + GELU, pre-activation saved
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    act = ops.gemm(a, w, bias=b, epilogue=lib.EPI_GELU, aux_out=pre)
+    assert rel_err(pre.float(), acc) < TOL
+    assert rel_err(act.float(), orc.gelu(pre.float().cpu().double())) < TOL
+    # GELU backward: acc * gelu'(saved pre-activation)
+    pre_in = rnd(M, N, seed=4)
+    out = ops.gemm(a, w, epilogue=lib.EPI_GELU_BWD, aux=pre_in.cuda())
+    ref = orc.gelu_bwd(A.double() @ W.double().t(), pre_in.double())
+    assert rel_err(out.float(), ref) < TOL
+    # dropout + residual, mask from the host Philox on the logical [M, N] index space
+    p, seed = 0.3, 4242
+    resid = rnd(M, N, seed=5)
+    mask = torch.from_numpy(philox.keep_mask(seed, 0, M * N, p)).view(M, N).double()
+    out = ops.gemm(a, w, bias=b, epilogue=lib.EPI_DROPOUT_RESID, aux=resid.cuda(), dropout_args=(p, True, seed, 0))
+    assert rel_err(out.float(), resid.double() + acc * mask) < TOL
+    out = ops.gemm(a, w, bias=b, epilogue=lib.EPI_DROPOUT_RESID, aux=resid.cuda(), dropout_args=(p, False, seed, 0))
+    assert rel_err(out.float(), resid.double() + acc * (1 - p)) < TOL
+    no_fault(ops)
+
+
+def test_padded_vocab_projection(ops):
+    """LM-head pattern: N not a multiple of anything, leading dimension padded, and the matching input-gradient
+    product whose reduction runs over the ragged dimension."""
+    T, D, V = 256, 64, 1001
+    ld = (V + 127) // 128 * 128
+    X, W = rnd(T, D, seed=1), rnd(V, D, seed=2, scale=0.2)
+    bias = torch.randn(V, generator=torch.Generator().manual_seed(3))
+    logits = torch.full((T, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm(X.cuda(), W.cuda(), bias=bias.cuda(), out=logits, N=V, ldc=ld)
+    ref = X.double() @ W.double().t() + bias.double()
+    assert rel_err(logits[:, :V].float(), ref) < TOL
+    assert float((logits[:, V:] - 7.0).abs().max()) == 0.0, "padding columns must not be written"
+    dl = logits  # pretend gradient; padding columns hold junk that must not leak into the product
+    dx = ops.gemm(dl, W.cuda(), a_kmajor=True, b_kmajor=False, M=T, N=D, K=V, lda=ld, ldb=D)
+    assert rel_err(dx.float(), dl[:, :V].double().cpu() @ W.double()) < TOL
+    dw = torch.empty(V, D, device="cuda", dtype=torch.float32)
+    ops.gemm(dl, X.cuda(), a_kmajor=False, b_kmajor=False, M=V, N=D, K=T, lda=ld, ldb=D, out=dw)
+    assert rel_err(dw, dl[:, :V].double().cpu().t() @ X.double()) < 1e-3
+    no_fault(ops)
+
+
+def test_rejects_bad_arguments(ops):
+    a = rnd(64, 64).cuda()
+    with pytest.raises(RuntimeError, match="aligned"):
+        ops.gemm(a[:, 1:], a, M=64, N=64, K=56, lda=64)  # operand pointer not 16-byte aligned
+    with pytest.raises(RuntimeError, match="shape"):
+        ops.gemm(a, a, M=64, N=64, K=64, lda=8)  # leading dimension smaller than K
