@@ -17,6 +17,9 @@ from . import _lib
 from ._lib import AttnShape, DropoutArgs, PTJ_BF16, PTJ_F32
 
 DROPOUT_RATE = 0.1
+# When set to a list, every tensor-core GEMM appends (start event, stop event, 2*M*N*K) to it: lets a benchmark
+# attribute device time and FLOPs to the GEMM kernel without a profiler.
+GEMM_PROFILE = None
 
 
 # ---- plumbing -------------------------------------------------------------------------------------------------------
@@ -198,11 +201,18 @@ def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None
     if dropout_args is not None:
         p, train, seed, sid = dropout_args
         dargs = ctypes.byref(DropoutArgs(p, int(bool(train)), _seed(seed), sid))
+    prof = GEMM_PROFILE if (GEMM_PROFILE is not None and a.dtype == torch.bfloat16) else None
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     _lib.check(
         _lib.lib().ptj_gemm(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(aux), _ptr(aux_out), M, N, K, lda, ldb, ldc,
                             int(a_kmajor), int(b_kmajor), _dt(a), _dt(out), epilogue, dargs, split_k, _ptr(workspace),
                             ws_n, _stream()),
         "ptj_gemm")
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N * K))
     return out
 
 

@@ -1,0 +1,204 @@
+"""Whole-path parity on the GPU: loss and every gradient of a GPT-2 train step, the optimizer step, determinism, and a
+200-step loss curve, against the CPU oracle and the reference's own outputs (tests/golden)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import pkg, rel_err, tt
+from oracle import gpt2_oracle as orc
+from oracle import philox
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-4
+BF16_TOL = 2e-2
+
+
+def tree_from_golden(g, dims):
+    L = int(dims[2])
+    flat = [tt(g[f"p{i}"]) for i in range(3 + 10 * L + 2)]
+    it = iter(flat)
+    return [[next(it), next(it)], [next(it)]] + [[next(it) for _ in range(10)] for _ in range(L)] + [[next(it), next(it)]]
+
+
+def to_cuda(tree, dtype=None):
+    return [[(t.to(dtype) if dtype is not None else t).cuda() for t in grp] for grp in tree]
+
+
+def flat(tree):
+    return [t for grp in tree for t in grp]
+
+
+def test_tiny_model_fp32_matches_reference_gradients(tiny_golden):
+    g, ops, gpt2 = tiny_golden, pkg("operators"), pkg("gpt2")
+    ops.DROPOUT_RATE = 0.0
+    params = tree_from_golden(g, g["dims"])
+    grads, (loss, acc, frac) = gpt2.t_loss_bkwd3_t(to_cuda(params), tt(g["y"]).cuda(), None, None, True, [1] * 7)
+    assert rel_err(loss, tt(g["loss"])) < F32_TOL
+    assert rel_err(acc, tt(g["acc"])) < 1e-6 and rel_err(frac, tt(g["frac"])) < 1e-6
+    for i, gr in enumerate(flat(grads)):
+        assert tuple(gr.shape) == g[f"g{i}"].shape
+        assert rel_err(gr, tt(g[f"g{i}"])) < F32_TOL, f"gradient {i}"
+    ops.DROPOUT_RATE = 0.1
+
+
+def test_cfg1_fp32_matches_reference(cfg1_golden):
+    """Benchmark configuration 1 (2 layers, d_model 128, 4 heads, FFN 512, seq 128, vocab 1024, batch 4, p = 0)."""
+    g, ops, gpt2, opt = cfg1_golden, pkg("operators"), pkg("gpt2"), pkg("optimizer")
+    ops.DROPOUT_RATE = 0.0
+    V, D, L, H, F, S, B = (int(v) for v in g["dims"])
+    params = opt.init_transformer_gpt2(V, D, L, H, F, S, device="cuda", seed=0)
+    for i, p in enumerate(flat(params)):
+        assert abs(float(p.double().norm()) - float(g[f"p{i}_l2"])) < 1e-6 * max(1.0, float(g[f"p{i}_l2"]))
+    grads, (loss, acc, frac) = gpt2.t_loss_bkwd3_t(params, tt(g["y"]).cuda(), None, None, True, None)
+    assert rel_err(loss, tt(g["loss"])) < F32_TOL
+    assert rel_err(acc, tt(g["acc"])) < 1e-6
+    stride = int(g["stride"])
+    for i, gr in enumerate(flat(grads)):
+        ref_l2 = float(g[f"g{i}_l2"])
+        assert abs(float(gr.double().norm()) - ref_l2) < F32_TOL * max(ref_l2, 1e-12), f"norm of gradient {i}"
+        assert rel_err(gr.reshape(-1)[::stride], tt(g[f"g{i}_sample"])) < F32_TOL, f"gradient {i}"
+    ops.DROPOUT_RATE = 0.1
+
+
+def test_forward_with_acts_and_separate_backward(tiny_golden):
+    """t_gpt2_forward_with_acts_t / t_gpt2_bkwd3_p_t used the way the reference's t_loss_bkwd3_t composes them."""
+    g, ops, gpt2 = tiny_golden, pkg("operators"), pkg("gpt2")
+    ops.DROPOUT_RATE = 0.0
+    params = tree_from_golden(g, g["dims"])
+    y = tt(g["y"])
+    logits, acts = gpt2.t_gpt2_forward_with_acts_t(to_cuda(params), y[:, :-1].cuda(), None, None, True, [3] * 7)
+    ref_logits = orc.forward_gpt2(params, y[:, :-1])
+    assert rel_err(logits, ref_logits) < F32_TOL
+    loss, n, dlogits = ops.t_avg_cross_entropy_loss_bkwd3_t(y[:, 1:].cuda(), logits.contiguous())
+    grads = gpt2.t_gpt2_bkwd3_p_t(dlogits, acts, to_cuda(params), y[:, :-1].cuda(), None, None, True, [3] * 7)
+    for i, gr in enumerate(flat(grads)):
+        assert rel_err(gr, tt(g[f"g{i}"])) < F32_TOL, f"gradient {i}"
+    # evaluation mode scales by (1 - p) at every dropout site
+    ops.DROPOUT_RATE = 0.1
+    logits_e, _ = gpt2.t_gpt2_forward_with_acts_t(to_cuda(params), y[:, :-1].cuda(), None, None, False, None)
+    assert rel_err(logits_e, orc.forward_gpt2(params, y[:, :-1], p=0.1, train=False)) < F32_TOL
+
+
+def _mask_fn(seeds, L, p):
+    def fn(site, shape):
+        if site == "embed":
+            seed = seeds[0]
+        else:
+            l, kind = site.split(".")
+            seed = seeds[1 + 3 * int(l[1:]) + {"attn": 0, "res1": 1, "res2": 2}[kind]]
+        n = math.prod(shape)
+        return torch.from_numpy(philox.keep_mask(seed, 0, n, p)).view(shape)
+    return fn
+
+
+def test_training_mode_dropout_all_four_sites():
+    """p = 0.1 at the embedding, the attention probabilities and both residual branches; the oracle receives the
+    same Philox masks, so loss and gradients must agree like in the p = 0 case."""
+    ops, gpt2 = pkg("operators"), pkg("gpt2")
+    p = 0.1
+    ops.DROPOUT_RATE = p
+    prm = orc.init_params(96, 32, 2, 2, 64, 24, seed=4)
+    y = torch.randint(1, 96, (3, 25), generator=torch.Generator().manual_seed(1), dtype=torch.int32)
+    seeds = [1000 + 17 * i for i in range(7)]
+    grads, (loss, acc, frac) = gpt2.t_loss_bkwd3_t(to_cuda(prm), y.cuda(), None, None, True, seeds)
+    ref, (rloss, racc, _) = orc.loss_and_grads(prm, y, p=p, train=True, mask_fn=_mask_fn(seeds, 2, p))
+    assert rel_err(loss, rloss) < F32_TOL
+    for i, (a, b) in enumerate(zip(flat(grads), flat(ref))):
+        assert rel_err(a, b) < F32_TOL, f"gradient {i}"
+    # and it differs from the p = 0 result (the masks really were applied)
+    ops.DROPOUT_RATE = 0.0
+    _, (loss0, _, _) = gpt2.t_loss_bkwd3_t(to_cuda(prm), y.cuda(), None, None, True, seeds)
+    assert abs(float(loss0) - float(loss)) > 1e-4
+    ops.DROPOUT_RATE = 0.1
+
+
+@pytest.mark.parametrize("dims", [(1024, 128, 2, 4, 512, 128, 4), (512, 128, 2, 2, 256, 128, 2)])
+def test_bf16_path_against_fp32_oracle(dims):
+    """bf16 storage / fp32 accumulate: tcgen05 GEMMs everywhere; head size 32 keeps attention on the CUDA-core
+    kernels, head size 64 with seq 128 takes the tensor-core attention kernels."""
+    ops, gpt2 = pkg("operators"), pkg("gpt2")
+    ops.DROPOUT_RATE = 0.0
+    V, D, L, H, F, S, B = dims
+    prm = orc.init_params(V, D, L, H, F, S, seed=0)
+    prm_r = [[t.bfloat16().float() if t.dim() > 1 else t for t in grp] for grp in prm]  # weights as the GPU sees them
+    y = torch.randint(1, V, (B, S + 1), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+    gp = [[(t.bfloat16() if t.dim() > 1 else t).cuda() for t in grp] for grp in prm]
+    grads, (loss, acc, frac) = gpt2.t_loss_bkwd3_t(gp, y.cuda(), None, None, True, None)
+    ref, (rloss, _, _) = orc.loss_and_grads(prm_r, y)
+    assert pkg("operators").last_kernel_fault() == 0
+    assert rel_err(loss, rloss) < BF16_TOL
+    for i, (a, b) in enumerate(zip(flat(grads), flat(ref))):
+        assert rel_err(a, b) < BF16_TOL, f"gradient {i}: {rel_err(a, b):.3e}"
+    ops.DROPOUT_RATE = 0.1
+
+
+def test_gradients_are_bit_reproducible():
+    ops, gpt2 = pkg("operators"), pkg("gpt2")
+    ops.DROPOUT_RATE = 0.1
+    for dtype in (torch.float32, torch.bfloat16):
+        prm = orc.init_params(256, 128, 2, 2, 256, 128, seed=2)
+        gp = [[(t.to(dtype) if t.dim() > 1 else t).cuda() for t in grp] for grp in prm]
+        y = torch.randint(0, 256, (2, 129), generator=torch.Generator().manual_seed(3), dtype=torch.int32).cuda()
+        seeds = list(range(50, 57))
+        g1, s1 = gpt2.t_loss_bkwd3_t(gp, y, None, None, True, seeds)
+        g2, s2 = gpt2.t_loss_bkwd3_t(gp, y, None, None, True, seeds)
+        assert all(torch.equal(a, b) for a, b in zip(flat(g1), flat(g2)))
+        assert torch.equal(s1[0], s2[0])
+
+
+def _oracle_train(prm, batches, lr, betas, eps, wd, clip):
+    mom = [[[torch.zeros_like(t) for t in grp] for grp in prm] for _ in range(2)]
+    mask = orc.decay_mask(prm)
+    losses = []
+    for i, y in enumerate(batches):
+        grads, (loss, _, _) = orc.loss_and_grads(prm, y)
+        s = orc.clip_scale(orc.grads_l2norm(grads), clip)
+        grads = [[g * s for g in grp] for grp in grads]
+        prm, mom = orc.adam_w(prm, grads, lr, betas, eps, mom, i, wd, mask)
+        losses.append(float(loss))
+    return prm, losses
+
+
+def test_loss_curve_200_steps_fp32_trainer():
+    """fwd + bwd + clip + AdamW for 200 steps on a toy model: every loss within 1 % of the oracle's curve."""
+    gpt2, tr = pkg("gpt2"), pkg("trainer")
+    cfg = gpt2.GPT2Config(vocab=64, dim=32, layers=2, heads=2, ffn=64, seq=16, dropout=0.0)
+    prm = orc.init_params(64, 32, 2, 2, 64, 16, seed=7)
+    g = torch.Generator().manual_seed(11)
+    batches = [torch.randint(1, 64, (4, 17), generator=g, dtype=torch.int32) for _ in range(8)] * 25
+    tc = tr.TrainConfig(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip=1.0, compute_dtype=torch.float32)
+    t = tr.Trainer(cfg, tc, params=prm, device="cuda")
+    gpu_losses = [t.step(y)[0] for y in batches]
+    gpu_losses = [float(x) for x in torch.stack(gpu_losses).cpu()]
+    _, ref_losses = _oracle_train(prm, batches, 3e-3, (0.9, 0.95), 1e-8, 0.1, 1.0)
+    assert ref_losses[-1] < 0.7 * ref_losses[0], "the toy problem is expected to train"
+    worst = max(abs(a - b) / b for a, b in zip(gpu_losses, ref_losses))
+    assert worst < 1e-2, f"loss curve deviates by {worst:.3%}"
+    assert abs(gpu_losses[0] - ref_losses[0]) / ref_losses[0] < F32_TOL
+
+
+def test_trainer_single_step_matches_oracle_update():
+    """One optimizer step: parameters and moments after clip + AdamW (t = 1) against the oracle."""
+    gpt2, tr = pkg("gpt2"), pkg("trainer")
+    cfg = gpt2.GPT2Config(vocab=80, dim=32, layers=1, heads=2, ffn=64, seq=16, dropout=0.0)
+    prm = orc.init_params(80, 32, 1, 2, 64, 16, seed=9)
+    y = torch.randint(1, 80, (2, 17), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+    tc = tr.TrainConfig(lr=1e-3, eps=1e-3, weight_decay=0.1, clip=0.5, compute_dtype=torch.float32)
+    t = tr.Trainer(cfg, tc, params=prm, device="cuda")
+    t.step(y)
+    grads, _ = orc.loss_and_grads(prm, y)
+    norm = orc.grads_l2norm(grads)
+    assert abs(t.grad_norm() - norm) < 1e-4 * norm
+    assert norm > 0.5, "the clip is meant to be active in this test"
+    s = orc.clip_scale(norm, 0.5)
+    mom = [[[torch.zeros_like(x) for x in grp] for grp in prm] for _ in range(2)]
+    new_p, mom = orc.adam_w(prm, [[g * s for g in grp] for grp in grads], 1e-3, (0.9, 0.95), 1e-3, mom, 0, 0.1,
+                            orc.decay_mask(prm))
+    for (name, _), a, b in zip(cfg.param_shapes(), flat(t.params_pytree()), flat(new_p)):
+        assert rel_err(a, b) < 1e-5, name
+    mv = t.layout.views(t.m)
+    for (name, _), b in zip(cfg.param_shapes(), flat(mom[0])):
+        assert rel_err(mv[name], b) < 2e-4, name
