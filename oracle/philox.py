@@ -50,3 +50,19 @@ def keep_mask(seed: int, stream_id: int, n: int, p: float) -> np.ndarray:
                            np.full(nblk, CTR3, np.uint64)], [seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF])
     flat = np.stack(words, axis=1).reshape(-1)[:n]
     return (flat >= np.uint32(threshold(p))).astype(np.float32)
+
+
+def keep_mask16(seed: int, stream_id: int, n: int, p: float) -> np.ndarray:
+    """Mask stream of the attention-probability site: 16 random bits per element, 8 elements per Philox call
+    (element e of a call takes the low half of word e // 2 when e is even, the high half when odd); dropped when
+    below floor(p * 65536)."""
+    nblk = (n + 7) // 8
+    ctr = np.arange(nblk, dtype=np.uint64)
+    words = philox4x32_10([ctr & U32, ctr >> np.uint64(32), np.full(nblk, stream_id, np.uint64),
+                           np.full(nblk, CTR3, np.uint64)], [seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF])
+    halves = []
+    for w in words:
+        halves += [w & np.uint32(0xFFFF), w >> np.uint32(16)]
+    flat = np.stack(halves, axis=1).reshape(-1)[:n]
+    t = min(65535, max(0, int(float(np.float32(p)) * 65536.0)))
+    return (flat >= np.uint32(t)).astype(np.float32)

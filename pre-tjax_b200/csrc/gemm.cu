@@ -163,7 +163,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
-      if (!mbar_wait(&tmem_full[buf], aphase, ctx, 0x0301u)) { ok = false; break; }
+      ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0301u);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+      if (!ok) break;
       tc_fence_after_sync();
       const int64_t row = static_cast<int64_t>(m_blk) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
