@@ -139,16 +139,29 @@ __host__ __device__ __forceinline__ bool dropout_keep(uint64_t seed, uint32_t st
 }
 
 // ---- tanh-GELU (model_torch_func.py:60-62) -------------------------------------------------------------------
+// FAST = true uses the hardware tanh approximation (relative error about 2^-11): invisible once the result is rounded
+// to bf16 (2^-8), and it keeps GEMM epilogues off the critical path. The float32 path always uses tanhf.
+template <bool FAST>
+__device__ __forceinline__ float tanh_sel(float x) {
+  if (FAST) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  return tanhf(x);
+}
+template <bool FAST = false>
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k = 0.7978845608028654f;  // sqrt(2/pi)
-  const float t = tanhf(k * (x + 0.044715f * x * x * x));
+  const float t = tanh_sel<FAST>(k * (x + 0.044715f * x * x * x));
   return 0.5f * x * (1.f + t);
 }
 // d gelu / dx (model_triton.py:262-267)
+template <bool FAST = false>
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float k = 0.7978845608028654f;
   const float x2 = x * x;
-  const float t = tanhf(k * (x + 0.044715f * x * x2));
+  const float t = tanh_sel<FAST>(k * (x + 0.044715f * x * x2));
   const float dt = (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x2);
   return 0.5f * (1.f + t) + 0.5f * x * dt;
 }

@@ -27,12 +27,13 @@ gelu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ ou
     Elem<T>::load_vec(a + i * V, va);
     if (OP == 1) Elem<T>::load_vec(b + i * V, vb);
 #pragma unroll
-    for (int j = 0; j < V; ++j) o[j] = OP == 0 ? gelu_tanh(va[j]) : va[j] * gelu_tanh_grad(vb[j]);
+    for (int j = 0; j < V; ++j)
+      o[j] = OP == 0 ? gelu_tanh<sizeof(T) == 2>(va[j]) : va[j] * gelu_tanh_grad<sizeof(T) == 2>(vb[j]);
     Elem<T>::store_vec(out + i * V, o);
   }
   for (int64_t i = nvec * V + tid; i < n; i += stride) {
     const float x = Elem<T>::load(a + i);
-    Elem<T>::store(out + i, OP == 0 ? gelu_tanh(x) : x * gelu_tanh_grad(Elem<T>::load(b + i)));
+    Elem<T>::store(out + i, OP == 0 ? gelu_tanh<sizeof(T) == 2>(x) : x * gelu_tanh_grad<sizeof(T) == 2>(Elem<T>::load(b + i)));
   }
 }
 

@@ -55,33 +55,45 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
 }
 
 // Gradient w.r.t. the embedding table (model_triton.py:183-185, 205-213). Token positions arrive stably sorted by
-// token id; the warp that sits on the first position of a run of equal ids walks the whole run in order, so every
-// table row is produced by one warp with a fixed summation order.
+// token id; the thread block that lands on the first position of a run of equal ids walks the whole run in order
+// (threads across the feature dimension, 4 features each), so every table row is produced by one block with a fixed
+// summation order and no atomics. Frequent tokens (a Zipf head) make long runs: the walk is a coalesced row read and
+// one Philox call per 4 features per row.
 template <typename T>
 __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t j = warp; j < tokens; j += nwarps) {
+  const bool masked = train && thr != 0u;
+  for (int64_t j = blockIdx.x; j < tokens; j += gridDim.x) {
     const int32_t id = ids[sorted_pos[j]];
-    if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run
+    if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run (uniform over the block)
     if (id < 0 || id >= vocab) continue;
     int64_t end = j + 1;
     while (end < tokens && ids[sorted_pos[end]] == id) ++end;
     float* out = d_w_emb + static_cast<int64_t>(id) * dim;
-    for (int c = lane; c < dim; c += 32) {
-      float s = 0.f;
+    for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {  // dim % 4 == 0 is checked on the host
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       for (int64_t q = j; q < end; ++q) {
         const int64_t idx = static_cast<int64_t>(sorted_pos[q]) * dim + c;
-        const float k =
-            train ? (dropout_keep(seed, stream_id, static_cast<uint64_t>(idx), thr) ? 1.f : 0.f) : eval_scale;
-        s += Elem<T>::load(dy + idx) * k;
+        float k0 = train ? 1.f : eval_scale, k1 = k0, k2 = k0, k3 = k0;
+        if (masked) {
+          const Philox4 r = philox4x32_10(seed, static_cast<uint64_t>(idx) >> 2, stream_id);
+          k0 = r.x >= thr ? 1.f : 0.f;
+          k1 = r.y >= thr ? 1.f : 0.f;
+          k2 = r.z >= thr ? 1.f : 0.f;
+          k3 = r.w >= thr ? 1.f : 0.f;
+        }
+        s0 = fmaf(Elem<T>::load(dy + idx), k0, s0);
+        s1 = fmaf(Elem<T>::load(dy + idx + 1), k1, s1);
+        s2 = fmaf(Elem<T>::load(dy + idx + 2), k2, s2);
+        s3 = fmaf(Elem<T>::load(dy + idx + 3), k3, s3);
       }
-      s *= scale;
-      out[c] = accumulate ? out[c] + s : s;
+      if (accumulate) {
+        out[c] += s0 * scale; out[c + 1] += s1 * scale; out[c + 2] += s2 * scale; out[c + 3] += s3 * scale;
+      } else {
+        out[c] = s0 * scale; out[c + 1] = s1 * scale; out[c + 2] = s2 * scale; out[c + 3] = s3 * scale;
+      }
     }
   }
 }
@@ -93,36 +105,64 @@ __global__ void zero_kernel(float* __restrict__ p, int64_t n) {
     p[i] = 0.f;
 }
 
-// stage 1: block (bx, by) sums rows [by*chunk, (by+1)*chunk) of columns bx*256 + tid
-template <typename T>
-__global__ void __launch_bounds__(256)
+// stage 1: block (bx, by) sums rows [by*chunk, (by+1)*chunk) of the 16-byte column groups bx*128 + tid
+// (VEC = true) or of single columns (VEC = false, any alignment).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(128)
 colsum_stage1_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols, int64_t ld,
                      int64_t chunk) {
-  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  constexpr int V = VEC ? Elem<T>::kVec : 1;
+  const int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // column group
+  const int64_t c0 = g * V;
+  if (c0 >= cols) return;
   const int64_t r0 = static_cast<int64_t>(blockIdx.y) * chunk;
   const int64_t r1 = r0 + chunk < rows ? r0 + chunk : rows;
-  float s = 0.f;
-  for (int64_t r = r0; r < r1; ++r) s += Elem<T>::load(x + r * ld + c);
-  partial[static_cast<int64_t>(blockIdx.y) * cols + c] = s;
+  float s[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) s[j] = 0.f;
+#pragma unroll 4
+  for (int64_t r = r0; r < r1; ++r) {
+    if (VEC) {
+      float v[Elem<T>::kVec];
+      Elem<T>::load_vec(x + r * ld + c0, v);  // may read padding columns (ld is a multiple of the vector), never writes them
+#pragma unroll
+      for (int j = 0; j < V; ++j) s[j] += v[j];
+    } else {
+      s[0] += Elem<T>::load(x + r * ld + c0);
+    }
+  }
+  float* out = partial + static_cast<int64_t>(blockIdx.y) * cols;
+#pragma unroll
+  for (int j = 0; j < V; ++j)
+    if (c0 + j < cols) out[c0 + j] = s[j];
 }
+// stage 2: a block owns 32 columns; its 8 warps sum strided subsets of the chunk rows, added in warp order.
 __global__ void __launch_bounds__(256)
 colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t cols, int nchunks) {
-  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
   float s = 0.f;
-  for (int k = 0; k < nchunks; ++k) s += partial[static_cast<int64_t>(k) * cols + c];
-  out[c] = s;
+  if (c < cols)
+    for (int k = warp; k < nchunks; k += 8) s += partial[static_cast<int64_t>(k) * cols + c];
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    out[c] = t;
+  }
 }
 
 inline int colsum_chunks(int64_t rows, int64_t cols) {
-  // enough row chunks to fill the machine: (cols/256) * chunks >= ~4 blocks per SM
-  const int64_t strips = ceil_div(cols, 256);
-  int64_t want = ceil_div(static_cast<int64_t>(kNumSMs) * 4, strips);
-  if (want < 1) want = 1;
-  const int64_t max_chunks = ceil_div(rows, 16);
+  // enough row chunks to fill the machine (about 8 blocks of 128 threads per SM), at least 32 rows per chunk
+  const int64_t strips = ceil_div(ceil_div(cols, 8), 128);
+  int64_t want = ceil_div(static_cast<int64_t>(kNumSMs) * 8, strips);
+  const int64_t max_chunks = ceil_div(rows, 32);
   if (want > max_chunks) want = max_chunks;
   if (want > 1024) want = 1024;
+  if (want < 1) want = 1;
   return static_cast<int>(want);
 }
 
@@ -165,7 +205,7 @@ extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* 
 extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb,
                              float* d_w_pos, int accumulate, int64_t batch, int64_t seq, int64_t dim, int64_t vocab,
                              float p, int train, uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
-  if (batch < 1 || seq < 1 || dim < 1 || vocab < 1 || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+  if (batch < 1 || seq < 1 || dim < 4 || dim % 4 != 0 || vocab < 1 || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
   if (batch * seq > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
   if (!dy || !ids || !sorted_pos || !d_w_emb || !d_w_pos) return PTJ_ERR_BAD_SHAPE;
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
@@ -177,7 +217,7 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
     zero_kernel<<<flat_grid(vocab * dim, 256 * 4), 256, 0, st>>>(d_w_emb, vocab * dim);
     PTJ_CHECK_LAUNCH();
   }
-  const int grid_e = flat_grid(tokens, 8);  // one warp per sorted position
+  const int grid_e = flat_grid(tokens, 1);  // one block per sorted position (only run heads do work)
   const int grid_p = flat_grid(seq * dim, 256);
   if (dtype == PTJ_F32) {
     embed_bwd_kernel<float><<<grid_e, 256, 0, st>>>(static_cast<const float*>(dy), ids, sorted_pos, d_w_emb, 1, tokens,
@@ -211,14 +251,19 @@ extern "C" int ptj_colsum(const void* x, float* out, float* scratch, size_t scra
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int nchunks = colsum_chunks(rows, cols);
   const int64_t chunk = ceil_div(rows, nchunks);
-  dim3 grid(static_cast<unsigned>(ceil_div(cols, 256)), static_cast<unsigned>(nchunks));
-  if (dtype == PTJ_F32)
-    colsum_stage1_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
-  else
-    colsum_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols,
-                                                              ld, chunk);
+  const int V = dtype == PTJ_F32 ? 4 : 8;
+  const bool vec = aligned16(x) && ld % V == 0 && ceil_div(cols, V) * V <= ld;
+  const int64_t groups = vec ? ceil_div(cols, V) : cols;
+  dim3 grid(static_cast<unsigned>(ceil_div(groups, 128)), static_cast<unsigned>(nchunks));
+  if (dtype == PTJ_F32) {
+    if (vec) colsum_stage1_kernel<float, true><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    else colsum_stage1_kernel<float, false><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+  } else {
+    if (vec) colsum_stage1_kernel<__nv_bfloat16, true><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    else colsum_stage1_kernel<__nv_bfloat16, false><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+  }
   PTJ_CHECK_LAUNCH();
-  colsum_stage2_kernel<<<static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st>>>(scratch, out, cols, nchunks);
+  colsum_stage2_kernel<<<static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st>>>(scratch, out, cols, nchunks);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

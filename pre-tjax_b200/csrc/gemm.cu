@@ -8,6 +8,8 @@
 // any transposed copy. Work items = output tiles x K splits, walked by a static persistent schedule.
 //
 // fp32 inputs: plain shared-memory tiled FMA kernel (exact fp32, any shape) for the fp32 parity path.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "tc_common.cuh"
@@ -20,17 +22,19 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kEpilogueWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kTmemCols = 512;     // two accumulator buffers, the second at column 256
+  static constexpr int kAccStride = 256;
 };
 
 struct GemmParams {
@@ -67,7 +71,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 4);
+      mbar_init(&tmem_empty[b], kEpilogueWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -134,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t aphase = (it >> 1) & 1u;
         if (!mbar_wait(&tmem_empty[buf], aphase ^ 1u, ctx, 0x0201u)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * Cfg::kAccStride);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, ctx, 0x0202u)) { ok = false; break; }
           tc_fence_after_sync();
@@ -156,6 +160,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int half = (warp - 2) >> 2;  // two warps share a lane quarter and split the tile's columns
+    constexpr int kChunks = BN / 64;   // 32-column chunks per warp
     int it = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
@@ -168,16 +174,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!ok) break;
       tc_fence_after_sync();
       const int64_t row = static_cast<int64_t>(m_blk) * BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * Cfg::kAccStride + half * (BN / 2));
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + chunk * 32, r);
         tmem_ld_wait();
         float acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + chunk * 32;
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + half * (BN / 2) + chunk * 32;
         if (p.split_k > 1) {
           if (row < p.M) {
             float* w = p.workspace + (static_cast<int64_t>(split) * p.M + row) * p.N;
@@ -217,21 +224,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
 }
 
-// c[m, n] = (accumulate ? c : 0) + bias[n] + sum_s ws[s, m, n]
-template <typename TOut>
+// c[m, n] = (accumulate ? c : 0) + bias[n] + sum_s ws[s, m, n]; four columns per thread (N % 4 == 0) or one.
+template <typename TOut, int W>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restrict__ c, const float* __restrict__ bias, int64_t M,
                      int64_t N, int64_t ldc, int split_k, int accumulate) {
   const int64_t total = M * N;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * W; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x * W) {
     const int64_t m = i / N, n = i - m * N;
-    float s = 0.f;
-    for (int k = 0; k < split_k; ++k) s += ws[static_cast<int64_t>(k) * total + i];
-    if (bias != nullptr) s += bias[n];
+    float s[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) s[j] = 0.f;
+    for (int k = 0; k < split_k; ++k) {
+      const float* src = ws + static_cast<int64_t>(k) * total + i;
+      if (W == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src);
+        s[0] += v.x; s[1] += v.y; s[2] += v.z; s[3] += v.w;
+      } else {
+        s[0] += *src;
+      }
+    }
     TOut* dst = c + m * ldc + n;
-    if (accumulate) s += Elem<TOut>::load(dst);
-    Elem<TOut>::store(dst, s);
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      if (bias != nullptr) s[j] += bias[n + j];
+      if (accumulate) s[j] += Elem<TOut>::load(dst + j);
+      Elem<TOut>::store(dst + j, s[j]);
+    }
   }
 }
 
@@ -378,12 +398,20 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   p.fault = tc::fault_word();
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
 
-  // tile width: fewer, fatter tiles unless that leaves SMs idle in the last wave
-  auto waves_cost = [&](int bn) {
+  // tile width: fewer, fatter tiles (less operand traffic per FLOP) unless that leaves SMs idle in the last wave.
+  // cost = waves x tile width x relative cost per column of that width
+  auto waves_cost = [&](int bn, double penalty) {
     const int64_t items = static_cast<int64_t>(p.num_m) * ceil_div(N, bn) * split_k;
-    return ceil_div(items, kNumSMs) * bn;
+    return static_cast<double>(ceil_div(items, kNumSMs)) * bn * penalty;
   };
-  const int bn = waves_cost(128) < waves_cost(256) ? 128 : 256;
+  int bn = 256;
+  double best = waves_cost(256, 1.0);
+  if (waves_cost(192, 1.08) < best) { bn = 192; best = waves_cost(192, 1.08); }
+  if (waves_cost(128, 1.35) < best) { bn = 128; }
+  if (const char* e = std::getenv("PTJ_GEMM_BN")) {  // tuning aid
+    const int v = std::atoi(e);
+    if (v == 128 || v == 192 || v == 256) bn = v;
+  }
   p.num_n = static_cast<int>(ceil_div(N, bn));
   if (static_cast<int64_t>(p.num_m) * p.num_n * split_k > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
 
@@ -409,20 +437,24 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
                         : launch_tc<BN_, true, false>(ta, tb, p, st))            \
             : (b_kmajor ? launch_tc<BN_, false, true>(ta, tb, p, st)             \
                         : launch_tc<BN_, false, false>(ta, tb, p, st)))
-  rc = bn == 128 ? PTJ_TC(128) : PTJ_TC(256);
+  rc = bn == 128 ? PTJ_TC(128) : (bn == 192 ? PTJ_TC(192) : PTJ_TC(256));
 #undef PTJ_TC
   if (rc != PTJ_OK) return rc;
 
   if (split_k > 1) {
     const int64_t total = M * N;
-    int64_t blocks = ceil_div(total, 256);
+    const bool w4 = N % 4 == 0;
+    int64_t blocks = ceil_div(total, 256 * (w4 ? 4 : 1));
     if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
-    if (out_dtype == PTJ_F32)
-      splitk_reduce_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N,
-                                                                            ldc, split_k, epilogue == PTJ_EPI_ACCUM);
-    else
-      splitk_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
-          workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    const int acc = epilogue == PTJ_EPI_ACCUM;
+    const int g = static_cast<int>(blocks);
+    if (out_dtype == PTJ_F32) {
+      if (w4) splitk_reduce_kernel<float, 4><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+      else splitk_reduce_kernel<float, 1><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+    } else {
+      if (w4) splitk_reduce_kernel<__nv_bfloat16, 4><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+      else splitk_reduce_kernel<__nv_bfloat16, 1><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    }
     PTJ_CHECK_LAUNCH();
   }
   return PTJ_OK;

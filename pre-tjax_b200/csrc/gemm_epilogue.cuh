@@ -56,7 +56,7 @@ __device__ __forceinline__ void epilogue_row_segment(const EpilogueParams& ep, i
     for (int j = 0; j < CNT; ++j) {
       float x = acc[j];
       if (sizeof(TOut) == 2) x = __bfloat162float(__float2bfloat16_rn(x));
-      acc[j] = gelu_tanh(x);
+      acc[j] = gelu_tanh<sizeof(TOut) == 2>(x);
     }
   } else if (ep.mode == PTJ_EPI_GELU_BWD || ep.mode == PTJ_EPI_DROPOUT_RESID || ep.mode == PTJ_EPI_ACCUM) {
     float a[CNT];
@@ -75,7 +75,7 @@ __device__ __forceinline__ void epilogue_row_segment(const EpilogueParams& ep, i
     }
     if (ep.mode == PTJ_EPI_GELU_BWD) {
 #pragma unroll
-      for (int j = 0; j < CNT; ++j) acc[j] *= gelu_tanh_grad(a[j]);
+      for (int j = 0; j < CNT; ++j) acc[j] *= gelu_tanh_grad<sizeof(TOut) == 2>(a[j]);
     } else if (ep.mode == PTJ_EPI_ACCUM) {
 #pragma unroll
       for (int j = 0; j < CNT; ++j) acc[j] += a[j];

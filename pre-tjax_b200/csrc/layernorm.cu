@@ -8,6 +8,17 @@ namespace ptj {
 namespace {
 
 constexpr int kLnThreads = 256;
+
+// V consecutive floats (V = 4 or 8, 16-byte aligned) with 16-byte loads. Scalar loads here would make every lane
+// touch its own 32-byte sector per instruction and swamp L1 with 30x the traffic of the activations themselves.
+template <int V>
+__device__ __forceinline__ void load_params(const float* __restrict__ p, float (&out)[V]) {
+#pragma unroll
+  for (int q = 0; q < V / 4; ++q) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(p) + q);
+    out[4 * q] = t.x; out[4 * q + 1] = t.y; out[4 * q + 2] = t.z; out[4 * q + 3] = t.w;
+  }
+}
 constexpr int kLnWarps = kLnThreads / 32;
 
 inline int ln_grid(int64_t rows) {
@@ -17,27 +28,18 @@ inline int ln_grid(int64_t rows) {
 }
 inline int ln_bwd_grid(int64_t rows) {
   int64_t blocks = ceil_div(rows, kLnWarps);
-  int64_t cap = static_cast<int64_t>(kNumSMs) * 2;
+  int64_t cap = static_cast<int64_t>(kNumSMs) * 2;  // two resident blocks per SM; each block leaves one partial row
   return static_cast<int>(blocks < cap ? blocks : cap);
 }
 
 template <typename T, int NV>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, NV <= 4 ? 4 : 2)
 ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               T* __restrict__ y, int64_t rows, int dim) {
   constexpr int V = Elem<T>::kVec;
   const int lane = threadIdx.x & 31;
   const int nvec = dim / V;
-  float g[NV][V], b[NV][V];
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int vi = lane + 32 * i;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-      g[i][j] = vi < nvec ? gamma[vi * V + j] : 0.f;
-      b[i][j] = vi < nvec ? beta[vi * V + j] : 0.f;
-    }
-  }
+  // gamma / beta are re-read from L1 for every row: keeping them in registers would halve the resident warps
   const float inv_n = 1.f / static_cast<float>(dim), inv_nm1 = 1.f / static_cast<float>(dim - 1);
   for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5); row < rows;
        row += static_cast<int64_t>(gridDim.x) * kLnWarps) {
@@ -74,9 +76,11 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + 32 * i;
       if (vi < nvec) {
-        float o[V];
+        float o[V], gm[V], bt[V];
+        load_params<V>(gamma + vi * V, gm);
+        load_params<V>(beta + vi * V, bt);
 #pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = g[i][j] * ((v[i][j] - mean) * rstd) + b[i][j];
+        for (int j = 0; j < V; ++j) o[j] = gm[j] * ((v[i][j] - mean) * rstd) + bt[j];
         Elem<T>::store_vec(yr + vi * V, o);
       }
     }
@@ -105,24 +109,25 @@ ln_fwd_generic_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
-// dx and the per-block partial sums of dgamma / dbeta in one pass over (dy, x).
+// dx and the per-block partial sums of dgamma / dbeta in one pass over (dy, x). The running column sums live in
+// shared memory (one private strip per warp, laid out [slot][lane] so accesses are conflict-free) rather than in
+// registers: the kernel is latency-bound, and the lower register count doubles the number of resident warps.
 template <typename T, int NV>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, (NV * Elem<T>::kVec <= 32) ? 2 : 1)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
               const T* dx_add, T* dx, float* __restrict__ partial, int64_t rows, int dim) {
   constexpr int V = Elem<T>::kVec;
-  extern __shared__ float sm_acc[];  // [2][dim]
+  constexpr int kSlots = NV * V * 32;   // per-warp accumulator slots per quantity
+  extern __shared__ float sm_acc[];     // [kLnWarps][2][kSlots]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim / V;
-  float g[NV][V], dg[NV][V], db[NV][V];
+  float* acc_g = sm_acc + warp * 2 * kSlots;
+  float* acc_b = acc_g + kSlots;
+  if (partial != nullptr) {
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int vi = lane + 32 * i;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-      g[i][j] = vi < nvec ? gamma[vi * V + j] : 0.f;
-      dg[i][j] = 0.f;
-      db[i][j] = 0.f;
+    for (int s = 0; s < NV * V; ++s) {
+      acc_g[s * 32 + lane] = 0.f;
+      acc_b[s * 32 + lane] = 0.f;
     }
   }
   const float inv_n = 1.f / static_cast<float>(dim), inv_nm1 = 1.f / static_cast<float>(dim - 1);
@@ -163,14 +168,20 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      if (lane + 32 * i < nvec) {
+      const int vi = lane + 32 * i;
+      if (vi < nvec) {
+        float gm[V];
+        load_params<V>(gamma + vi * V, gm);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = (v[i][j] - mean) * rstd;
           v[i][j] = xh;
-          dg[i][j] += u[i][j] * xh;
-          db[i][j] += u[i][j];
-          const float gh = u[i][j] * g[i][j];
+          if (partial != nullptr) {
+            const int slot = (i * V + j) * 32 + lane;
+            acc_g[slot] += u[i][j] * xh;
+            acc_b[slot] += u[i][j];
+          }
+          const float gh = u[i][j] * gm[j];
           u[i][j] = gh;
           s1 += gh;
           s2 += gh * xh;
@@ -200,31 +211,18 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
     }
   }
   if (partial == nullptr) return;
-  // warps fold their register partials into shared memory one after another: fixed order => reproducible
-  for (int w = 0; w < kLnWarps; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) {
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const int c = vi * V + j;
-            if (w == 0) {
-              sm_acc[c] = dg[i][j];
-              sm_acc[dim + c] = db[i][j];
-            } else {
-              sm_acc[c] += dg[i][j];
-              sm_acc[dim + c] += db[i][j];
-            }
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
+  __syncthreads();
+  // fold the warps' strips in warp order (fixed order => reproducible) and scatter slots back to columns
   float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * dim;
-  for (int c = threadIdx.x; c < 2 * dim; c += blockDim.x) out[c] = sm_acc[c];
+  for (int t = threadIdx.x; t < 2 * kSlots; t += blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kLnWarps; ++w) sum += sm_acc[w * 2 * kSlots + t];
+    const int which = t / kSlots, rem = t - which * kSlots;
+    const int ij = rem >> 5, ln = rem & 31;
+    const int vi = ln + 32 * (ij / V);
+    if (vi < nvec) out[which * dim + vi * V + (ij % V)] = sum;
+  }
 }
 
 template <typename T>
@@ -272,20 +270,31 @@ ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
   }
 }
 
-// dgamma[c] = sum over blocks of partial[b][0][c], dbeta likewise; blocks summed in index order.
-__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta, int nblocks, int dim) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * dim) return;
+// dgamma[c] = sum over blocks of partial[b][0][c], dbeta likewise. A block owns 32 columns; its 8 warps each sum a
+// strided subset of the partial rows and the 8 results are added in warp order (fixed order => reproducible).
+__global__ void __launch_bounds__(256)
+ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                       int nblocks, int dim) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * 2 * dim + c];
-  if (c < dim) dgamma[c] = s; else dbeta[c - dim] = s;
+  if (c < 2 * dim)
+    for (int b = warp; b < nblocks; b += 8) s += partial[static_cast<size_t>(b) * 2 * dim + c];
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < 2 * dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    if (c < dim) dgamma[c] = t; else dbeta[c - dim] = t;
+  }
 }
 
 template <typename T>
 int launch_fwd(const T* x, const float* gamma, const float* beta, T* y, int64_t rows, int dim, cudaStream_t st) {
   constexpr int V = Elem<T>::kVec;
-  const bool vec_ok = dim % V == 0 && aligned16(x) && aligned16(y);
+  const bool vec_ok = dim % V == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   const int nv = vec_ok ? static_cast<int>(ceil_div(dim / V, 32)) : 99;
   const int grid = ln_grid(rows);
 #define PTJ_LN_FWD(NV) case NV: ln_fwd_kernel<T, NV><<<grid, kLnThreads, 0, st>>>(x, gamma, beta, y, rows, dim); break;
@@ -306,12 +315,11 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
                float* scratch, int64_t rows, int dim, cudaStream_t st) {
   constexpr int V = Elem<T>::kVec;
   const bool vec_ok = dim % V == 0 && aligned16(x) && aligned16(dy) && (dx == nullptr || aligned16(dx)) &&
-                      (dx_add == nullptr || aligned16(dx_add)) &&
-                      static_cast<size_t>(dim) * 2 * sizeof(float) <= 96 * 1024;
+                      (dx_add == nullptr || aligned16(dx_add)) && aligned16(gamma);
   const int nv = vec_ok ? static_cast<int>(ceil_div(dim / V, 32)) : 99;
   const int grid = ln_bwd_grid(rows);
   float* partial = dgamma != nullptr ? scratch : nullptr;
-  const size_t smem = static_cast<size_t>(dim) * 2 * sizeof(float);
+  const size_t smem = static_cast<size_t>(kLnWarps) * 2 * (nv <= 8 ? nv : 0) * V * 32 * sizeof(float);
 #define PTJ_LN_BWD(NV)                                                                                   \
   case NV:                                                                                               \
     if (smem > 48 * 1024)                                                                                \
@@ -326,7 +334,7 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
 #undef PTJ_LN_BWD
   PTJ_CHECK_LAUNCH();
   if (partial != nullptr) {
-    ln_bwd_finalize_kernel<<<static_cast<int>(ceil_div(2 * dim, 256)), 256, 0, st>>>(partial, dgamma, dbeta, grid, dim);
+    ln_bwd_finalize_kernel<<<static_cast<int>(ceil_div(2 * dim, 32)), 256, 0, st>>>(partial, dgamma, dbeta, grid, dim);
     PTJ_CHECK_LAUNCH();
   }
   return PTJ_OK;
