@@ -1,6 +1,10 @@
 """Per-kernel micro-benchmarks at the GPT-2 small training shapes: achieved TFLOP/s or GB/s next to the measured peaks.
 
-    python pre-tjax_b200/kernel_bench.py [--json out.json] [--tokens 8192] [--only gemm|attention|memory] [--reps N]
+    python pre-tjax_b200/kernel_bench.py [--json out.json] [--tokens 8192] [--only gemm|attention|memory]
+                                         [--case SUBSTRING] [--reps N] [--no-graph]
+
+--case keeps only the cases whose name contains SUBSTRING and --no-graph launches directly instead of replaying a
+CUDA graph: together they give a small, plain process to put under a profiler.
 
 Each case is timed with CUDA events on the launching stream after warm-up, back to back without host
 synchronisation. Memory-bound cases cycle through enough distinct copies of their operands that the bytes touched
@@ -31,12 +35,16 @@ def peaks():
 
 
 REPS = 20
+USE_GRAPH = True
+CASE = None
 
 
-def time_us(fn, reps=None, warm=3):
+def time_us(fn, reps=None, warm=3, name=None):
     """Average device time of fn() in microseconds; fn may take the repetition index (to rotate operands).
     The repetitions are captured into one CUDA graph and replayed, so the host-side cost of a launch (tens of
     microseconds from Python) does not hide kernels that only take a few microseconds."""
+    if CASE is not None and name is not None and CASE not in name:
+        return None
     reps = reps or REPS
     import inspect
     takes_i = len(inspect.signature(fn).parameters) > 0
@@ -44,14 +52,19 @@ def time_us(fn, reps=None, warm=3):
     for i in range(warm):
         call(i)
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if USE_GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                call(i)
+        graph.replay()
+        e0.record()
+        graph.replay()
+    else:
+        e0.record()
         for i in range(reps):
             call(i)
-    graph.replay()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1e3 / reps
@@ -68,9 +81,11 @@ def main():
     T = int(args[args.index("--tokens") + 1]) if "--tokens" in args else 8192
     out_json = args[args.index("--json") + 1] if "--json" in args else None
     only = args[args.index("--only") + 1] if "--only" in args else None
-    global REPS
+    global REPS, USE_GRAPH, CASE
     if "--reps" in args:
         REPS = int(args[args.index("--reps") + 1])
+    USE_GRAPH = "--no-graph" not in args
+    CASE = args[args.index("--case") + 1] if "--case" in args else None
     want = lambda section: only is None or only == section
     ptj = importlib.import_module("pre-tjax_b200")
     ops, lib = ptj.operators, ptj._lib
@@ -83,6 +98,8 @@ def main():
     rows = []
 
     def add(name, us, flops=None, nbytes=None):
+        if us is None:
+            return
         r = {"kernel": name, "us": round(us, 2)}
         if flops is not None:
             r.update(tflops=round(flops / us / 1e6, 1), frac=round(flops / us / 1e6 / peak_tf, 3), bound="tensor")
@@ -121,7 +138,7 @@ def main():
             ("gemm wgrad lm-head  dlogits^T x [50257,768]", lambda: step._head_wgrad(logits, x_d, g_emb), 2 * T * V * D),
         ]
         for name, fn, fl in cases:
-            add(name, time_us(fn), flops=fl)
+            add(name, time_us(fn, name=name), flops=fl)
         del logits, w_emb, g_emb
 
     # ---- attention (causal, dropout 0.1 on the probabilities) ----
