@@ -35,7 +35,8 @@ typedef enum {
   PTJ_ERR_WORKSPACE = -5,   /* the scratch buffer passed in is too small or NULL                       */
   PTJ_ERR_UNSUPPORTED = -6, /* combination of options not implemented                                  */
   PTJ_ERR_DEVICE = -7,      /* current device is not an sm_100 part / driver entry point missing       */
-  PTJ_ERR_TIMEOUT = -8      /* a bounded wait inside a kernel ran out (reported via ptj_last_kernel_fault) */
+  PTJ_ERR_TIMEOUT = -8,     /* a bounded wait inside a kernel ran out (reported via ptj_last_kernel_fault) */
+  PTJ_ERR_TOO_LARGE = -9    /* a size exceeds the fixed capacity of a no-allocation entry point            */
 } ptj_status;
 
 enum { PTJ_F32 = 0, PTJ_BF16 = 1 };
@@ -66,6 +67,23 @@ size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim);
 int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
                       float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
                       int64_t dim, int dtype, void* stream);
+
+/* LayerNorm backward that needs no scratch buffer from the caller. It has no counterpart in the reference: it
+ * exists for callers that cannot allocate device memory themselves, e.g. code running inside a process whose GPU
+ * memory was handed out up front to another allocator (cudaMalloc would fail, fragment that pool or stall the
+ * device) or a step that must stay off the driver's allocation path. Same arguments and results (bit for bit) as
+ * ptj_layernorm_bwd minus scratch / scratch_floats; the partial column sums go to a fixed 4.6 MiB array inside the
+ * library that every GPU loading the library holds until the process exits.
+ *   - dim <= ptj_layernorm_bwd_noalloc_max_dim() (2048); larger sizes return PTJ_ERR_TOO_LARGE.
+ *   - The first call on a device looks up the array's device address (a driver query, done once per device with
+ *     that device current); make that first call before any stream capture.
+ *   - It calls no cudaMalloc / cudaFree or other allocating routine.
+ *   - All calls on a device share the one array, which keeps the last call's contents (nothing in it has to start
+ *     at zero: every call overwrites what it reads). Two calls that overlap on the GPU (different streams) race;
+ *     order them on one stream or with events. */
+size_t ptj_layernorm_bwd_noalloc_max_dim(void);
+int ptj_layernorm_bwd_noalloc(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                              float* dgamma, float* dbeta, int64_t rows, int64_t dim, int dtype, void* stream);
 
 /* ---- GELU (tanh form) ------------------------------------------------------------------------------- */
 /* Replaces t_gelu_fwd_t (model_triton.py:254-260) and t_gelu_bkwd2_t (:296-304). */

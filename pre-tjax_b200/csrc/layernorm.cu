@@ -2,6 +2,8 @@
 // epsilon (model_torch_func.py:104-108). Backward formula: model_triton.py:1773-1783 (dx) and :1652-1660 (dgamma,
 // dbeta). HBM-bound: one warp owns one row, the row lives in registers between the statistics and the output pass,
 // all global accesses are 16-byte vectors.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ptj {
@@ -389,4 +391,55 @@ extern "C" int ptj_layernorm_bwd(const void* dy, const void* x, const float* gam
                       static_cast<const __nv_bfloat16*>(dx_add), static_cast<__nv_bfloat16*>(dx), dgamma, dbeta, scratch,
                       rows, (int)dim, st);
   return PTJ_ERR_DTYPE;
+}
+
+// ---- LayerNorm backward for callers that must not allocate ------------------------------------------------------
+// The partial column sums of ptj_layernorm_bwd normally live in a scratch buffer the caller allocates. Some callers
+// cannot do that: code that runs inside a process whose device memory was handed out up front to another allocator
+// (a framework-owned pool sized to the whole GPU, where cudaMalloc would fail, fragment the pool or stall the device),
+// or a step that must stay off the driver's allocation path for latency reasons. For them the scratch is this
+// fixed array in the library's own image: 148 * 2 thread blocks x (dgamma, dbeta) x kStaticMaxDim floats = 4.6 MiB,
+// held by every GPU that loads the library until the process exits.
+constexpr int kStaticMaxDim = 2048;
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(kNumSMs) * 2 * 2 * kStaticMaxDim;
+static __device__ __align__(256) float g_ln_bwd_static_scratch[kStaticScratchFloats];
+
+namespace ptj {
+namespace {
+// The array's name is only a host-side handle; kernels need its DEVICE address, which differs per GPU. It is looked
+// up once per device, with that device current, and cached.
+float* static_scratch_for_current_device() {
+  constexpr int kMaxDev = 64;
+  static float* cache[kMaxDev] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_ln_bwd_static_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cache[dev] = ptr;
+  }
+  return cache[dev];
+}
+}  // namespace
+}  // namespace ptj
+
+extern "C" size_t ptj_layernorm_bwd_noalloc_max_dim(void) { return kStaticMaxDim; }
+
+extern "C" int ptj_layernorm_bwd_noalloc(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                                         float* dgamma, float* dbeta, int64_t rows, int64_t dim, int dtype,
+                                         void* stream) {
+  if (rows < 0 || dim < 1) return PTJ_ERR_BAD_SHAPE;
+  if (dim > kStaticMaxDim || ptj_layernorm_bwd_scratch_floats(rows, dim) > kStaticScratchFloats) return PTJ_ERR_TOO_LARGE;
+  float* scratch = static_scratch_for_current_device();  // first call on a device resolves the address
+  if (scratch == nullptr) return PTJ_ERR_DEVICE;
+  return ptj_layernorm_bwd(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, kStaticScratchFloats, rows, dim, dtype,
+                           stream);
 }

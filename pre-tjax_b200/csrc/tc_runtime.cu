@@ -86,6 +86,7 @@ extern "C" const char* ptj_status_string(int status) {
     case PTJ_ERR_UNSUPPORTED: return "unsupported combination of options";
     case PTJ_ERR_DEVICE: return "device is not sm_100 or a driver entry point is missing";
     case PTJ_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case PTJ_ERR_TOO_LARGE: return "size exceeds the fixed capacity of the no-allocation entry point";
     default: return "unknown status";
   }
 }
