@@ -85,6 +85,13 @@ __device__ __forceinline__ void tmem_ld_row32(uint32_t taddr, float (&f)[32]) {
   for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
 }
 
+// 2^x on the special-function unit (inputs here are <= 0 or small; subnormal results flush to zero)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // descriptors of the five operand flavours used below (all tiles are 128-byte swizzled, 8-line groups 1024 B apart)
 __device__ __forceinline__ uint64_t desc_kmajor_d(uint32_t tile, int k16) {  // [rows][64 d], K = d
   return smem_desc_sw128(tile + k16 * 32, 16, 1024);
@@ -186,35 +193,47 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     float alpha = 1.f, rowsum = 0.f;
     dead = __any_sync(0xffffffffu, dead);  // warp-uniform from here on: tcgen05.ld needs the whole warp
     if (!dead) {
-      // pass 1: row maximum of the scaled, causally masked scores (log2 domain)
-      float mx = m2;
+      // pass 1: row maximum of the raw scores (the causal mask only matters on the diagonal tile), then scaled
+      float mraw = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float s[32];
         tmem_ld_row32(t_s + c * 32, s);
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = s[i] * p.scale_log2;
-          mx = fmaxf(mx, (diag && c * 32 + i > tid) ? -INFINITY : v);
+          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, c * 32 + i > tid ? -INFINITY : s[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, s[i]);
         }
       }
-      alpha = exp2f(m2 - mx);
+      const float mx = fmaxf(m2, mraw * p.scale_log2);
+      alpha = ex2_approx(m2 - mx);
       m2 = mx;
       // pass 2: probabilities, row sum, dropout, bf16 tile for the second MMA
+      const bool masked = p.dr.train && p.dr.thr16 != 0u;
+      const float f_eval = p.dr.train ? 1.f : p.dr.eval_scale;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float s[32];
         tmem_ld_row32(t_s + c * 32, s);
         uint32_t keep = 0xffffffffu;
-        if (p.dr.train && p.dr.thr16 != 0u)
+        if (masked)
           keep = keep_bits32(p.dr, (static_cast<uint64_t>(bh) * p.S + q_row) * p.S + static_cast<uint64_t>(j) * T + c * 32);
-        const float f_eval = p.dr.train ? 1.f : p.dr.eval_scale;
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(s[i] * p.scale_log2 - m2);
-          if (diag && c * 32 + i > tid) e = 0.f;
-          rowsum += e;
-          s[i] = ((keep >> i) & 1u) ? e * f_eval : 0.f;
+          for (int i = 0; i < 32; ++i) {
+            const float e = c * 32 + i > tid ? 0.f : ex2_approx(fmaf(s[i], p.scale_log2, -m2));
+            rowsum += e;
+            s[i] = ((keep >> i) & 1u) ? e * f_eval : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float e = ex2_approx(fmaf(s[i], p.scale_log2, -m2));
+            rowsum += e;
+            s[i] = ((keep >> i) & 1u) ? e * f_eval : 0.f;
+          }
         }
         store_row32_sw128(p_s, tid, c * 32, s);
       }
@@ -289,12 +308,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // ---------------------------------------------------------------------------------------------------------------------
 // backward. MODE 0: block owns a KV tile, loops over query tiles >= it, produces dK and dV.
 //           MODE 1: block owns a query tile, loops over KV tiles <= it, produces dQ.
+// Tensor memory (256 columns, so two blocks share an SM): [0,128) holds S and is then overwritten by dP (every
+// thread keeps its row of probabilities in registers as packed bf16), [128,192) and [192,256) are the accumulators.
+// Shared memory (96 KB): Q, K, V, dO tiles and ONE 32 KB buffer that first carries Pd (for dV) and then dS.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kBwdSmem = 4 * kTileBytes + 4 * kTileBytes + 1024 + 128;  // Q, K, V, dO, Pd(2), dS(2)
-constexpr int kBwdTmemCols = 512;                                        // S 128, dP 128, acc0 64, acc1 64
+constexpr int kBwdSmem = 4 * kTileBytes + 2 * kTileBytes + 1024 + 128;
+constexpr int kBwdTmemCols = 256;
 
 template <int MODE>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, 2)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
                    const RowView d_o, const RowView o_view, const float* __restrict__ row_max,
@@ -305,22 +327,23 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* k_s = sm + kTileBytes;
   uint8_t* v_s = sm + 2 * kTileBytes;
   uint8_t* g_s = sm + 3 * kTileBytes;
-  uint8_t* p_s = sm + 4 * kTileBytes;   // Pd  (MODE 0 only)
-  uint8_t* ds_s = sm + 6 * kTileBytes;  // dS
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 8 * kTileBytes);
-  uint64_t *bar_fix = bars, *bar_mov = bars + 1, *bar_sp = bars + 2, *bar_acc = bars + 3;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint8_t* w_s = sm + 4 * kTileBytes;  // Pd, then dS (two [128][64] sub-tiles)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 6 * kTileBytes);
+  // bar_fix: resident tiles; bar_m0 / bar_m1: the two moving tiles; bar_s: S ready; bar_p: dP ready (and, MODE 0, the
+  // dV MMA has consumed Pd); bar_acc: last accumulation MMA of the iteration done
+  uint64_t *bar_fix = bars, *bar_m0 = bars + 1, *bar_m1 = bars + 2, *bar_s = bars + 3, *bar_p = bars + 4, *bar_acc = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  // MODE 0: light (late) KV tiles last; MODE 1: heavy (late) query tiles first
+  // MODE 0: heavy KV tiles (early ones, many query tiles) first; MODE 1: heavy (late) query tiles first
   const int own = MODE == 0 ? static_cast<int>(blockIdx.x) / p.BH : p.nq - 1 - static_cast<int>(blockIdx.x) / p.BH;
   const int bh = static_cast<int>(blockIdx.x) % p.BH;
   const int b = bh / p.H, h = bh % p.H;
   const AbortCtx ctx{abort_flag, p.fault};
 
   if (tid == 0) {
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -334,13 +357,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-  constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);      // Q K^T and dO V^T
-  constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);       // Pd^T dO, dS^T Q
-  constexpr uint32_t idesc_q = idesc_bf16_f32(T, DH, false, true);      // dS K
+  constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);   // Q K^T and dO V^T
+  constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);    // Pd^T dO, dS^T Q
+  constexpr uint32_t idesc_q = idesc_bf16_f32(T, DH, false, true);   // dS K
 
-  // the tile this block owns stays resident: MODE 0: K_j, V_j ; MODE 1: Q_i, dO_i
   const int lo = MODE == 0 ? own : 0;
   const int hi = MODE == 0 ? p.nq : own + 1;
+  // moving tile 0 feeds the S MMA and stays busy until the end of the iteration (MODE 0: Q, MODE 1: K);
+  // moving tile 1 is only needed until dP (MODE 0: dO, also read by the dV MMA; MODE 1: V)
+  uint8_t* m0_s = MODE == 0 ? q_s : k_s;
+  uint8_t* m1_s = MODE == 0 ? g_s : v_s;
+  const CUtensorMap* m0_map = MODE == 0 ? &tm_q : &tm_k;
+  const CUtensorMap* m1_map = MODE == 0 ? &tm_g : &tm_v;
   bool dead = false;
   if (tid == 0) {
     mbar_expect_tx(bar_fix, 2 * kTileBytes);
@@ -351,24 +379,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tma_load_4d(q_s, &tm_q, bar_fix, 0, own * T, h, b);
       tma_load_4d(g_s, &tm_g, bar_fix, 0, own * T, h, b);
     }
-    mbar_expect_tx(bar_mov, 2 * kTileBytes);
-    if (MODE == 0) {
-      tma_load_4d(q_s, &tm_q, bar_mov, 0, lo * T, h, b);
-      tma_load_4d(g_s, &tm_g, bar_mov, 0, lo * T, h, b);
-    } else {
-      tma_load_4d(k_s, &tm_k, bar_mov, 0, lo * T, h, b);
-      tma_load_4d(v_s, &tm_v, bar_mov, 0, lo * T, h, b);
-    }
+    mbar_expect_tx(bar_m0, kTileBytes);
+    tma_load_4d(m0_s, m0_map, bar_m0, 0, lo * T, h, b);
+    mbar_expect_tx(bar_m1, kTileBytes);
+    tma_load_4d(m1_s, m1_map, bar_m1, 0, lo * T, h, b);
     dead = !mbar_wait(bar_fix, 0, ctx, 0x2001u);
   }
 
-  // per-row constants of the query row this thread owns (MODE 1: fixed; MODE 0: reloaded per query tile)
-  float m_nat = 0.f, inv_l = 0.f, delta = 0.f;
+  // per-row constants of a query row: log2-domain row maximum, 1 / row sum, delta = sum_d dO[q,d] O[q,d]
+  struct RowConsts { float m2, inv_l, delta; };
   auto load_row_consts = [&](int q_tile) {
     const int64_t qr = static_cast<int64_t>(q_tile) * T + tid;
     const int64_t ri = static_cast<int64_t>(bh) * p.S + qr;
-    m_nat = row_max[ri] * kLog2e;  // back to the log2 domain
-    inv_l = 1.f / row_sum[ri];
+    RowConsts rc;
+    rc.m2 = row_max[ri] * kLog2e;
+    rc.inv_l = 1.f / row_sum[ri];
     const __nv_bfloat16* go = d_o.row(b, h, qr);
     const __nv_bfloat16* oo = o_view.row(b, h, qr);
     float acc = 0.f;
@@ -380,108 +405,159 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc = fmaf(x[i], y[i], acc);
     }
-    delta = acc;  // sum_d dO[q,d] O[q,d]
+    rc.delta = acc;
+    return rc;
   };
-  if (MODE == 1) load_row_consts(own);
+  RowConsts rc = load_row_consts(MODE == 0 ? lo : own);
 
   int it = 0;
   for (int t = lo; t < hi; ++t, ++it) {
     const uint32_t ph = it & 1;
     const int qt = MODE == 0 ? t : own;
     const int kt = MODE == 0 ? own : t;
-    if (MODE == 0) load_row_consts(qt);
+    const bool diag = qt == kt;
+    const int64_t q_row = static_cast<int64_t>(qt) * T + tid;
+    const uint64_t idx_row = (static_cast<uint64_t>(bh) * p.S + q_row) * p.S + static_cast<uint64_t>(kt) * T;
+    const bool masked = p.dr.train && p.dr.thr16 != 0u;
+    const float f_keep = p.dr.train ? 1.f : p.dr.eval_scale;
+
+    // ---- S = Q K^T ----
     if (tid == 0 && !dead) {
-      dead = !mbar_wait(bar_mov, ph, ctx, 0x2002u);
+      dead = !mbar_wait(bar_m0, ph, ctx, 0x2002u);
       if (!dead) {
         tc_fence_after_sync();
 #pragma unroll
         for (int k16 = 0; k16 < DH / 16; ++k16)
           mma_bf16_ss(tmem, desc_kmajor_d(smem_u32(q_s), k16), desc_kmajor_d(smem_u32(k_s), k16), idesc_s, k16 > 0);
-#pragma unroll
-        for (int k16 = 0; k16 < DH / 16; ++k16)
-          mma_bf16_ss(tmem + 128, desc_kmajor_d(smem_u32(g_s), k16), desc_kmajor_d(smem_u32(v_s), k16), idesc_s, k16 > 0);
-        mma_commit(bar_sp);
+        mma_commit(bar_s);
       }
     }
-    if (!dead) dead = !mbar_wait(bar_sp, ph, ctx, 0x2003u);
+    if (!dead) dead = !mbar_wait(bar_s, ph, ctx, 0x2003u);
     tc_fence_after_sync();
     dead = __any_sync(0xffffffffu, dead);
+
+    // probabilities of this thread's row, kept in registers as packed bf16 pairs, and the dropout keep bits
+    uint32_t pk[T / 2];
+    uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
     if (!dead) {
-      const bool diag = qt == kt;
-      const int64_t q_row = static_cast<int64_t>(qt) * T + tid;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        float s[32], dp[32];
+        float s[32];
         tmem_ld_row32(tmem + lane_base + c * 32, s);
-        tmem_ld_row32(tmem + lane_base + 128 + c * 32, dp);
-        uint32_t keep = 0xffffffffu;
-        if (p.dr.train && p.dr.thr16 != 0u)
-          keep = keep_bits32(p.dr, (static_cast<uint64_t>(bh) * p.S + q_row) * p.S + static_cast<uint64_t>(kt) * T + c * 32);
-        const float f_eval = p.dr.train ? 1.f : p.dr.eval_scale;
+        if (masked) keep[c] = keep_bits32(p.dr, idx_row + c * 32);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float pr = exp2f(s[i] * p.scale_log2 - m_nat) * inv_l;
+          float pr = ex2_approx(fmaf(s[i], p.scale_log2, -rc.m2)) * rc.inv_l;
           if (diag && c * 32 + i > tid) pr = 0.f;
-          const float f = ((keep >> i) & 1u) ? f_eval : 0.f;
-          s[i] = pr * f;                                    // dropped-out probability (for dV)
-          dp[i] = pr * (dp[i] * f - delta) * p.scale;       // gradient w.r.t. the raw score q.k
+          s[i] = pr;
         }
-        if (MODE == 0) store_row32_sw128(p_s, tid, c * 32, s);
-        store_row32_sw128(ds_s, tid, c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(s[2 * i], s[2 * i + 1]);
+          pk[c * 16 + i] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        if (MODE == 0) {  // Pd = P * keep (* (1-p) in evaluation) for dV += Pd^T dO
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = ((keep[c] >> i) & 1u) ? s[i] * f_keep : 0.f;
+          store_row32_sw128(w_s, tid, c * 32, s);
+        }
       }
     }
+    if (MODE == 0) fence_proxy_async_smem();
+    tc_fence_before_sync();
+    if (__syncthreads_or(dead ? 1 : 0)) { dead = true; break; }  // S consumed by every thread, Pd complete
+
+    // ---- dP = dO V^T into the columns S occupied (MODE 0: preceded by dV += Pd^T dO) ----
+    if (tid == 0) {
+      tc_fence_after_sync();
+      dead = !mbar_wait(bar_m1, ph, ctx, 0x2004u);
+      if (!dead) {
+        tc_fence_after_sync();
+        if (MODE == 0) {
+#pragma unroll
+          for (int k16 = 0; k16 < T / 16; ++k16)
+            mma_bf16_ss(tmem + 128, desc_p_transposed(smem_u32(w_s), k16), desc_rows_as_k(smem_u32(g_s), k16), idesc_t,
+                        (it > 0 || k16 > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k16 = 0; k16 < DH / 16; ++k16)
+          mma_bf16_ss(tmem, desc_kmajor_d(smem_u32(g_s), k16), desc_kmajor_d(smem_u32(v_s), k16), idesc_s, k16 > 0);
+        mma_commit(bar_p);
+      }
+    }
+    if (!dead) dead = !mbar_wait(bar_p, ph, ctx, 0x2005u);
+    tc_fence_after_sync();
+    if (tid == 0 && !dead && t + 1 < hi) {  // moving tile 1 is free: fetch the next one while dS is being formed
+      mbar_expect_tx(bar_m1, kTileBytes);
+      tma_load_4d(m1_s, m1_map, bar_m1, 0, (t + 1) * T, h, b);
+    }
+    // the buffer that receives dS was last read by the previous iteration's accumulation MMA (MODE 1) or by this
+    // iteration's dV MMA (MODE 0, covered by bar_p)
+    if (MODE == 1 && it > 0 && !dead) dead = !mbar_wait(bar_acc, ph ^ 1u, ctx, 0x2006u);
+    dead = __any_sync(0xffffffffu, dead);
+    if (!dead) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float dp[32];
+        tmem_ld_row32(tmem + lane_base + c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const uint32_t w = pk[c * 16 + (i >> 1)];
+          const float pr = __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+          const float f = ((keep[c] >> i) & 1u) ? f_keep : 0.f;
+          dp[i] = pr * (dp[i] * f - rc.delta) * p.scale;  // gradient w.r.t. the raw score q.k
+        }
+        store_row32_sw128(w_s, tid, c * 32, dp);
+      }
+    }
+    // constants of the next query row (MODE 0): issue the loads now, they are consumed after the barrier
+    RowConsts rc_next = rc;
+    if (MODE == 0 && t + 1 < hi) rc_next = load_row_consts(t + 1);
     fence_proxy_async_smem();
     tc_fence_before_sync();
-    if (__syncthreads_or(dead ? 1 : 0)) { dead = true; break; }
+    if (__syncthreads_or(dead ? 1 : 0)) { dead = true; break; }  // dP consumed, dS complete
+
+    // ---- accumulate: MODE 0 dK += dS^T Q ; MODE 1 dQ += dS K ----
     if (tid == 0) {
       tc_fence_after_sync();
       if (MODE == 0) {
 #pragma unroll
-        for (int k16 = 0; k16 < T / 16; ++k16)  // dV[kv, d] += Pd^T[kv, q] dO[q, d]
-          mma_bf16_ss(tmem + 256, desc_p_transposed(smem_u32(p_s), k16), desc_rows_as_k(smem_u32(g_s), k16), idesc_t,
-                      (it > 0 || k16 > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k16 = 0; k16 < T / 16; ++k16)  // dK[kv, d] += dS^T[kv, q] Q[q, d]
-          mma_bf16_ss(tmem + 320, desc_p_transposed(smem_u32(ds_s), k16), desc_rows_as_k(smem_u32(q_s), k16), idesc_t,
+        for (int k16 = 0; k16 < T / 16; ++k16)
+          mma_bf16_ss(tmem + 192, desc_p_transposed(smem_u32(w_s), k16), desc_rows_as_k(smem_u32(q_s), k16), idesc_t,
                       (it > 0 || k16 > 0) ? 1u : 0u);
       } else {
 #pragma unroll
-        for (int k16 = 0; k16 < T / 16; ++k16)  // dQ[q, d] += dS[q, kv] K[kv, d]
-          mma_bf16_ss(tmem + 256, desc_p_kmajor(smem_u32(ds_s), k16), desc_rows_as_k(smem_u32(k_s), k16), idesc_q,
+        for (int k16 = 0; k16 < T / 16; ++k16)
+          mma_bf16_ss(tmem + 128, desc_p_kmajor(smem_u32(w_s), k16), desc_rows_as_k(smem_u32(k_s), k16), idesc_q,
                       (it > 0 || k16 > 0) ? 1u : 0u);
       }
       mma_commit(bar_acc);
-      // the moving tiles and the Pd/dS tiles are reusable once these MMAs are done
-      dead = !mbar_wait(bar_acc, ph, ctx, 0x2004u);
-      if (!dead && t + 1 < hi) {
-        mbar_expect_tx(bar_mov, 2 * kTileBytes);
-        if (MODE == 0) {
-          tma_load_4d(q_s, &tm_q, bar_mov, 0, (t + 1) * T, h, b);
-          tma_load_4d(g_s, &tm_g, bar_mov, 0, (t + 1) * T, h, b);
-        } else {
-          tma_load_4d(k_s, &tm_k, bar_mov, 0, (t + 1) * T, h, b);
-          tma_load_4d(v_s, &tm_v, bar_mov, 0, (t + 1) * T, h, b);
+      if (t + 1 < hi) {  // moving tile 0 is reusable once this MMA has read it
+        dead = !mbar_wait(bar_acc, ph, ctx, 0x2007u);
+        if (!dead) {
+          mbar_expect_tx(bar_m0, kTileBytes);
+          tma_load_4d(m0_s, m0_map, bar_m0, 0, (t + 1) * T, h, b);
         }
       }
     }
-    // every thread waits for the accumulation MMAs too: they read the Pd/dS tiles the next iteration overwrites
-    if (tid != 0 && !dead) dead = !mbar_wait(bar_acc, ph, ctx, 0x2005u);
-    tc_fence_after_sync();
-    dead = __any_sync(0xffffffffu, dead);
+    // MODE 0 overwrites the Pd/dS buffer early in the next iteration: every thread waits for the MMA that reads it
+    if (MODE == 0 && tid != 0 && !dead && t + 1 < hi) dead = !mbar_wait(bar_acc, ph, ctx, 0x2008u);
+    rc = rc_next;
   }
 
+  if (!dead) dead = !mbar_wait(bar_acc, (it - 1) & 1, ctx, 0x2009u);  // the last accumulation MMA
   if (!__syncthreads_or(dead ? 1 : 0)) {
     tc_fence_after_sync();
     const int64_t r = static_cast<int64_t>(own) * T + tid;
 #pragma unroll
     for (int which = 0; which < (MODE == 0 ? 2 : 1); ++which) {
-      // MODE 0: which 0 = dV (acc0 -> out1), which 1 = dK (acc1 -> out0); MODE 1: dQ (acc0 -> out0)
+      // MODE 0: which 0 = dV (columns 128.. -> out1), which 1 = dK (columns 192.. -> out0); MODE 1: dQ -> out0
       const RowView& dst_view = (MODE == 0 && which == 0) ? out1 : out0;
       __nv_bfloat16* dst = dst_view.row(b, h, r);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float v[32];
-        tmem_ld_row32(tmem + lane_base + 256 + which * 64 + c * 32, v);
+        tmem_ld_row32(tmem + lane_base + 128 + which * 64 + c * 32, v);
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {
           float t8[8];
