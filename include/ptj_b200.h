@@ -13,8 +13,9 @@
  *
  * Dropout everywhere follows the reference semantics (model_torch_func.py:98-102): in training the value is
  * multiplied by a 0/1 mask with keep probability 1-p and is NOT rescaled; in evaluation it is multiplied by 1-p.
- * Masks come from Philox4x32-10 keyed by `seed`, counter = (element index / 4, stream id), so forward and
- * backward regenerate identical masks from (seed, stream id) without storing them.
+ * Masks come from Philox4x32-10 keyed by `seed`, counter = (element index / 8, stream id): each call serves eight
+ * consecutive elements with 16 bits each and an element is dropped when its 16 bits are below floor(p * 65536).
+ * Forward and backward regenerate identical masks from (seed, stream id, element index) without storing them.
  */
 #ifndef PTJ_B200_H_
 #define PTJ_B200_H_

@@ -1,8 +1,8 @@
 """Host restatement of the counter-based dropout masks.  TEST INFRASTRUCTURE ONLY.
 
 Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11) keyed by a 64-bit
-seed; the counter is (element index // 4, stream id, constant) and the four output words serve four consecutive
-elements. An element is kept when its word is >= floor(p * 2^32). The reference has no counterpart (its masks come
+seed; the counter is (element index // 8, stream id, constant) and the four output words serve eight consecutive
+elements with 16 bits each. An element is kept when its 16 bits are >= floor(p * 65536). The reference has no counterpart (its masks come
 from triton.language.rand / torch.bernoulli), so these masks are pinned only to the Philox known-answer vectors
 checked in tests/test_oracle_golden.py, not to the reference.
 """
@@ -33,29 +33,14 @@ def philox4x32_10(counter, key):
     return [x.astype(np.uint32) for x in c]
 
 
-def threshold(p: float) -> int:
-    t = float(np.float32(p)) * 4294967296.0
-    if t <= 0:
-        return 0
-    if t >= 4294967295.0:
-        return 0xFFFFFFFF
-    return int(t)
+def threshold16(p: float) -> int:
+    return min(65535, max(0, int(float(np.float32(p)) * 65536.0)))
 
 
 def keep_mask(seed: int, stream_id: int, n: int, p: float) -> np.ndarray:
-    """float32 0/1 mask for element indices 0..n-1."""
-    nblk = (n + 3) // 4
-    ctr = np.arange(nblk, dtype=np.uint64)
-    words = philox4x32_10([ctr & U32, ctr >> np.uint64(32), np.full(nblk, stream_id, np.uint64),
-                           np.full(nblk, CTR3, np.uint64)], [seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF])
-    flat = np.stack(words, axis=1).reshape(-1)[:n]
-    return (flat >= np.uint32(threshold(p))).astype(np.float32)
-
-
-def keep_mask16(seed: int, stream_id: int, n: int, p: float) -> np.ndarray:
-    """Mask stream of the attention-probability site: 16 random bits per element, 8 elements per Philox call
-    (element e of a call takes the low half of word e // 2 when e is even, the high half when odd); dropped when
-    below floor(p * 65536)."""
+    """float32 0/1 mask for element indices 0..n-1 of one site: 16 random bits per element, 8 elements per Philox call
+    (element e of a call takes the low half of word e // 2 when e is even, the high half when odd); an element is
+    dropped when its 16 bits are below floor(p * 65536)."""
     nblk = (n + 7) // 8
     ctr = np.arange(nblk, dtype=np.uint64)
     words = philox4x32_10([ctr & U32, ctr >> np.uint64(32), np.full(nblk, stream_id, np.uint64),
@@ -64,5 +49,4 @@ def keep_mask16(seed: int, stream_id: int, n: int, p: float) -> np.ndarray:
     for w in words:
         halves += [w & np.uint32(0xFFFF), w >> np.uint32(16)]
     flat = np.stack(halves, axis=1).reshape(-1)[:n]
-    t = min(65535, max(0, int(float(np.float32(p)) * 65536.0)))
-    return (flat >= np.uint32(t)).astype(np.float32)
+    return (flat >= np.uint32(threshold16(p))).astype(np.float32)

@@ -13,7 +13,7 @@ bool shape_ok(const ptj_attn_shape* s) {
 }
 AttnDropout make_dropout(float p, int train, uint64_t seed, uint32_t stream_id) {
   AttnDropout d;
-  d.thr16 = attn_dropout_threshold16(p);
+  d.thr16 = dropout_threshold16(p);
   d.eval_scale = 1.f - p;
   d.train = train;
   d.seed = seed;

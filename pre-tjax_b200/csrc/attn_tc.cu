@@ -48,15 +48,7 @@ struct AttnParams {
 __device__ __forceinline__ uint32_t keep_bits32(const AttnDropout& dr, uint64_t idx0) {
   uint32_t bits = 0;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const Philox4 r = philox4x32_10(dr.seed, (idx0 >> 3) + c, dr.stream_id);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      bits |= ((w[e] & 0xffffu) >= dr.thr16 ? 1u : 0u) << (c * 8 + 2 * e);
-      bits |= ((w[e] >> 16) >= dr.thr16 ? 1u : 0u) << (c * 8 + 2 * e + 1);
-    }
-  }
+  for (int c = 0; c < 4; ++c) bits |= dropout_keep_bits8(dr.seed, dr.stream_id, (idx0 >> 3) + c, dr.thr16) << (c * 8);
   return bits;
 }
 

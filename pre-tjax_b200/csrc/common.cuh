@@ -122,20 +122,33 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint64_t seed, uint64_
   }
   return Philox4{c0, c1, c2, c3};
 }
-// An element is DROPPED when its 32-bit random word is below p * 2^32.
-__host__ __device__ __forceinline__ uint32_t dropout_threshold(float p) {
-  double t = static_cast<double>(p) * 4294967296.0;
+// ---- the dropout mask stream (one definition for every site) ---------------------------------------------------
+// Element idx of a site's index space takes 16 random bits: Philox call number idx / 8 (counter low/high words),
+// keyed by the site's seed and stream id, yields four 32-bit words = eight 16-bit lanes; element e = idx % 8 uses the
+// low half of word e / 2 when e is even and the high half when odd. The element is DROPPED when its lane is below
+// floor(p * 65536). Forward and backward regenerate the same bits; nothing is stored.
+__host__ __device__ __forceinline__ uint32_t dropout_threshold16(float p) {
+  double t = static_cast<double>(p) * 65536.0;
   if (t <= 0.0) return 0u;
-  if (t >= 4294967295.0) return 0xffffffffu;
+  if (t >= 65535.0) return 65535u;
   return static_cast<uint32_t>(t);
 }
-// Keep flag of element `idx` (any idx, not only multiples of 4).
-__host__ __device__ __forceinline__ bool dropout_keep(uint64_t seed, uint32_t stream_id, uint64_t idx,
-                                                       uint32_t thr) {
-  const Philox4 r = philox4x32_10(seed, idx >> 2, stream_id);
-  const uint32_t lane = static_cast<uint32_t>(idx & 3);
-  const uint32_t w = lane == 0 ? r.x : lane == 1 ? r.y : lane == 2 ? r.z : r.w;
-  return w >= thr;
+// keep flags (bit e = element 8*call + e) of one Philox call
+__host__ __device__ __forceinline__ uint32_t dropout_keep_bits8(uint64_t seed, uint32_t stream_id, uint64_t call,
+                                                                uint32_t thr16) {
+  const Philox4 r = philox4x32_10(seed, call, stream_id);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  uint32_t bits = 0;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    bits |= ((w[e] & 0xffffu) >= thr16 ? 1u : 0u) << (2 * e);
+    bits |= ((w[e] >> 16) >= thr16 ? 1u : 0u) << (2 * e + 1);
+  }
+  return bits;
+}
+// keep flag of a single element (any idx)
+__host__ __device__ __forceinline__ bool dropout_keep(uint64_t seed, uint32_t stream_id, uint64_t idx, uint32_t thr16) {
+  return (dropout_keep_bits8(seed, stream_id, idx >> 3, thr16) >> (idx & 7)) & 1u;
 }
 
 // ---- tanh-GELU (model_torch_func.py:60-62) -------------------------------------------------------------------
@@ -150,20 +163,22 @@ __device__ __forceinline__ float tanh_sel(float x) {
   }
   return tanhf(x);
 }
+// gelu(x) = 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3) = x (k + k c x^2)
 template <bool FAST = false>
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float k = 0.7978845608028654f;  // sqrt(2/pi)
-  const float t = tanh_sel<FAST>(k * (x + 0.044715f * x * x * x));
-  return 0.5f * x * (1.f + t);
+  const float k = 0.7978845608028654f, kc = 0.7978845608028654f * 0.044715f;
+  const float t = tanh_sel<FAST>(x * fmaf(x * x, kc, k));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
 }
-// d gelu / dx (model_triton.py:262-267)
+// d gelu / dx = 0.5 (1 + t) + 0.5 x (1 - t^2) (k + 3 k c x^2)   (model_triton.py:262-267)
 template <bool FAST = false>
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
-  const float k = 0.7978845608028654f;
+  const float k = 0.7978845608028654f, kc = 0.7978845608028654f * 0.044715f;
   const float x2 = x * x;
-  const float t = tanh_sel<FAST>(k * (x + 0.044715f * x * x2));
-  const float dt = (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x2);
-  return 0.5f * (1.f + t) + 0.5f * x * dt;
+  const float t = tanh_sel<FAST>(x * fmaf(x2, kc, k));
+  const float dt = fmaf(-t, t, 1.f) * fmaf(x2, 3.f * kc, k);
+  return fmaf(0.5f * x, dt, fmaf(0.5f, t, 0.5f));
 }
 
 }  // namespace ptj

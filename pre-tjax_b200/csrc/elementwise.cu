@@ -50,21 +50,16 @@ dropout_kernel(const T* __restrict__ x, const T* __restrict__ resid, T* __restri
     float vx[V], vr[V], o[V];
     Elem<T>::load_vec(x + i * V, vx);
     if (resid != nullptr) Elem<T>::load_vec(resid + i * V, vr);
+    uint32_t keep = 0xffu;
+    if (train && thr != 0u) {
+      // V = 8: the vector is exactly one Philox call; V = 4: the even / odd vector takes the low / high four lanes
+      keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(i * V) >> 3, thr);
+      if (V == 4) keep >>= (i & 1) * 4;
+    }
 #pragma unroll
-    for (int q = 0; q < V / 4; ++q) {
-      float k[4] = {eval_scale, eval_scale, eval_scale, eval_scale};
-      if (train) {
-        const Philox4 r = philox4x32_10(seed, static_cast<uint64_t>(i) * (V / 4) + q, stream_id);
-        k[0] = r.x >= thr ? 1.f : 0.f;
-        k[1] = r.y >= thr ? 1.f : 0.f;
-        k[2] = r.z >= thr ? 1.f : 0.f;
-        k[3] = r.w >= thr ? 1.f : 0.f;
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float d = vx[4 * q + j] * k[j];
-        o[4 * q + j] = resid != nullptr ? vr[4 * q + j] + d : d;
-      }
+    for (int j = 0; j < V; ++j) {
+      const float d = train ? (((keep >> j) & 1u) ? vx[j] : 0.f) : vx[j] * eval_scale;
+      o[j] = resid != nullptr ? vr[j] + d : d;
     }
     Elem<T>::store_vec(y + i * V, o);
   }
@@ -131,7 +126,7 @@ extern "C" int ptj_dropout(const void* x, const void* residual, void* y, int64_t
   if (!x || !y) return PTJ_ERR_BAD_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool vec = aligned16(x) && aligned16(y) && (residual == nullptr || aligned16(residual));
-  const uint32_t thr = dropout_threshold(p);
+  const uint32_t thr = dropout_threshold16(p);
   if (dtype == PTJ_F32) {
     dropout_kernel<float><<<ew_grid(n / 4), kEwThreads, 0, st>>>(
         static_cast<const float*>(x), static_cast<const float*>(residual), static_cast<float*>(y), n, vec, thr,

@@ -23,12 +23,10 @@ embed_fwd_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ w_emb, 
     const TW* e = w_emb + id * dim + c;
     const TW* p = w_pos + (t % seq) * dim + c;
     float k[4] = {eval_scale, eval_scale, eval_scale, eval_scale};
-    if (train) {
-      const Philox4 r = philox4x32_10(seed, static_cast<uint64_t>(i) >> 2, stream_id);
-      k[0] = r.x >= thr ? 1.f : 0.f;
-      k[1] = r.y >= thr ? 1.f : 0.f;
-      k[2] = r.z >= thr ? 1.f : 0.f;
-      k[3] = r.w >= thr ? 1.f : 0.f;
+    if (train) {  // i is a multiple of 4: these four elements are the low or the high half of one Philox call
+      const uint32_t keep = thr != 0u ? dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(i) >> 3, thr) >> (i & 4) : 0xfu;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) k[j] = ((keep >> j) & 1u) ? 1.f : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -58,7 +56,7 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
 // token id; the thread block that lands on the first position of a run of equal ids walks the whole run in order
 // (threads across the feature dimension, 4 features each), so every table row is produced by one block with a fixed
 // summation order and no atomics. Frequent tokens (a Zipf head) make long runs: the walk is a coalesced row read and
-// one Philox call per 4 features per row.
+// one Philox call per 8 features per row.
 template <typename T>
 __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
@@ -77,12 +75,12 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
       for (int64_t q = j; q < end; ++q) {
         const int64_t idx = static_cast<int64_t>(sorted_pos[q]) * dim + c;
         float k0 = train ? 1.f : eval_scale, k1 = k0, k2 = k0, k3 = k0;
-        if (masked) {
-          const Philox4 r = philox4x32_10(seed, static_cast<uint64_t>(idx) >> 2, stream_id);
-          k0 = r.x >= thr ? 1.f : 0.f;
-          k1 = r.y >= thr ? 1.f : 0.f;
-          k2 = r.z >= thr ? 1.f : 0.f;
-          k3 = r.w >= thr ? 1.f : 0.f;
+        if (masked) {  // idx is a multiple of 4
+          const uint32_t keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(idx) >> 3, thr) >> (idx & 4);
+          k0 = (keep & 1u) ? 1.f : 0.f;
+          k1 = (keep & 2u) ? 1.f : 0.f;
+          k2 = (keep & 4u) ? 1.f : 0.f;
+          k3 = (keep & 8u) ? 1.f : 0.f;
         }
         s0 = fmaf(Elem<T>::load(dy + idx), k0, s0);
         s1 = fmaf(Elem<T>::load(dy + idx + 1), k1, s1);
@@ -188,7 +186,7 @@ extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* 
   const int64_t tokens = batch * seq;
   const int grid = flat_grid(tokens * dim / 4, 256);
   const float scale = sqrtf(static_cast<float>(dim));
-  const uint32_t thr = dropout_threshold(p);
+  const uint32_t thr = dropout_threshold16(p);
 #define PTJ_EMBED(TW, T)                                                                                      \
   embed_fwd_kernel<TW, T><<<grid, 256, 0, st>>>(ids, static_cast<const TW*>(w_emb), static_cast<const TW*>(w_pos), \
                                                 static_cast<T*>(y), tokens, seq, (int)dim, vocab, scale, thr,  \
@@ -212,7 +210,7 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tokens = batch * seq;
   const float scale = sqrtf(static_cast<float>(dim));
-  const uint32_t thr = dropout_threshold(p);
+  const uint32_t thr = dropout_threshold16(p);
   if (!accumulate) {
     zero_kernel<<<flat_grid(vocab * dim, 256 * 4), 256, 0, st>>>(d_w_emb, vocab * dim);
     PTJ_CHECK_LAUNCH();

@@ -348,11 +348,12 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   ep.ldc = ldc;
   ep.mode = epilogue;
   const size_t osz = dtype_size(out_dtype);
+  ep.bias_vec_ok = bias != nullptr && aligned16(bias);
   ep.vec_ok = aligned16(c) && (ldc * osz) % 16 == 0 && (aux == nullptr || aligned16(aux)) &&
               (aux_out == nullptr || aligned16(aux_out));
   if (dropout != nullptr) {
     if (!(dropout->p >= 0.f && dropout->p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
-    ep.drop_thr = dropout_threshold(dropout->p);
+    ep.drop_thr = dropout_threshold16(dropout->p);
     ep.eval_scale = 1.f - dropout->p;
     ep.train = dropout->train;
     ep.seed = dropout->seed;

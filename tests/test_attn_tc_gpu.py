@@ -51,7 +51,7 @@ def run_case(ops, B, H, S, p, train, seed, fused_layout):
         qf, kf, vf, gf = (t.float().cpu() for t in (q, k, v, do4))
         mask = None
         if train and p > 0:
-            mask = torch.from_numpy(philox.keep_mask16(seed, 0, B * H * S * S, p)).view(B, H, S, S)
+            mask = torch.from_numpy(philox.keep_mask(seed, 0, B * H * S * S, p)).view(B, H, S, S)
         o_ref, _ = orc.causal_attention(qf, kf, vf, p, train, mask)
         assert rel_err(o4, o_ref) < TOL, f"O {rel_err(o4, o_ref):.3e}"
         rm, rl = orc.causal_attention_stats(qf, kf)

@@ -90,8 +90,7 @@ def _mask_fn(seeds, L, p):
             l, kind = site.split(".")
             seed = seeds[1 + 3 * int(l[1:]) + {"attn": 0, "res1": 1, "res2": 2}[kind]]
         n = math.prod(shape)
-        gen = philox.keep_mask16 if site.endswith(".attn") else philox.keep_mask
-        return torch.from_numpy(gen(seed, 0, n, p)).view(shape)
+        return torch.from_numpy(philox.keep_mask(seed, 0, n, p)).view(shape)
     return fn
 
 

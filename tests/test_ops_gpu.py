@@ -253,7 +253,7 @@ def test_attention_dropout_with_host_mask(ops):
     ops.DROPOUT_RATE = p
     qkv, d_o = rnd(B, H, 3, S, D, seed=1), rnd(B, H, S, D, seed=2)
     q, k, v = qkv.unbind(dim=2)
-    mask = torch.from_numpy(philox.keep_mask16(seed, 0, B * H * S * S, p)).view(B, H, S, S)
+    mask = torch.from_numpy(philox.keep_mask(seed, 0, B * H * S * S, p)).view(B, H, S, S)
     out, acts = ops.t_scaled_dot_prod_attn_fwd3_t(gpu(qkv), None, True, seed)
     o_ref, _ = orc.causal_attention(q, k, v, p, True, mask)
     check(out, o_ref, F32_TOL)
