@@ -34,8 +34,9 @@ if str(ROOT) not in sys.path:
 METRIC = "GPT-2 113M train tokens/s"
 UNIT = "tokens/s"
 MICRO_BATCH = 8
-# DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per launch of the dominant kernel, averaged over the GEMM launches of the train step,
+# from the ncu capture summarised under profiles/
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 82.3e6  # profiles/bench_gpt2small_train_step_launch_list.md
 
 
 def zipf_ids(vocab: int, shape, seed: int, a: float = 1.1) -> torch.Tensor:
