@@ -62,37 +62,64 @@ __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  __shared__ int32_t pos_s[256];
   const bool masked = train && thr != 0u;
+  const float k_all = train ? 1.f : eval_scale;
   for (int64_t j = blockIdx.x; j < tokens; j += gridDim.x) {
     const int32_t id = ids[sorted_pos[j]];
     if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run (uniform over the block)
     if (id < 0 || id >= vocab) continue;
-    int64_t end = j + 1;
-    while (end < tokens && ids[sorted_pos[end]] == id) ++end;
     float* out = d_w_emb + static_cast<int64_t>(id) * dim;
-    for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {  // dim % 4 == 0 is checked on the host
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      for (int64_t q = j; q < end; ++q) {
-        const int64_t idx = static_cast<int64_t>(sorted_pos[q]) * dim + c;
-        float k0 = train ? 1.f : eval_scale, k1 = k0, k2 = k0, k3 = k0;
-        if (masked) {  // idx is a multiple of 4
-          const uint32_t keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(idx) >> 3, thr) >> (idx & 4);
-          k0 = (keep & 1u) ? 1.f : 0.f;
-          k1 = (keep & 2u) ? 1.f : 0.f;
-          k2 = (keep & 4u) ? 1.f : 0.f;
-          k3 = (keep & 8u) ? 1.f : 0.f;
+    // feature columns this thread owns (4 consecutive per slot; dim % 4 == 0 is checked on the host)
+    constexpr int kSlots = 4;  // up to 4 * 256 * 4 = 4096 features
+    float acc[kSlots][4];
+#pragma unroll
+    for (int sl = 0; sl < kSlots; ++sl)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[sl][e] = 0.f;
+    // walk the run in batches of 256 positions: the batch is fetched by the whole block at once (the end of the
+    // run is found by counting matches), then every thread sums its columns over the batch in order
+    for (int64_t base = j;; base += 256) {
+      const int64_t q = base + threadIdx.x;
+      int32_t pos = -1;
+      if (q < tokens) {
+        pos = sorted_pos[q];
+        if (ids[pos] != id) pos = -1;
+      }
+      __syncthreads();  // previous batch fully consumed
+      pos_s[threadIdx.x] = pos;
+      const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
+#pragma unroll
+      for (int sl = 0; sl < kSlots; ++sl) {
+        const int c = (sl * 256 + threadIdx.x) * 4;
+        if (c >= dim) break;
+#pragma unroll 4
+        for (int r = 0; r < n; ++r) {
+          const int64_t idx = static_cast<int64_t>(pos_s[r]) * dim + c;
+          float k0 = k_all, k1 = k_all, k2 = k_all, k3 = k_all;
+          if (masked) {  // idx is a multiple of 4
+            const uint32_t keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(idx) >> 3, thr) >> (idx & 4);
+            k0 = (keep & 1u) ? 1.f : 0.f;
+            k1 = (keep & 2u) ? 1.f : 0.f;
+            k2 = (keep & 4u) ? 1.f : 0.f;
+            k3 = (keep & 8u) ? 1.f : 0.f;
+          }
+          acc[sl][0] = fmaf(Elem<T>::load(dy + idx), k0, acc[sl][0]);
+          acc[sl][1] = fmaf(Elem<T>::load(dy + idx + 1), k1, acc[sl][1]);
+          acc[sl][2] = fmaf(Elem<T>::load(dy + idx + 2), k2, acc[sl][2]);
+          acc[sl][3] = fmaf(Elem<T>::load(dy + idx + 3), k3, acc[sl][3]);
         }
-        s0 = fmaf(Elem<T>::load(dy + idx), k0, s0);
-        s1 = fmaf(Elem<T>::load(dy + idx + 1), k1, s1);
-        s2 = fmaf(Elem<T>::load(dy + idx + 2), k2, s2);
-        s3 = fmaf(Elem<T>::load(dy + idx + 3), k3, s3);
       }
-      if (accumulate) {
-        out[c] += s0 * scale; out[c + 1] += s1 * scale; out[c + 2] += s2 * scale; out[c + 3] += s3 * scale;
-      } else {
-        out[c] = s0 * scale; out[c + 1] = s1 * scale; out[c + 2] = s2 * scale; out[c + 3] = s3 * scale;
-      }
+      if (n < 256) break;
     }
+#pragma unroll
+    for (int sl = 0; sl < kSlots; ++sl) {
+      const int c = (sl * 256 + threadIdx.x) * 4;
+      if (c >= dim) break;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[c + e] = (accumulate ? out[c + e] : 0.f) + acc[sl][e] * scale;
+    }
+    __syncthreads();
   }
 }
 
@@ -203,7 +230,8 @@ extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* 
 extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb,
                              float* d_w_pos, int accumulate, int64_t batch, int64_t seq, int64_t dim, int64_t vocab,
                              float p, int train, uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
-  if (batch < 1 || seq < 1 || dim < 4 || dim % 4 != 0 || vocab < 1 || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+  if (batch < 1 || seq < 1 || dim < 4 || dim % 4 != 0 || dim > 4096 || vocab < 1 || !(p >= 0.f && p <= 1.f))
+    return PTJ_ERR_BAD_SHAPE;
   if (batch * seq > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
   if (!dy || !ids || !sorted_pos || !d_w_emb || !d_w_pos) return PTJ_ERR_BAD_SHAPE;
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
