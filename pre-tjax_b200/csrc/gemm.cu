@@ -32,7 +32,8 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+  static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStripsBytes + 1024 + kBarrierBytes;
   static constexpr int kTmemCols = 512;     // two accumulator buffers, the second at column 256
   static constexpr int kAccStride = 256;
 };
@@ -43,8 +44,33 @@ struct GemmParams {
   int num_m, num_n, num_kb, split_k;
   float* workspace;  // [split_k, M, N] partial sums when split_k > 1
   int out_bf16;
+  int debug;  // timing experiments only (results are garbage): 1 = no TMA copies, 2 = no MMAs
   unsigned int* fault;
 };
+
+// Epilogue of one 32-row x 32-column block of an accumulator tile (one row per lane): arithmetic per thread, stores
+// through the warp's staging strip when the block is full and rows are 16-byte aligned, else per thread.
+template <typename TOut>
+__device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t* strip, int64_t row0, int64_t row,
+                                              int64_t n0, float (&acc)[32], int lane) {
+  const bool inside = epilogue_pre<TOut, 32>(ep, row, n0, acc);
+  TOut* c = static_cast<TOut*>(ep.c);
+  TOut* aux_out = static_cast<TOut*>(ep.aux_out);
+  const bool want_pre = ep.mode == PTJ_EPI_GELU && aux_out != nullptr;
+  const bool staged = ep.vec_ok && n0 + 32 <= ep.N;  // warp-uniform
+  if (want_pre) {
+    if (staged) warp_store_block<TOut>(strip, aux_out, ep.ldc, row0, n0, ep.M, acc, lane);
+    else if (inside) store_row<TOut, 32>(aux_out + row * ep.ldc, n0, ep.N, false, acc);
+  }
+  float side[32];
+  if (const void* sp = epilogue_side_input(ep)) {
+    if (staged) warp_load_block<TOut>(strip, static_cast<const TOut*>(sp), ep.ldc, row0, n0, ep.M, side, lane);
+    else if (inside) load_row<TOut, 32>(static_cast<const TOut*>(sp) + row * ep.ldc, n0, ep.N, false, side);
+  }
+  if (inside) epilogue_post<TOut, 32>(ep, row, n0, acc, side);
+  if (staged) warp_store_block<TOut>(strip, c, ep.ldc, row0, n0, ep.M, acc, lane);
+  else if (inside) store_row<TOut, 32>(c + row * ep.ldc, n0, ep.N, false, acc);
+}
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -53,7 +79,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + Cfg::kStages;
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -102,6 +129,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0101u)) { ok = false; break; }
+          if (p.debug == 1) {
+            mbar_arrive(&full[stage]);
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_expect_tx(&full[stage], Cfg::kStageBytes);
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
@@ -150,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                             : smem_desc_sw128(sa + k4 * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? smem_desc_sw128(sb + k4 * 32, 16, 1024)
                                             : smem_desc_sw128(sb + k4 * 2048, 8192, 1024);
-            mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+            if (p.debug != 2) mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
@@ -173,7 +205,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after_sync();
-      const int64_t row = static_cast<int64_t>(m_blk) * BM + quarter * 32 + lane;
+      const int64_t row0 = static_cast<int64_t>(m_blk) * BM + quarter * 32;
+      const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * Cfg::kAccStride + half * (BN / 2));
 #pragma unroll 1
@@ -185,23 +218,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + half * (BN / 2) + chunk * 32;
+        uint8_t* strip = strips + (warp - 2) * kStripBytes;
         if (p.split_k > 1) {
-          if (row < p.M) {
-            float* w = p.workspace + (static_cast<int64_t>(split) * p.M + row) * p.N;
-            if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
+          float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
+          if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
+            warp_store_block<float>(strip, w, p.N, row0, n0, p.M, acc, lane);
+          } else if (row < p.M) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(w + n0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) w[n0 + j] = acc[j];
-            }
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
           }
         } else if (p.out_bf16) {
-          epilogue_row_segment<__nv_bfloat16, 32>(p.ep, row, n0, acc);
+          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane);
         } else {
-          epilogue_row_segment<float, 32>(p.ep, row, n0, acc);
+          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane);
         }
       }
       tc_fence_before_sync();
@@ -221,6 +251,212 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- CTA-pair kernel -------------------------------------------------------------------------------------------
+// Two CTAs of a cluster (two neighbouring SMs) share one 256 x BN output tile through tcgen05.mma.cta_group::2:
+// CTA r of the pair loads A rows [r*128, r*128+128) and B rows [r*BN/2, (r+1)*BN/2) of the tile into its own
+// shared memory and keeps rows r*128.. of the accumulator in its own tensor memory; one thread of the leader (rank 0)
+// issues the MMAs for both. Per CTA and 16-deep K step that is 8 KB of TMA writes + 8 KB of operand reads instead
+// of 12 + 12 in the single-CTA kernel, which is what the shared-memory port can sustain at full tensor rate.
+// Signals: both CTAs' TMA loads complete on the LEADER's full barrier; tcgen05.commit multicasts the "stage free"
+// and "accumulator ready" arrivals to both CTAs; the peer's epilogue warps arrive remotely on the leader's
+// "accumulator drained" barrier. No TMA multicast is used anywhere.
+template <int BN>
+struct PairCfg {
+  static constexpr int kStages = BN == 256 ? 6 : 8;
+  static constexpr int kABytes = BM * BK * 2;        // per CTA: 128 rows of A
+  static constexpr int kBBytes = (BN / 2) * BK * 2;  // per CTA: half of the tile's B rows
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStripsBytes + 1024 + kBarrierBytes;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kAccStride = 256;
+};
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using Cfg = PairCfg<BN>;
+  constexpr int HB = BN / 2;  // B rows held by one CTA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes);
+  uint64_t* full = bars;                      // used in the leader only
+  uint64_t* empty = bars + Cfg::kStages;      // one set per CTA, both signalled by the leader's commits
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;       // used in the leader only: 8 local + 8 remote epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const AbortCtx ctx{abort_flag, p.fault};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 2 * kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
+  const int total = tiles * p.split_k;
+  const int pair = static_cast<int>(blockIdx.x) >> 1, npairs = static_cast<int>(gridDim.x) >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = pair; item < total && ok; item += npairs) {
+        const int split = item / tiles, tile = item - split * tiles;
+        const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        const int m0 = m_blk * 2 * BM + static_cast<int>(rank) * BM;
+        const int n0 = n_blk * BN + static_cast<int>(rank) * HB;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0401u)) { ok = false; break; }
+          const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::kStageBytes);  // both CTAs' bytes land here
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          if (A_KMAJOR) {
+            tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(sa + h * 8192, &tmap_a, leader_full, m0 + h * 64, kb * BK);
+          }
+          if (B_KMAJOR) {
+            tma_load_2d_pair(sb, &tmap_b, leader_full, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int h = 0; h < HB / 64; ++h) tma_load_2d_pair(sb + h * 8192, &tmap_b, leader_full, n0 + h * 64, kb * BK);
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN, !A_KMAJOR, !B_KMAJOR);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int item = pair; item < total && ok; item += npairs, ++it) {
+        const int split = item / tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1u;
+        if (!mbar_wait_cluster(&tmem_empty[buf], aphase ^ 1u, ctx, 0x0501u)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * Cfg::kAccStride);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_cluster(&full[stage], phase, ctx, 0x0502u)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t adesc = A_KMAJOR ? smem_desc_sw128(sa + k4 * 32, 16, 1024)
+                                            : smem_desc_sw128(sa + k4 * 2048, 8192, 1024);
+            const uint64_t bdesc = B_KMAJOR ? smem_desc_sw128(sb + k4 * 32, 16, 1024)
+                                            : smem_desc_sw128(sb + k4 * 2048, 8192, 1024);
+            mma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(&empty[stage], 3);  // stage free in both CTAs once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit_pair(&tmem_full[buf], 3);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunks = BN / 64;
+    const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
+    const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
+    int it = 0;
+    bool ok = true;
+    for (int item = pair; item < total && ok; item += npairs, ++it) {
+      const int split = item / tiles, tile = item - split * tiles;
+      const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1u;
+      ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0601u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * BM + static_cast<int64_t>(rank) * BM + quarter * 32;
+      const int64_t row = row0 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * Cfg::kAccStride + half * (BN / 2));
+#pragma unroll 1
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + chunk * 32, r);
+        tmem_ld_wait();
+        float acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + half * (BN / 2) + chunk * 32;
+        uint8_t* strip = strips + (warp - 2) * kStripBytes;
+        if (p.split_k > 1) {
+          float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
+          if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
+            warp_store_block<float>(strip, w, p.N, row0, n0, p.M, acc, lane);
+          } else if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
+          }
+        } else if (p.out_bf16) {
+          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane);
+        } else {
+          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(buf == 0 ? leader_empty0 : leader_empty1);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while its peer may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -318,6 +554,70 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
   return PTJ_OK;
 }
 
+// sums the K-split partial tiles in a fixed order (no-op when split_k == 1)
+int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int64_t N, int64_t ldc, int split_k,
+                   int epilogue, int out_dtype, cudaStream_t st) {
+  if (split_k <= 1) return PTJ_OK;
+  const int64_t total = M * N;
+  const bool w4 = N % 4 == 0;
+  int64_t blocks = ceil_div(total, 256 * (w4 ? 4 : 1));
+  if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+  const int acc = epilogue == PTJ_EPI_ACCUM;
+  const int g = static_cast<int>(blocks);
+  if (out_dtype == PTJ_F32) {
+    if (w4) splitk_reduce_kernel<float, 4><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+    else splitk_reduce_kernel<float, 1><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+  } else {
+    if (w4) splitk_reduce_kernel<__nv_bfloat16, 4><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    else splitk_reduce_kernel<__nv_bfloat16, 1><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+  }
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+template <int BN, bool AK, bool BK_>
+int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+  using Cfg = PairCfg<BN>;
+  auto kern = gemm_tc_pair_kernel<BN, AK, BK_>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return PTJ_ERR_LAUNCH;
+  }
+  const int total = p.num_m * p.num_n * p.split_k;
+  const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return PTJ_ERR_LAUNCH;
+  }
+  count_launch(1);
+  return PTJ_OK;
+}
+
+// Which kernel: the CTA-pair kernel halves the shared-memory traffic per FLOP and wins wherever the main loop is
+// long (K >= 2048: weight gradients, the second FFN matrix) or the output is huge (LM head); its 256 x 256 tiles
+// quantise worse on the small N = 768 products, which stay on the single-CTA kernel. PTJ_GEMM_PAIR=0 / 1 forces it.
+bool use_pair_kernel(int64_t M, int64_t N, int64_t K) {
+  static const int forced = [] {
+    const char* e = std::getenv("PTJ_GEMM_PAIR");
+    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+  }();
+  if (M < 256 || N < 256) return false;
+  if (forced >= 0) return forced == 1;
+  return K >= 2048 || N >= 8192;
+}
+
 }  // namespace
 }  // namespace ptj
 
@@ -398,6 +698,34 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   p.out_bf16 = out_dtype == PTJ_BF16;
   p.fault = tc::fault_word();
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
+  if (const char* e = std::getenv("PTJ_GEMM_DEBUG")) p.debug = std::atoi(e);
+
+  if (use_pair_kernel(M, N, K)) {
+    const int pbn = 256;
+    p.num_m = static_cast<int>(ceil_div(M, 2 * BM));
+    p.num_n = static_cast<int>(ceil_div(N, pbn));
+    CUtensorMap ta, tb;
+    {
+      const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+      const uint64_t dims_mn[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
+      const uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+      const uint32_t box_k[2] = {64, 128}, box_mn[2] = {64, 64};
+      if (!make_tmap_bf16(&ta, a, 2, a_kmajor ? dims_k : dims_mn, str, a_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
+    }
+    {
+      const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+      const uint64_t dims_mn[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+      const uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+      const uint32_t box_k[2] = {64, static_cast<uint32_t>(pbn / 2)}, box_mn[2] = {64, 64};
+      if (!make_tmap_bf16(&tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
+    }
+    int prc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true>(ta, tb, p, st)
+                                   : launch_tc_pair<256, true, false>(ta, tb, p, st))
+                       : (b_kmajor ? launch_tc_pair<256, false, true>(ta, tb, p, st)
+                                   : launch_tc_pair<256, false, false>(ta, tb, p, st));
+    if (prc != PTJ_OK) return prc;
+    return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
+  }
 
   // tile width: fewer, fatter tiles (less operand traffic per FLOP) unless that leaves SMs idle in the last wave.
   // cost = waves x tile width x relative cost per column of that width
@@ -442,21 +770,5 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
 #undef PTJ_TC
   if (rc != PTJ_OK) return rc;
 
-  if (split_k > 1) {
-    const int64_t total = M * N;
-    const bool w4 = N % 4 == 0;
-    int64_t blocks = ceil_div(total, 256 * (w4 ? 4 : 1));
-    if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
-    const int acc = epilogue == PTJ_EPI_ACCUM;
-    const int g = static_cast<int>(blocks);
-    if (out_dtype == PTJ_F32) {
-      if (w4) splitk_reduce_kernel<float, 4><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
-      else splitk_reduce_kernel<float, 1><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
-    } else {
-      if (w4) splitk_reduce_kernel<__nv_bfloat16, 4><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
-      else splitk_reduce_kernel<__nv_bfloat16, 1><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
-    }
-    PTJ_CHECK_LAUNCH();
-  }
-  return PTJ_OK;
+  return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
 }
