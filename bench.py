@@ -143,8 +143,11 @@ def run_reference_arm(args, cfg):
 
 
 def workload_config(cfg, n):
-    return {"workload": "gpt2-small 12L/d768/12H/FFN3072/S1024/V50257 (124,453,201 params; the reference calls its "
-                        "V=35k/S=512 variant 113M): full train step fwd+bwd+clip+AdamW, dropout 0.1, Zipf(1.1) ids",
+    name = {12: "gpt2-small", 24: "gpt2-medium"}.get(cfg.layers, "gpt2")
+    note = " (the reference calls its V=35k/S=512 variant of this model 113M)" if cfg.layers == 12 else ""
+    return {"workload": f"{name} {cfg.layers}L/d{cfg.dim}/{cfg.heads}H/FFN{cfg.ffn}/S{cfg.seq}/V{cfg.vocab}, "
+                        f"{cfg.num_params():,} params{note}: full train step fwd+bwd+clip+AdamW, "
+                        f"dropout {cfg.dropout}, Zipf(1.1) ids",
             "global_batch": MICRO_BATCH * n, "micro_batch_per_gpu": MICRO_BATCH, "seq_len": cfg.seq,
             "parallelism": f"dp{n}", "l2": "per-step working set (about 1.3 GB of weights+moments traffic and several "
                                            "GB of activations) far exceeds the 126 MB L2; no explicit flush"}
@@ -157,13 +160,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="gpt2-small")
+    ap.add_argument("--model", default="gpt2-small", choices=["gpt2-small", "gpt2-medium"])
+    ap.add_argument("--micro-batch", type=int, default=None, help="sequences per GPU (default 8; 16 for gpt2-medium)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     ptj = importlib.import_module("pre-tjax_b200")
     cfg = ptj.PRESETS[args.model]
+    global MICRO_BATCH
+    MICRO_BATCH = args.micro_batch or (16 if args.model == "gpt2-medium" else 8)
     if args.impl == "reference":
         run_reference_arm(args, cfg)
         return
