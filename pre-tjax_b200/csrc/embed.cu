@@ -53,32 +53,30 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
 }
 
 // Gradient w.r.t. the embedding table (model_triton.py:183-185, 205-213). Token positions arrive stably sorted by
-// token id; the thread block that lands on the first position of a run of equal ids walks the whole run in order
-// (threads across the feature dimension, 4 features each), so every table row is produced by one block with a fixed
-// summation order and no atomics. Frequent tokens (a Zipf head) make long runs: the walk is a coalesced row read and
-// one Philox call per 8 features per row.
-template <typename T>
+// token id; the thread block that lands on the first position of a run of equal ids sums the whole run: the run is
+// fetched in batches of 256 positions, warp w takes rows w, w+8, ... of a batch (lanes across the features, 8 per
+// vector = one Philox call), and the 8 per-warp partial rows are added in warp order at the end. One block, fixed
+// order, no atomics => every table row is reproducible. Frequent tokens (a Zipf head) make runs of ~1000 rows.
+template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  extern __shared__ float part[];  // [8][dim]
   __shared__ int32_t pos_s[256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool masked = train && thr != 0u;
   const float k_all = train ? 1.f : eval_scale;
+  const int nvec = dim / 8;  // dim % 8 == 0 is checked on the host
   for (int64_t j = blockIdx.x; j < tokens; j += gridDim.x) {
     const int32_t id = ids[sorted_pos[j]];
     if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run (uniform over the block)
     if (id < 0 || id >= vocab) continue;
-    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
-    // feature columns this thread owns (4 consecutive per slot; dim % 4 == 0 is checked on the host)
-    constexpr int kSlots = 4;  // up to 4 * 256 * 4 = 4096 features
-    float acc[kSlots][4];
+    float acc[NV][8];
 #pragma unroll
-    for (int sl = 0; sl < kSlots; ++sl)
+    for (int i = 0; i < NV; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[sl][e] = 0.f;
-    // walk the run in batches of 256 positions: the batch is fetched by the whole block at once (the end of the
-    // run is found by counting matches), then every thread sums its columns over the batch in order
+      for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
     for (int64_t base = j;; base += 256) {
       const int64_t q = base + threadIdx.x;
       int32_t pos = -1;
@@ -89,35 +87,47 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
       __syncthreads();  // previous batch fully consumed
       pos_s[threadIdx.x] = pos;
       const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
+      for (int r = warp; r < n; r += 8) {
+        const int64_t row = static_cast<int64_t>(pos_s[r]) * dim;
 #pragma unroll
-      for (int sl = 0; sl < kSlots; ++sl) {
-        const int c = (sl * 256 + threadIdx.x) * 4;
-        if (c >= dim) break;
-#pragma unroll 4
-        for (int r = 0; r < n; ++r) {
-          const int64_t idx = static_cast<int64_t>(pos_s[r]) * dim + c;
-          float k0 = k_all, k1 = k_all, k2 = k_all, k3 = k_all;
-          if (masked) {  // idx is a multiple of 4
-            const uint32_t keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(idx) >> 3, thr) >> (idx & 4);
-            k0 = (keep & 1u) ? 1.f : 0.f;
-            k1 = (keep & 2u) ? 1.f : 0.f;
-            k2 = (keep & 4u) ? 1.f : 0.f;
-            k3 = (keep & 8u) ? 1.f : 0.f;
+        for (int i = 0; i < NV; ++i) {
+          const int v = lane + 32 * i;
+          if (v < nvec) {
+            float x[8];
+            if (sizeof(T) == 2) {
+              Elem<__nv_bfloat16>::load_vec(reinterpret_cast<const __nv_bfloat16*>(dy) + row + v * 8, x);
+            } else {
+              float lo[4], hi[4];
+              Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + row + v * 8, lo);
+              Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + row + v * 8 + 4, hi);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { x[e] = lo[e]; x[4 + e] = hi[e]; }
+            }
+            uint32_t keep = 0xffu;
+            if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(row + v * 8) >> 3, thr);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
           }
-          acc[sl][0] = fmaf(Elem<T>::load(dy + idx), k0, acc[sl][0]);
-          acc[sl][1] = fmaf(Elem<T>::load(dy + idx + 1), k1, acc[sl][1]);
-          acc[sl][2] = fmaf(Elem<T>::load(dy + idx + 2), k2, acc[sl][2]);
-          acc[sl][3] = fmaf(Elem<T>::load(dy + idx + 3), k3, acc[sl][3]);
         }
       }
       if (n < 256) break;
     }
+    __syncthreads();
 #pragma unroll
-    for (int sl = 0; sl < kSlots; ++sl) {
-      const int c = (sl * 256 + threadIdx.x) * 4;
-      if (c >= dim) break;
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) out[c + e] = (accumulate ? out[c + e] : 0.f) + acc[sl][e] * scale;
+        for (int e = 0; e < 8; ++e) part[warp * dim + v * 8 + e] = acc[i][e];
+      }
+    }
+    __syncthreads();
+    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += part[w * dim + c];
+      out[c] = (accumulate ? out[c] : 0.f) + s * scale;
     }
     __syncthreads();
   }
@@ -198,6 +208,25 @@ inline int flat_grid(int64_t work, int per_block) {
   return static_cast<int>(b < cap ? b : cap);
 }
 
+template <typename T>
+int launch_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb, int64_t tokens,
+                     int dim, int64_t vocab, float scale, uint32_t thr, float eval_scale, int train, uint64_t seed,
+                     uint32_t stream_id, int grid, cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(8) * dim * sizeof(float);
+  const int nv = (dim / 8 + 31) / 32;
+#define PTJ_EMB(NV)                                                                                              \
+  {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(embed_bwd_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    embed_bwd_kernel<T, NV><<<grid, 256, smem, st>>>(static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, tokens, \
+                                                     dim, vocab, scale, thr, eval_scale, train, seed, stream_id); \
+  }
+  if (nv <= 1) PTJ_EMB(1) else if (nv <= 2) PTJ_EMB(2) else if (nv <= 4) PTJ_EMB(4) else if (nv <= 8) PTJ_EMB(8) else PTJ_EMB(16)
+#undef PTJ_EMB
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
 }  // namespace
 }  // namespace ptj
 
@@ -230,10 +259,11 @@ extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* 
 extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb,
                              float* d_w_pos, int accumulate, int64_t batch, int64_t seq, int64_t dim, int64_t vocab,
                              float p, int train, uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
-  if (batch < 1 || seq < 1 || dim < 4 || dim % 4 != 0 || dim > 4096 || vocab < 1 || !(p >= 0.f && p <= 1.f))
+  if (batch < 1 || seq < 1 || dim < 8 || dim % 8 != 0 || dim > 4096 || vocab < 1 || !(p >= 0.f && p <= 1.f))
     return PTJ_ERR_BAD_SHAPE;
   if (batch * seq > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
   if (!dy || !ids || !sorted_pos || !d_w_emb || !d_w_pos) return PTJ_ERR_BAD_SHAPE;
+  if (!aligned16(dy)) return PTJ_ERR_MISALIGNED;
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tokens = batch * seq;
@@ -246,15 +276,16 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
   const int grid_e = flat_grid(tokens, 1);  // one block per sorted position (only run heads do work)
   const int grid_p = flat_grid(seq * dim, 256);
   if (dtype == PTJ_F32) {
-    embed_bwd_kernel<float><<<grid_e, 256, 0, st>>>(static_cast<const float*>(dy), ids, sorted_pos, d_w_emb, 1, tokens,
-                                                    (int)dim, vocab, scale, thr, 1.f - p, train, seed, stream_id);
+    if (launch_embed_bwd<float>(dy, ids, sorted_pos, d_w_emb, tokens, (int)dim, vocab, scale, thr, 1.f - p, train, seed,
+                                stream_id, grid_e, st) != PTJ_OK)
+      return PTJ_ERR_LAUNCH;
     PTJ_CHECK_LAUNCH();
     pos_bwd_kernel<float><<<grid_p, 256, 0, st>>>(static_cast<const float*>(dy), d_w_pos, batch, seq, (int)dim, thr,
                                                   1.f - p, train, seed, stream_id);
   } else {
-    embed_bwd_kernel<__nv_bfloat16><<<grid_e, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), ids, sorted_pos,
-                                                            d_w_emb, 1, tokens, (int)dim, vocab, scale, thr, 1.f - p,
-                                                            train, seed, stream_id);
+    if (launch_embed_bwd<__nv_bfloat16>(dy, ids, sorted_pos, d_w_emb, tokens, (int)dim, vocab, scale, thr, 1.f - p, train,
+                                        seed, stream_id, grid_e, st) != PTJ_OK)
+      return PTJ_ERR_LAUNCH;
     PTJ_CHECK_LAUNCH();
     pos_bwd_kernel<__nv_bfloat16><<<grid_p, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), d_w_pos, batch, seq,
                                                           (int)dim, thr, 1.f - p, train, seed, stream_id);
