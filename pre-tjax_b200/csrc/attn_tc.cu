@@ -13,289 +13,12 @@
 //   backward: kernel A (one block per KV tile, loops over query tiles): dV += Pd^T dO, dK += dS^T Q  (tensor memory)
 //             kernel B (one block per query tile, loops over KV tiles): dQ += dS K
 //             both recompute S and dP = dO V^T; no atomics, so results are bit-reproducible.
-#include "attn_common.cuh"
-#include "tc_common.cuh"
-#include "tc_runtime.h"
+#include "attn_tc_dev.cuh"
 
 namespace ptj {
 namespace {
 
-using namespace tc;
-
-constexpr int T = 128;            // tile edge along queries and keys
-constexpr int DH = 64;            // head size
-constexpr int kTileBytes = T * DH * 2;  // one [128][64] bf16 tile
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-
-struct RowView {  // a [batch, heads, seq, 64] view with 64 contiguous
-  __nv_bfloat16* base;
-  int64_t sb, sh, sr;
-  __device__ __forceinline__ __nv_bfloat16* row(int64_t b, int64_t h, int64_t r) const {
-    return base + b * sb + h * sh + r * sr;
-  }
-};
-
-struct AttnParams {
-  int S, H, BH, nq;
-  float scale_log2;  // log2(e) / sqrt(d_head)
-  float scale;       // 1 / sqrt(d_head)
-  AttnDropout dr;
-  unsigned int* fault;
-};
-
-// keep flags of 32 consecutive probability elements starting at flat index idx0 (a multiple of 8)
-__device__ __forceinline__ uint32_t keep_bits32(const AttnDropout& dr, uint64_t idx0) {
-  uint32_t bits = 0;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) bits |= dropout_keep_bits8(dr.seed, dr.stream_id, (idx0 >> 3) + c, dr.thr16) << (c * 8);
-  return bits;
-}
-
-// Write 32 consecutive columns (col0 % 32 == 0) of row r of a [128][128] bf16 tile stored as two [128][64]
-// 128-byte-swizzled sub-tiles that are kTileBytes apart.
-__device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int r, int col0, const float (&v)[32]) {
-  uint8_t* line = tile + (col0 >> 6) * kTileBytes + r * 128;
-  const int cb = (col0 & 63) >> 3;
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(v[t * 8 + 2 * i], v[t * 8 + 2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(line + (((cb + t) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
-
-__device__ __forceinline__ void tmem_ld_row32(uint32_t taddr, float (&f)[32]) {
-  uint32_t r[32];
-  tmem_ld_32x32(taddr, r);
-  tmem_ld_wait();
-#pragma unroll
-  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-}
-
-// 2^x on the special-function unit (inputs here are <= 0 or small; subnormal results flush to zero)
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// descriptors of the five operand flavours used below (all tiles are 128-byte swizzled, 8-line groups 1024 B apart)
-__device__ __forceinline__ uint64_t desc_kmajor_d(uint32_t tile, int k16) {  // [rows][64 d], K = d
-  return smem_desc_sw128(tile + k16 * 32, 16, 1024);
-}
-__device__ __forceinline__ uint64_t desc_rows_as_k(uint32_t tile, int k16) {  // [128 rows][64 d], K = rows, MN = d
-  return smem_desc_sw128(tile + k16 * 2048, kTileBytes, 1024);
-}
-__device__ __forceinline__ uint64_t desc_p_kmajor(uint32_t tile, int k16) {  // [128 q][128 kv], M = q, K = kv
-  return smem_desc_sw128(tile + (k16 >> 2) * kTileBytes + (k16 & 3) * 32, 16, 1024);
-}
-__device__ __forceinline__ uint64_t desc_p_transposed(uint32_t tile, int k16) {  // same bytes, M = kv, K = q rows
-  return smem_desc_sw128(tile + k16 * 2048, kTileBytes, 1024);
-}
-
-__device__ __forceinline__ uint8_t* align1024(uint8_t* raw) {
-  return raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
-}
-
-// ---------------------------------------------------------------------------------------------------------------------
-// forward
-// ---------------------------------------------------------------------------------------------------------------------
-constexpr int kFwdSmem = 3 * kTileBytes + 2 * kTileBytes + 1024 + 128;  // Q, K, V, P(2 sub-tiles), align, barriers
-constexpr int kFwdTmemCols = 256;                                        // S: 128 columns, O_j: 64 columns
-
-__global__ void __launch_bounds__(128, 2)
-attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const RowView out, float* __restrict__ row_max,
-                   float* __restrict__ row_sum, const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* sm = align1024(smem_raw);
-  uint8_t* q_s = sm;
-  uint8_t* k_s = sm + kTileBytes;
-  uint8_t* v_s = sm + 2 * kTileBytes;
-  uint8_t* p_s = sm + 3 * kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 5 * kTileBytes);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3, *bar_o = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int qt = p.nq - 1 - static_cast<int>(blockIdx.x) / p.BH;  // heavy (late) query tiles are scheduled first
-  const int bh = static_cast<int>(blockIdx.x) % p.BH;
-  const int b = bh / p.H, h = bh % p.H;
-  const AbortCtx ctx{abort_flag, p.fault};
-
-  if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 0) {
-    __syncwarp();
-    tmem_alloc(tmem_slot, kFwdTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem + (static_cast<uint32_t>(warp * 32) << 16);  // this warp's lanes, S at column 0
-  const uint32_t t_o = t_s + 128;                                           // O_j at column 128
-  constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);
-  constexpr uint32_t idesc_o = idesc_bf16_f32(T, DH, false, true);
-  const int nkv = qt + 1;
-  bool dead = false;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, kTileBytes);
-    tma_load_4d(q_s, &tm_q, bar_q, 0, qt * T, h, b);
-    mbar_expect_tx(bar_k, kTileBytes);
-    tma_load_4d(k_s, &tm_k, bar_k, 0, 0, h, b);
-    mbar_expect_tx(bar_v, kTileBytes);
-    tma_load_4d(v_s, &tm_v, bar_v, 0, 0, h, b);
-    dead = !mbar_wait(bar_q, 0, ctx, 0x1001u) || !mbar_wait(bar_k, 0, ctx, 0x1002u);
-    if (!dead) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int k16 = 0; k16 < DH / 16; ++k16)
-        mma_bf16_ss(tmem, desc_kmajor_d(smem_u32(q_s), k16), desc_kmajor_d(smem_u32(k_s), k16), idesc_s, k16 > 0);
-      mma_commit(bar_s);
-    }
-  }
-
-  const int64_t q_row = static_cast<int64_t>(qt) * T + tid;
-  float m2 = -INFINITY, l = 0.f;
-  float o[DH];
-#pragma unroll
-  for (int d = 0; d < DH; ++d) o[d] = 0.f;
-
-  for (int j = 0; j < nkv; ++j) {
-    const uint32_t ph = j & 1;
-    if (!dead) dead = !mbar_wait(bar_s, ph, ctx, 0x1003u);
-    tc_fence_after_sync();
-    if (tid == 0 && !dead && j + 1 < nkv) {  // K tile is free: the score MMA has finished reading it
-      mbar_expect_tx(bar_k, kTileBytes);
-      tma_load_4d(k_s, &tm_k, bar_k, 0, (j + 1) * T, h, b);
-    }
-    const bool diag = j == qt;
-    float alpha = 1.f, rowsum = 0.f;
-    dead = __any_sync(0xffffffffu, dead);  // warp-uniform from here on: tcgen05.ld needs the whole warp
-    if (!dead) {
-      // pass 1: row maximum of the raw scores (the causal mask only matters on the diagonal tile), then scaled
-      float mraw = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float s[32];
-        tmem_ld_row32(t_s + c * 32, s);
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, c * 32 + i > tid ? -INFINITY : s[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mraw = fmaxf(mraw, s[i]);
-        }
-      }
-      const float mx = fmaxf(m2, mraw * p.scale_log2);
-      alpha = ex2_approx(m2 - mx);
-      m2 = mx;
-      // pass 2: probabilities, row sum, dropout, bf16 tile for the second MMA
-      const bool masked = p.dr.train && p.dr.thr16 != 0u;
-      const float f_eval = p.dr.train ? 1.f : p.dr.eval_scale;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float s[32];
-        tmem_ld_row32(t_s + c * 32, s);
-        uint32_t keep = 0xffffffffu;
-        if (masked)
-          keep = keep_bits32(p.dr, (static_cast<uint64_t>(bh) * p.S + q_row) * p.S + static_cast<uint64_t>(j) * T + c * 32);
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = c * 32 + i > tid ? 0.f : ex2_approx(fmaf(s[i], p.scale_log2, -m2));
-            rowsum += e;
-            s[i] = ((keep >> i) & 1u) ? e * f_eval : 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = ex2_approx(fmaf(s[i], p.scale_log2, -m2));
-            rowsum += e;
-            s[i] = ((keep >> i) & 1u) ? e * f_eval : 0.f;
-          }
-        }
-        store_row32_sw128(p_s, tid, c * 32, s);
-      }
-      l = l * alpha + rowsum;
-    }
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    if (__syncthreads_or(dead ? 1 : 0)) { dead = true; break; }
-    if (tid == 0) {
-      tc_fence_after_sync();
-      dead = !mbar_wait(bar_v, ph, ctx, 0x1004u);
-      if (!dead) {
-        tc_fence_after_sync();
-#pragma unroll
-        for (int k16 = 0; k16 < T / 16; ++k16)
-          mma_bf16_ss(tmem + 128, desc_p_kmajor(smem_u32(p_s), k16), desc_rows_as_k(smem_u32(v_s), k16), idesc_o, k16 > 0);
-        mma_commit(bar_o);
-        if (j + 1 < nkv) {  // next score tile right behind it: S in tensor memory has been consumed by every thread
-          dead = !mbar_wait(bar_k, ph ^ 1u, ctx, 0x1005u);
-          if (!dead) {
-            tc_fence_after_sync();
-#pragma unroll
-            for (int k16 = 0; k16 < DH / 16; ++k16)
-              mma_bf16_ss(tmem, desc_kmajor_d(smem_u32(q_s), k16), desc_kmajor_d(smem_u32(k_s), k16), idesc_s, k16 > 0);
-            mma_commit(bar_s);
-          }
-        }
-      }
-    }
-    if (!dead) dead = !mbar_wait(bar_o, ph, ctx, 0x1006u);
-    tc_fence_after_sync();
-    if (tid == 0 && !dead && j + 1 < nkv) {  // V tile is free
-      mbar_expect_tx(bar_v, kTileBytes);
-      tma_load_4d(v_s, &tm_v, bar_v, 0, (j + 1) * T, h, b);
-    }
-    dead = __any_sync(0xffffffffu, dead);
-    if (!dead) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float t[32];
-        tmem_ld_row32(t_o + c * 32, t);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + t[i];
-      }
-    }
-  }
-
-  if (!__syncthreads_or(dead ? 1 : 0)) {
-    const float inv = 1.f / l;
-    __nv_bfloat16* dst = out.row(b, h, q_row);
-#pragma unroll
-    for (int c = 0; c < DH / 8; ++c) {
-      float t[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) t[i] = o[c * 8 + i] * inv;
-      Elem<__nv_bfloat16>::store_vec(dst + c * 8, t);
-    }
-    const int64_t ri = static_cast<int64_t>(bh) * p.S + q_row;
-    row_max[ri] = m2 * kLn2;
-    row_sum[ri] = l;
-  } else {
-    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before shared memory is released
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem, kFwdTmemCols);
-  }
-}
+using namespace attn_tc;
 
 // ---------------------------------------------------------------------------------------------------------------------
 // backward. MODE 0: block owns a KV tile, loops over query tiles >= it, produces dK and dV.
@@ -570,33 +293,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
-bool make_map(CUtensorMap* m, const void* base, const ptj_attn_shape& sh, const int64_t (&st)[3]) {
-  const uint64_t dims[4] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(sh.seq), static_cast<uint64_t>(sh.heads),
-                            static_cast<uint64_t>(sh.batch)};
-  // a size-1 dimension may come with a zero stride; the encoder wants positive multiples of 16 bytes
-  auto fix = [&](int64_t s) { return static_cast<uint64_t>(s > 0 ? s : DH) * 2; };
-  const uint64_t strides[3] = {fix(st[2]), fix(st[1]), fix(st[0])};
-  const uint32_t box[4] = {DH, T, 1, 1};
-  return make_tmap_bf16(m, base, 4, dims, strides, box);
-}
-
-RowView make_view(const void* base, const int64_t (&st)[3]) {
-  return RowView{static_cast<__nv_bfloat16*>(const_cast<void*>(base)), st[0], st[1], st[2]};
-}
-
-AttnParams make_params(const ptj_attn_shape& sh, const AttnDropout& dr) {
-  AttnParams p{};
-  p.S = static_cast<int>(sh.seq);
-  p.H = static_cast<int>(sh.heads);
-  p.BH = static_cast<int>(sh.batch * sh.heads);
-  p.nq = p.S / T;
-  p.scale = 1.f / sqrtf(static_cast<float>(DH));
-  p.scale_log2 = p.scale * kLog2e;
-  p.dr = dr;
-  p.fault = tc::fault_word();
-  return p;
-}
-
 }  // namespace
 
 bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs) {
@@ -610,22 +306,6 @@ bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int np
     if ((sh.batch > 1 && st[0] <= 0) || (sh.heads > 1 && st[1] <= 0)) return false;
   }
   return ptj_device_check() == PTJ_OK;
-}
-
-int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
-  CUtensorMap tq, tk, tv;
-  if (!make_map(&tq, q, sh, sh.q_strides) || !make_map(&tk, k, sh, sh.k_strides) || !make_map(&tv, v, sh, sh.v_strides))
-    return PTJ_ERR_LAUNCH;
-  const AttnParams p = make_params(sh, dr);
-  if (p.fault == nullptr) return PTJ_ERR_DEVICE;
-  if (cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return PTJ_ERR_LAUNCH;
-  }
-  attn_fwd_tc_kernel<<<p.nq * p.BH, 128, kFwdSmem, st>>>(tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p);
-  PTJ_CHECK_LAUNCH();
-  return PTJ_OK;
 }
 
 int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
