@@ -194,11 +194,17 @@ typedef struct {
 int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
                  const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
                  int dtype, void* stream);
-/* dq/dk/dv use q/k/v strides of `dshape`; d_o and o use o_strides of `shape`. */
+/* dq/dk/dv use q/k/v strides of `dshape`; d_o and o use o_strides of `shape`.
+ * workspace: ptj_attn_bwd_workspace_bytes(shape, dtype) bytes of device memory, 16-byte aligned, contents
+ * irrelevant before and after the call (the tensor-core path keeps each KV tile's share of dQ there in fp32 and sums
+ * the shares in a fixed order instead of the reference's tl.atomic_add, model_triton.py:938; 0 bytes = not needed,
+ * NULL allowed). Too small a workspace returns PTJ_ERR_WORKSPACE. */
+size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int dtype);
 int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                  const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
                  const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
-                 uint64_t seed, uint32_t stream_id, int dtype, void* stream);
+                 uint64_t seed, uint32_t stream_id, void* workspace, size_t workspace_bytes, int dtype,
+                 void* stream);
 
 /* ---- optimizer -------------------------------------------------------------------------------------- */
 /* sum of squares of a float vector -> out[0] (deterministic two-stage). Replaces grads_l2norm

@@ -43,10 +43,21 @@ extern "C" int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o
   return attn_fwd_simt(q, k, v, o, row_max, row_sum, *shape, dr, dtype, st);
 }
 
+static bool bwd_uses_tc(const ptj_attn_shape* shape, int dtype) {
+  const void* none[1] = {nullptr};
+  return dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, none, 0);
+}
+
+extern "C" size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int dtype) {
+  if (!shape_ok(shape) || !bwd_uses_tc(shape, dtype)) return 0;
+  return attn_bwd_tc_workspace_bytes(*shape);
+}
+
 extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                             const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
                             const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
-                            uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
+                            uint64_t seed, uint32_t stream_id, void* workspace, size_t workspace_bytes, int dtype,
+                            void* stream) {
   if (!shape_ok(shape) || !shape_ok(dshape) || !d_o || !q || !k || !v || !o || !row_max || !row_sum || !dq || !dk ||
       !dv || !(p >= 0.f && p <= 1.f))
     return PTJ_ERR_BAD_SHAPE;
@@ -58,6 +69,6 @@ extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const
   const AttnDropout dr = make_dropout(p, train, seed, stream_id);
   const void* ptrs[8] = {d_o, q, k, v, o, dq, dk, dv};
   if (dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, ptrs, 8) && attn_tc_supported(*dshape, ptrs, 0))
-    return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, st);
+    return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, workspace, workspace_bytes, st);
   return attn_bwd_simt(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, dtype, st);
 }

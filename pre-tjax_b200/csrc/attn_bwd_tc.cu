@@ -1,0 +1,614 @@
+// Causal flash attention backward on tcgen05 tensor cores (bf16 in, fp32 accumulate), d_head = 64, seq % 128 == 0.
+// Semantics: model_triton.py:801-811 / 550-577: with P = softmax(causal(Q K^T / sqrt(d))) recomputed from the saved row
+// statistics and Pd = dropout(P):  dV = Pd^T dO,  dP = dO V^T,  dS = P o (dP o keep - delta) / sqrt(d) with
+// delta = rowsum(dO o O),  dK = dS^T Q,  dQ = dS K.
+//
+// Three launches:
+//   1. prep:   delta[q] and the log2-domain log-sum-exp of every query row (one warp per four rows)
+//   2. main:   persistent, warp-specialised block per SM. A work item is a (KV tile j, batch*head); its tiles are the
+//              query tiles i >= j. dK_j and dV_j accumulate in tensor memory over the item; the 128 x 64 product
+//              dS_ij K_j (tile i's share of dQ_i) is written to an fp32 workspace.
+//   3. reduce: dQ_i = sum over j <= i of the workspace tiles, in a fixed order, to bf16.
+// No atomics anywhere, so every result is bit-reproducible (the reference adds dQ with tl.atomic_add, :938).
+//
+// Main kernel, 384 threads:
+//   warp 0      one thread issues the TMA copies: K_j, V_j of an item (2 buffers), Q_i and dO_i of a tile (2 stages,
+//               stage = tile parity)
+//   warp 1      issues S = Q_i K_j^T and dP = dO_i V_j^T (dP goes into the columns S occupied once the scores have
+//               been read out)
+//   warp 2      issues dV += Pd^T dO_i and dK += dS^T Q_i for every tile in stream order (one issuer keeps the
+//               accumulation order fixed)
+//   warp 3      issues the dQ share dS K_j
+//   warps 4..7 / 8..11  two compute groups; group x takes the tiles of the block's tile stream with g % 2 == x, so one
+//               group's exponentials overlap the other's loads, stores and barriers. Thread t owns query row t of
+//               the tile (tensor-memory lane t). It forms P (kept as packed bf16 whose sign bit marks a dropped
+//               element), writes Pd to shared memory, then turns dP into dS in the same buffer.
+// Tensor memory (512 columns): [0,256) S / dP of the two groups, [256,384) the dQ shares of the two groups,
+// [384,448) dV, [448,512) dK.
+#include "attn_tc_dev.cuh"
+
+namespace ptj {
+namespace {
+
+using namespace attn_tc;
+
+constexpr int kThreads = 384;
+constexpr int kOffKV = 0;                                  // K[2], V[2] (item buffers)
+constexpr int kOffQG = 4 * kTileBytes;                     // per stage: Q then dO
+constexpr int kOffW = kOffQG + 4 * kTileBytes;             // per group: one [128][128] bf16 tile, Pd then dS
+constexpr int kOffBars = kOffW + 4 * kTileBytes;
+constexpr int kNumBars = 32;
+constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColDQ = 256, kColDV = 384, kColDK = 448;
+
+struct Sched {
+  int total, rounds, nq, BH;
+};
+
+// Position in the stream of (item, query tile) pairs of one thread block; every role walks the same stream.
+// Items are ordered heaviest first (KV tile 0 has the most query tiles) and dealt in boustrophedon order.
+struct Cursor {
+  int n, ord, kt, bh, i, g;
+  bool valid;
+  __device__ __forceinline__ void next_item(const Sched& s) {
+    valid = false;
+    while (++n < s.rounds) {
+      const int pos = (n & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+      const int sp = n * static_cast<int>(gridDim.x) + pos;
+      if (sp < s.total) {
+        kt = sp / s.BH;
+        bh = sp % s.BH;
+        i = kt;
+        ++ord;
+        valid = true;
+        return;
+      }
+    }
+  }
+  __device__ __forceinline__ void init(const Sched& s) {
+    n = -1; ord = -1; g = 0; kt = 0; bh = 0; i = 0;
+    next_item(s);
+  }
+  __device__ __forceinline__ bool first(const Sched&) const { return i == kt; }
+  __device__ __forceinline__ bool last(const Sched& s) const { return i == s.nq - 1; }
+  __device__ __forceinline__ void advance(const Sched& s) {
+    ++g;
+    if (i == s.nq - 1) next_item(s); else ++i;
+  }
+};
+
+// ---- 1. per-row constants ------------------------------------------------------------------------------------------
+// Eight lanes per query row: delta = sum_d dO[q,d] O[q,d]; lse2 = (row_max + log(row_sum)) * log2(e).
+__global__ void __launch_bounds__(256)
+attn_bwd_prep_kernel(const RowView d_o, const RowView o_view, const float* __restrict__ row_max,
+                     const float* __restrict__ row_sum, float* __restrict__ delta, float* __restrict__ lse2, int S, int H,
+                     int64_t rows) {
+  const int64_t r = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 3;
+  const int part = threadIdx.x & 7;
+  float acc = 0.f;
+  if (r < rows) {
+    const int64_t bh = r / S, q = r % S;
+    const __nv_bfloat16* g = d_o.row(bh / H, bh % H, q) + part * 8;
+    const __nv_bfloat16* o = o_view.row(bh / H, bh % H, q) + part * 8;
+    float x[8], y[8];
+    Elem<__nv_bfloat16>::load_vec(g, x);
+    Elem<__nv_bfloat16>::load_vec(o, y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(x[i], y[i], acc);
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (r < rows && part == 0) {
+    delta[r] = acc;
+    lse2[r] = (row_max[r] + logf(row_sum[r])) * kLog2e;
+  }
+}
+
+// ---- 3. dQ = sum of the per-KV-tile shares ---------------------------------------------------------------------------
+// part[((bh * ntri + qt (qt + 1) / 2 + kt) * 128 + row) * 64 + col]; one thread sums four columns of one row over kt.
+__global__ void __launch_bounds__(256)
+attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, int H, int nq, int64_t total_vec) {
+  const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (v >= total_vec) return;
+  const int c4 = static_cast<int>(v & 15);
+  const int64_t r = v >> 4;  // bh * S + q
+  const int64_t bh = r / S, q = r % S;
+  const int qt = static_cast<int>(q / T), row = static_cast<int>(q % T);
+  const int64_t ntri = static_cast<int64_t>(nq) * (nq + 1) / 2;
+  const float4* src = reinterpret_cast<const float4*>(part) +
+                      ((bh * ntri + static_cast<int64_t>(qt) * (qt + 1) / 2) * T + row) * (DH / 4) + c4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int kt = 0; kt <= qt; ++kt) {
+    const float4 t = __ldcs(src + static_cast<int64_t>(kt) * T * (DH / 4));
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  __nv_bfloat16* dst = dq.row(bh / H, bh % H, q) + c4 * 4;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+  uint2 pk;
+  pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+  pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = pk;
+}
+
+// ---- 2. main kernel --------------------------------------------------------------------------------------------------
+struct BwdViews {
+  RowView dk, dv;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
+                   const float* __restrict__ delta, const float* __restrict__ lse2, float* __restrict__ dq_part,
+                   const BwdViews outv, const AttnParams p, const Sched sched) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* kv_s = sm + kOffKV;  // item buffer b: K at b * 2 tiles, V right behind it
+  uint8_t* qg_s = sm + kOffQG;  // stage x: Q at x * 2 tiles, dO right behind it
+  uint8_t* w_s = sm + kOffW;    // group x: [128][128] bf16 at x * 2 tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBars);
+  uint64_t* kv_full = bars;            // [2]
+  uint64_t* kv_empty = bars + 2;       // [2] two arrivals: last dP and last dQ share of the item
+  uint64_t* qg_full = bars + 4;        // [2]
+  uint64_t* qg_empty = bars + 6;       // [2] the tile's dK MMA is done (S, dP, dV came before it)
+  uint64_t* s_full = bars + 8;         // [2] per group from here on
+  uint64_t* s_free = bars + 10;        //     scores are in registers (one arrival per warp)
+  uint64_t* dp_full = bars + 12;
+  uint64_t* dp_free = bars + 14;       //     dP is in registers (one arrival per warp)
+  uint64_t* pd_ready = bars + 16;      //     Pd is in the group's shared-memory tile (one arrival per warp)
+  uint64_t* dv_done = bars + 18;       //     the dV MMA has read it
+  uint64_t* ds_ready = bars + 20;      //     dS is in the group's shared-memory tile (one arrival per warp)
+  uint64_t* dkq_done = bars + 22;      //     two arrivals: the dK MMA and the dQ-share MMA have read it
+  uint64_t* dq_full = bars + 24;
+  uint64_t* dq_free = bars + 26;       //     the dQ share has been copied out (one arrival per warp)
+  uint64_t* acc_full = bars + 28;      // the item's last dV / dK MMAs are done
+  uint64_t* acc_free = bars + 29;      // dV / dK have been copied out (one arrival per warp of the finishing group)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const AbortCtx ctx{abort_flag, p.fault};
+
+  if (tid == 0) {
+    for (int i = 0; i < kNumBars; ++i) {
+      uint64_t* b = &bars[i];
+      const int pair = i >> 1;  // barriers come in pairs up to acc_full / acc_free
+      uint32_t count = 1;       // TMA transactions and MMA commits
+      if (b == acc_free || pair == 5 || pair == 7 || pair == 8 || pair == 10 || pair == 13) count = 4;  // compute warps
+      if (pair == 1 || pair == 11) count = 2;  // kv_empty, dkq_done: two MMA issuers
+      if (b == acc_full) count = 1;
+      mbar_init(b, count);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_g);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);  // Q K^T and dO V^T
+  constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);   // Pd^T dO and dS^T Q
+  constexpr uint32_t idesc_q = idesc_bf16_f32(T, DH, false, true);  // dS K
+
+  // the copy / MMA warps hand most of their registers to the compute warps (whole groups of four warps switch together)
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+
+  // A polling role gives up when nothing has moved for the wait limit, or when another thread already aborted.
+  auto stalled = [&](bool progress, long long& t_idle, unsigned int site) {
+    if (progress) {
+      t_idle = clock64();
+      return false;
+    }
+    if (*abort_flag) return true;
+    if (clock64() - t_idle > kWaitLimitCycles) {
+      *abort_flag = 1;
+      record_fault(p.fault, site);
+      return true;
+    }
+    return false;
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      Cursor ci, ct;  // items (K_j, V_j) and tiles (Q_i, dO_i) are two independent sequences
+      ci.init(sched);
+      ct.init(sched);
+      long long t_idle = clock64();
+      while (ci.valid || ct.valid) {
+        bool progress = false;
+        if (ci.valid) {
+          const int b = ci.ord & 1;
+          if (mbar_try_wait(&kv_empty[b], ((ci.ord >> 1) & 1) ^ 1u)) {
+            mbar_expect_tx(&kv_full[b], 2 * kTileBytes);
+            tma_load_4d(kv_s + b * 2 * kTileBytes, &tm_k, &kv_full[b], 0, ci.kt * T, ci.bh % p.H, ci.bh / p.H);
+            tma_load_4d(kv_s + b * 2 * kTileBytes + kTileBytes, &tm_v, &kv_full[b], 0, ci.kt * T, ci.bh % p.H, ci.bh / p.H);
+            ci.g += sched.nq - ci.i;  // skip the item's tiles
+            ci.next_item(sched);
+            progress = true;
+          }
+        }
+        if (ct.valid) {
+          const int x = ct.g & 1;
+          if (mbar_try_wait(&qg_empty[x], ((ct.g >> 1) & 1) ^ 1u)) {
+            mbar_expect_tx(&qg_full[x], 2 * kTileBytes);
+            tma_load_4d(qg_s + x * 2 * kTileBytes, &tm_q, &qg_full[x], 0, ct.i * T, ct.bh % p.H, ct.bh / p.H);
+            tma_load_4d(qg_s + x * 2 * kTileBytes + kTileBytes, &tm_g, &qg_full[x], 0, ct.i * T, ct.bh % p.H, ct.bh / p.H);
+            ct.advance(sched);
+            progress = true;
+          }
+        }
+        if (stalled(progress, t_idle, 0x2101u)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer: S = Q K^T, then dP = dO V^T over it
+    // (all lanes walk the streams so that addresses and descriptors stay warp-uniform; an elected lane issues)
+    Cursor cs, cd;
+    cs.init(sched);
+    cd.init(sched);
+    long long t_idle = clock64();
+    while (cs.valid || cd.valid) {
+      bool progress = false;
+      if (cs.valid) {
+        const int x = cs.g & 1;
+        const uint32_t ph = (cs.g >> 1) & 1;
+        bool ready = mbar_try_wait(&qg_full[x], ph) && mbar_try_wait(&dp_free[x], ph ^ 1u);  // dP of tile g - 2 was read
+        if (ready && cs.first(sched)) ready = mbar_try_wait(&kv_full[cs.ord & 1], (cs.ord >> 1) & 1);
+        if (__all_sync(0xffffffffu, ready)) {
+          tc_fence_after_sync();
+          const uint32_t qa = smem_u32(qg_s + x * 2 * kTileBytes), ka = smem_u32(kv_s + (cs.ord & 1) * 2 * kTileBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < DH / 16; ++k16)
+            mma_bf16_ss_elect(tmem + kColS + x * T, desc_kmajor_d(qa, k16), desc_kmajor_d(ka, k16), idesc_s, k16 > 0);
+          mma_commit_elect(&s_full[x]);
+          cs.advance(sched);
+          progress = true;
+        }
+      }
+      if (cd.valid && (!cs.valid || cd.g < cs.g)) {
+        const int x = cd.g & 1;
+        const uint32_t ph = (cd.g >> 1) & 1;
+        if (__all_sync(0xffffffffu, mbar_try_wait(&s_free[x], ph))) {
+          tc_fence_after_sync();
+          const uint32_t ga = smem_u32(qg_s + x * 2 * kTileBytes + kTileBytes);
+          const uint32_t va = smem_u32(kv_s + (cd.ord & 1) * 2 * kTileBytes + kTileBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < DH / 16; ++k16)
+            mma_bf16_ss_elect(tmem + kColS + x * T, desc_kmajor_d(ga, k16), desc_kmajor_d(va, k16), idesc_s, k16 > 0);
+          mma_commit_elect(&dp_full[x]);
+          if (cd.last(sched)) mma_commit_elect(&kv_empty[cd.ord & 1]);
+          cd.advance(sched);
+          progress = true;
+        }
+      }
+      if (__any_sync(0xffffffffu, stalled(progress, t_idle, 0x2201u))) break;
+    }
+  } else if (warp == 2) {
+    // ---------------------------------------------------------------- MMA issuer: dV += Pd^T dO and dK += dS^T Q
+    // Two sequences over the stream; each accumulates in stream order, whichever operand is ready goes first.
+    Cursor cv, ck;
+    cv.init(sched);
+    ck.init(sched);
+    long long t_idle = clock64();
+    while (cv.valid || ck.valid) {
+      bool progress = false;
+      if (cv.valid) {
+        const int x = cv.g & 1;
+        bool ready = mbar_try_wait(&pd_ready[x], (cv.g >> 1) & 1);
+        if (ready && cv.first(sched)) ready = mbar_try_wait(acc_free, (cv.ord & 1) ^ 1u);  // previous item copied out
+        if (__all_sync(0xffffffffu, ready)) {
+          tc_fence_after_sync();
+          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), ga = smem_u32(qg_s + x * 2 * kTileBytes + kTileBytes);
+          const uint32_t acc = cv.first(sched) ? 0u : 1u;
+#pragma unroll
+          for (int k16 = 0; k16 < T / 16; ++k16)
+            mma_bf16_ss_elect(tmem + kColDV, desc_p_transposed(wa, k16), desc_rows_as_k(ga, k16), idesc_t, k16 > 0 ? 1u : acc);
+          mma_commit_elect(&dv_done[x]);
+          cv.advance(sched);
+          progress = true;
+        }
+      }
+      if (ck.valid && (!cv.valid || ck.g < cv.g)) {
+        const int x = ck.g & 1;
+        if (__all_sync(0xffffffffu, mbar_try_wait(&ds_ready[x], (ck.g >> 1) & 1))) {
+          tc_fence_after_sync();
+          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), qa = smem_u32(qg_s + x * 2 * kTileBytes);
+          const uint32_t acc = ck.first(sched) ? 0u : 1u;
+#pragma unroll
+          for (int k16 = 0; k16 < T / 16; ++k16)
+            mma_bf16_ss_elect(tmem + kColDK, desc_p_transposed(wa, k16), desc_rows_as_k(qa, k16), idesc_t, k16 > 0 ? 1u : acc);
+          mma_commit_elect(&dkq_done[x]);
+          mma_commit_elect(&qg_empty[x]);
+          if (ck.last(sched)) mma_commit_elect(acc_full);
+          ck.advance(sched);
+          progress = true;
+        }
+      }
+      if (__any_sync(0xffffffffu, stalled(progress, t_idle, 0x2301u))) break;
+    }
+  } else if (warp == 3) {
+    // ---------------------------------------------------------------- MMA issuer: the tile's dQ share dS K_j
+    Cursor c;
+    c.init(sched);
+    bool ok = true;
+    while (c.valid && ok) {
+      const int x = c.g & 1;
+      const uint32_t ph = (c.g >> 1) & 1;
+      const bool w = mbar_wait(&ds_ready[x], ph, ctx, 0x2401u) && mbar_wait(&dq_free[x], ph ^ 1u, ctx, 0x2402u);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), ka = smem_u32(kv_s + (c.ord & 1) * 2 * kTileBytes);
+#pragma unroll
+      for (int k16 = 0; k16 < T / 16; ++k16)
+        mma_bf16_ss_elect(tmem + kColDQ + x * DH, desc_p_kmajor(wa, k16), desc_rows_as_k(ka, k16), idesc_q, k16 > 0);
+      mma_commit_elect(&dq_full[x]);
+      mma_commit_elect(&dkq_done[x]);
+      if (c.last(sched)) mma_commit_elect(&kv_empty[c.ord & 1]);
+      c.advance(sched);
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- compute groups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
+    const int grp = (warp - 4) >> 2;         // this group handles the stream's tiles with (g & 1) == grp
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + kColS + grp * T;     // S, then dP
+    const uint32_t t_q = tmem + lane_base + kColDQ + grp * DH;   // the tile's dQ share
+    uint8_t* w_tile = w_s + grp * 2 * kTileBytes;
+    const bool masked = p.dr.train && p.dr.thr16 != 0u;
+    const float f_keep = p.dr.train ? 1.f : p.dr.eval_scale;
+    const uint32_t thr_hi = p.dr.thr16 << 16;
+    const int ntri = p.nq * (p.nq + 1) / 2;
+
+    Cursor c;
+    c.init(sched);
+    bool ok = true;
+    int64_t pend_part = -1;  // workspace tile that takes the dQ share still sitting in tensor memory
+    int pend_g = 0;
+    auto drain_dq = [&]() {  // copy the previous own tile's dQ share (its MMA finished long ago) to the workspace
+      if (pend_part < 0) return;
+      ok = mbar_wait(&dq_full[grp], (pend_g >> 1) & 1, ctx, 0x2501u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      tc_fence_after_sync();
+      float4* dst = reinterpret_cast<float4*>(dq_part + (pend_part * T + row) * DH);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        float t[32];
+        tmem_ld_32x32f(t_q + cc * 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) __stcs(dst + cc * 8 + i, make_float4(t[4 * i], t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_free[grp]);
+      pend_part = -1;
+    };
+
+    while (c.valid && ok) {
+      if ((c.g & 1) == grp) {
+        const uint32_t ph = (c.g >> 1) & 1;
+        const int64_t q_row = static_cast<int64_t>(c.i) * T + row;
+        const int64_t ri = static_cast<int64_t>(c.bh) * p.S + q_row;
+        const float lse = lse2[ri];
+        const float dsc = delta[ri] * p.scale;  // delta / sqrt(d)
+        // dropout random words of this thread's row, one 32-column chunk ahead of their use
+        uint32_t rw[2][4][4];
+        const uint64_t call0 = ((static_cast<uint64_t>(c.bh) * p.S + q_row) * p.S + static_cast<uint64_t>(c.kt) * T) >> 3;
+        if (masked) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + q, p.dr.stream_id, rw[0][q]);
+        }
+        drain_dq();
+        if (!ok) break;
+
+        // ---- P from the scores; Pd to shared memory; P kept as packed bf16, sign bit set where dropped ----
+        ok = mbar_wait(&s_full[grp], ph, ctx, 0x2502u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        float s[4][32];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32f(t_s + cc * 32, s[cc]);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[grp]);  // dP may now overwrite the scores
+        // the group's shared-memory tile was last read by the previous own tile's dK and dQ-share MMAs
+        ok = mbar_wait(&dkq_done[grp], ph ^ 1u, ctx, 0x2503u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const bool diag = c.i == c.kt;
+        const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(-lse, -lse);
+        uint32_t pk[T / 2];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          if (masked && cc + 1 < 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + (cc + 1) * 4 + q, p.dr.stream_id, rw[(cc + 1) & 1][q]);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float a, b;
+            unpack2(fma2(pack2(s[cc][i], s[cc][i + 1]), sc2, nl2), a, b);
+            a = ex2_approx(a);
+            b = ex2_approx(b);
+            if (diag) {  // causal mask: only the diagonal tile has columns beyond the row
+              if (cc * 32 + i > row) a = 0.f;
+              if (cc * 32 + i + 1 > row) b = 0.f;
+            }
+            float sa = a, sb = b;  // signed copies: negative = dropped
+            if (masked) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
+              const uint32_t w = rw[cc & 1][i >> 3][(i & 7) >> 1];
+              if ((w << 16) < thr_hi) { sa = -a; a = 0.f; }
+              if (w < thr_hi) { sb = -b; b = 0.f; }
+            }
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(sa, sb);
+            pk[cc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h2);
+            s[cc][i] = a * f_keep;
+            s[cc][i + 1] = b * f_keep;
+          }
+          store_row32_sw128(w_tile, row, cc * 32, s[cc]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pd_ready[grp]);
+
+        // ---- dS = P o (dP o keep - delta) / sqrt(d) into the same tile, once the dV MMA has read Pd ----
+        ok = mbar_wait(&dp_full[grp], ph, ctx, 0x2504u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32f(t_s + cc * 32, s[cc]);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dp_free[grp]);  // the next own tile's scores may now overwrite dP
+        ok = mbar_wait(&dv_done[grp], ph, ctx, 0x2505u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float ksc = f_keep * p.scale;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const uint32_t w = pk[cc * 16 + (i >> 1)];
+            const float xa = __uint_as_float(w << 16), xb = __uint_as_float(w & 0xffff0000u);
+            const float da = xa < 0.f ? 0.f : s[cc][i], db = xb < 0.f ? 0.f : s[cc][i + 1];
+            s[cc][i] = fabsf(xa) * fmaf(da, ksc, -dsc);
+            s[cc][i + 1] = fabsf(xb) * fmaf(db, ksc, -dsc);
+          }
+          store_row32_sw128(w_tile, row, cc * 32, s[cc]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_ready[grp]);
+        pend_part = static_cast<int64_t>(c.bh) * ntri + c.i * (c.i + 1) / 2 + c.kt;
+        pend_g = c.g;
+
+        if (c.last(sched)) {  // the item's dV and dK are complete once the MMAs issued so far have run
+          ok = mbar_wait(acc_full, c.ord & 1, ctx, 0x2506u);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const int64_t kv_row = static_cast<int64_t>(c.kt) * T + row;
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const RowView& view = which == 0 ? outv.dv : outv.dk;
+            __nv_bfloat16* dst = view.row(c.bh / p.H, c.bh % p.H, kv_row);
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              float t[32];
+              tmem_ld_32x32f(tmem + lane_base + (which == 0 ? kColDV : kColDK) + cc * 32, t);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c8 = 0; c8 < 4; ++c8) {
+                float t8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t8[i] = t[c8 * 8 + i];
+                Elem<__nv_bfloat16>::store_vec(dst + cc * 32 + c8 * 8, t8);
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_free);
+        }
+      }
+      c.advance(sched);
+    }
+    if (ok) drain_dq();
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before shared memory is released
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+
+bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs) {
+  if (sh.d_head != DH || sh.seq % T != 0 || sh.seq < T || sh.seq > (1 << 20)) return false;
+  if (sh.batch * sh.heads * (sh.seq / T) > 0x7fffffffLL) return false;
+  for (int i = 0; i < nptrs; ++i)
+    if (!aligned16(ptrs[i])) return false;
+  const int64_t* sts[4] = {sh.q_strides, sh.k_strides, sh.v_strides, sh.o_strides};
+  for (const int64_t* st : sts) {
+    if (st[0] % 8 != 0 || st[1] % 8 != 0 || st[2] % 8 != 0 || st[2] < DH) return false;
+    if ((sh.batch > 1 && st[0] <= 0) || (sh.heads > 1 && st[1] <= 0)) return false;
+  }
+  return ptj_device_check() == PTJ_OK;
+}
+
+size_t attn_bwd_tc_workspace_bytes(const ptj_attn_shape& sh) {
+  const int64_t nq = sh.seq / T, bh = sh.batch * sh.heads;
+  const int64_t part = bh * (nq * (nq + 1) / 2) * T * DH;  // dQ shares
+  const int64_t rows = bh * sh.seq;                        // delta, lse2
+  return static_cast<size_t>(part + 2 * rows) * sizeof(float);
+}
+
+int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
+                const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
+                const ptj_attn_shape& dsh, const AttnDropout& dr, void* workspace, size_t workspace_bytes,
+                cudaStream_t st) {
+  if (workspace == nullptr || workspace_bytes < attn_bwd_tc_workspace_bytes(sh) || !aligned16(workspace))
+    return PTJ_ERR_WORKSPACE;
+  CUtensorMap tq, tk, tv, tg;
+  if (!make_map(&tq, q, sh, sh.q_strides) || !make_map(&tk, k, sh, sh.k_strides) ||
+      !make_map(&tv, v, sh, sh.v_strides) || !make_map(&tg, d_o, sh, sh.o_strides))
+    return PTJ_ERR_LAUNCH;
+  const AttnParams p = make_params(sh, dr);
+  if (p.fault == nullptr) return PTJ_ERR_DEVICE;
+  if (cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return PTJ_ERR_LAUNCH;
+  }
+  const int64_t rows = static_cast<int64_t>(p.BH) * p.S;
+  float* part = static_cast<float*>(workspace);
+  float* delta = part + static_cast<int64_t>(p.BH) * (p.nq * (p.nq + 1) / 2) * T * DH;
+  float* lse2 = delta + rows;
+  const RowView g_view = make_view(d_o, sh.o_strides), o_view = make_view(o, sh.o_strides);
+  attn_bwd_prep_kernel<<<static_cast<unsigned>((rows * 8 + 255) / 256), 256, 0, st>>>(g_view, o_view, row_max, row_sum,
+                                                                                     delta, lse2, p.S, p.H, rows);
+  PTJ_CHECK_LAUNCH();
+  Sched s;
+  s.nq = p.nq;
+  s.BH = p.BH;
+  s.total = p.nq * p.BH;
+  const int grid = s.total < kNumSMs ? s.total : kNumSMs;
+  s.rounds = (s.total + grid - 1) / grid;
+  BwdViews views{make_view(dk, dsh.k_strides), make_view(dv, dsh.v_strides)};
+  attn_bwd_ws_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, tg, delta, lse2, part, views, p, s);
+  PTJ_CHECK_LAUNCH();
+  const int64_t total_vec = rows * (DH / 4);
+  attn_dq_reduce_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, st>>>(part, make_view(dq, dsh.q_strides),
+                                                                                        p.S, p.H, p.nq, total_vec);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+}  // namespace ptj

@@ -179,7 +179,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer, scores: S_g = Q K_g^T
-    // every lane walks the stream and waits (addresses and descriptors stay warp-uniform); lane 0 issues
+    // every lane walks the stream and waits (addresses and descriptors stay warp-uniform); an elected lane issues
     constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);
     Cursor a;
     a.init(sched);
@@ -196,14 +196,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t qa = smem_u32(q_s + qb * kTileBytes), ka = smem_u32(k_s + st * kTileBytes);
-      if (lane == 0) {
+      uint64_t da[DH / 16], db[DH / 16];  // built by every lane: warp-uniform values
 #pragma unroll
-        for (int k16 = 0; k16 < DH / 16; ++k16)
-          mma_bf16_ss(tmem + sb * T, desc_kmajor_d(qa, k16), desc_kmajor_d(ka, k16), idesc_s, k16 > 0);
-        mma_commit(&s_full[sb]);
-        mma_commit(&k_empty[st]);
-        if (a.j == a.qt) mma_commit(&q_empty[qb]);
+      for (int k16 = 0; k16 < DH / 16; ++k16) {
+        da[k16] = desc_kmajor_d(qa, k16);
+        db[k16] = desc_kmajor_d(ka, k16);
       }
+      const uint32_t dst = tmem + sb * T;
+#pragma unroll
+      for (int k16 = 0; k16 < DH / 16; ++k16) mma_bf16_ss_elect(dst, da[k16], db[k16], idesc_s, k16 > 0);
+      mma_commit_elect(&s_full[sb]);
+      mma_commit_elect(&k_empty[st]);
+      if (a.j == a.qt) mma_commit_elect(&q_empty[qb]);
       a.advance(sched);
     }
   } else if (warp < 4) {
@@ -229,14 +233,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t pa = smem_u32(p_s + grp * 2 * kTileBytes), va = smem_u32(v_s + st * kTileBytes);
-        if (lane == 0) {
+        uint64_t da[T / 16], db[T / 16];  // built by every lane: warp-uniform values
 #pragma unroll
-          for (int k16 = 0; k16 < T / 16; ++k16)
-            mma_bf16_ss(tmem + kSBufs * T + grp * DH, desc_p_kmajor(pa, k16), desc_rows_as_k(va, k16), idesc_o,
-                        (k16 > 0 || !first) ? 1u : 0u);
-          mma_commit(&o_full[grp]);
-          mma_commit(&v_empty[st]);
+        for (int k16 = 0; k16 < T / 16; ++k16) {
+          da[k16] = desc_p_kmajor(pa, k16);
+          db[k16] = desc_rows_as_k(va, k16);
         }
+        const uint32_t dst = tmem + kSBufs * T + grp * DH;
+#pragma unroll
+        for (int k16 = 0; k16 < T / 16; ++k16)
+          mma_bf16_ss_elect(dst, da[k16], db[k16], idesc_o, (k16 > 0 || !first) ? 1u : 0u);
+        mma_commit_elect(&o_full[grp]);
+        mma_commit_elect(&v_empty[st]);
       }
       b.advance(sched);
     }

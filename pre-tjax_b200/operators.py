@@ -261,16 +261,36 @@ def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None):
     return m, l
 
 
-def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None):
+_ATTN_WORKSPACE = {}  # (device, stream) -> byte tensor, grown on demand
+
+
+def attn_bwd_workspace(nbytes, device):
+    """A reusable scratch buffer for attn_bwd on the current stream (contents never carry over between calls)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ATTN_WORKSPACE.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 16), device=device, dtype=torch.uint8)
+        _ATTN_WORKSPACE[key] = buf
+    return buf
+
+
+def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None, workspace=None):
+    """workspace: optional uint8 tensor of at least ptj_attn_bwd_workspace_bytes; by default one buffer per
+    (device, stream) is kept and reused."""
     B, H, N, D = q.shape
     assert d_o.stride() == o.stride(), "dO and O must share a layout"
     sh = _attn_shape(B, H, N, D, q, k, v, o.stride()[:3])
     dsh = _attn_shape(B, H, N, D, dq, dk, dv, o.stride()[:3])
     p = DROPOUT_RATE if p is None else p
+    need = int(_lib.lib().ptj_attn_bwd_workspace_bytes(ctypes.byref(sh), _dt(q)))
+    if workspace is None and need > 0:
+        workspace = attn_bwd_workspace(need, q.device)
+    wptr = _ptr(workspace) if workspace is not None else None
+    wbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
     _lib.check(
         _lib.lib().ptj_attn_bwd(_ptr(d_o), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(m), _ptr(l), _ptr(dq), _ptr(dk),
                                 _ptr(dv), ctypes.byref(sh), ctypes.byref(dsh), p, int(bool(train)), _seed(seed),
-                                stream_id, _dt(q), _stream()), "ptj_attn_bwd")
+                                stream_id, wptr, wbytes, _dt(q), _stream()), "ptj_attn_bwd")
 
 
 def t_scaled_dot_prod_attn_fwd3_t(qkv: torch.Tensor, mask: torch.Tensor = None, train=True, p_gen_aux=None):
