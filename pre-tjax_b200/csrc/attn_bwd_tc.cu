@@ -12,8 +12,7 @@
 // No atomics anywhere, so every result is bit-reproducible (the reference adds dQ with tl.atomic_add, :938).
 //
 // Main kernel, 384 threads:
-//   warp 0      one thread issues the TMA copies: K_j, V_j of an item (2 buffers), Q_i and dO_i of a tile (2 stages,
-//               stage = tile parity)
+//   warp 0      one thread issues the TMA copies: K_j, V_j of an item (2 buffers), Q_i and dO_i of a tile (3 stages)
 //   warp 1      issues S = Q_i K_j^T and dP = dO_i V_j^T (dP goes into the columns S occupied once the scores have
 //               been read out)
 //   warp 2      issues dV += Pd^T dO_i and dK += dS^T Q_i for every tile in stream order (one issuer keeps the
@@ -34,16 +33,18 @@ using namespace attn_tc;
 
 constexpr int kThreads = 384;
 constexpr int kOffKV = 0;                                  // K[2], V[2] (item buffers)
+constexpr int kQGStages = 3;
 constexpr int kOffQG = 4 * kTileBytes;                     // per stage: Q then dO
-constexpr int kOffW = kOffQG + 4 * kTileBytes;             // per group: one [128][128] bf16 tile, Pd then dS
+constexpr int kOffW = kOffQG + kQGStages * 2 * kTileBytes; // per group: one [128][128] bf16 tile, Pd then dS
 constexpr int kOffBars = kOffW + 4 * kTileBytes;
 constexpr int kNumBars = 32;
-constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;
+constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 1024;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColDQ = 256, kColDV = 384, kColDK = 448;
 
 struct Sched {
   int total, rounds, nq, BH;
+  uint32_t bh_magic;  // ceil(2^32 / BH): x / BH == umulhi(x, bh_magic) for every x the kernel meets (checked on the host)
 };
 
 // Position in the stream of (item, query tile) pairs of one thread block; every role walks the same stream.
@@ -57,8 +58,8 @@ struct Cursor {
       const int pos = (n & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
       const int sp = n * static_cast<int>(gridDim.x) + pos;
       if (sp < s.total) {
-        kt = sp / s.BH;
-        bh = sp % s.BH;
+        kt = s.BH == 1 ? sp : static_cast<int>(__umulhi(static_cast<uint32_t>(sp), s.bh_magic));  // sp / BH
+        bh = sp - kt * s.BH;
         i = kt;
         ++ord;
         valid = true;
@@ -107,18 +108,22 @@ attn_bwd_prep_kernel(const RowView d_o, const RowView o_view, const float* __res
 }
 
 // ---- 3. dQ = sum of the per-KV-tile shares ---------------------------------------------------------------------------
-// part[((bh * ntri + qt (qt + 1) / 2 + kt) * 128 + row) * 64 + col]; one thread sums four columns of one row over kt.
+// A share is stored as 16 blocks of four columns, 128 rows each (a warp of the main kernel writes 512 contiguous
+// bytes per store): float4 index ((bh * ntri + qt (qt + 1) / 2 + kt) * 16 + c4) * 128 + row. One thread sums one
+// float4 over kt; consecutive threads take consecutive rows.
 __global__ void __launch_bounds__(256)
 attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, int H, int nq, int64_t total_vec) {
   const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (v >= total_vec) return;
-  const int c4 = static_cast<int>(v & 15);
-  const int64_t r = v >> 4;  // bh * S + q
-  const int64_t bh = r / S, q = r % S;
-  const int qt = static_cast<int>(q / T), row = static_cast<int>(q % T);
+  const int row = static_cast<int>(v % T);
+  const int c4 = static_cast<int>((v / T) % (DH / 4));
+  const int64_t tile_id = v / (T * (DH / 4));  // bh * nq + qt
+  const int64_t bh = tile_id / nq;
+  const int qt = static_cast<int>(tile_id % nq);
+  const int64_t q = static_cast<int64_t>(qt) * T + row;
   const int64_t ntri = static_cast<int64_t>(nq) * (nq + 1) / 2;
   const float4* src = reinterpret_cast<const float4*>(part) +
-                      ((bh * ntri + static_cast<int64_t>(qt) * (qt + 1) / 2) * T + row) * (DH / 4) + c4;
+                      ((bh * ntri + static_cast<int64_t>(qt) * (qt + 1) / 2) * (DH / 4) + c4) * T + row;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int kt = 0; kt <= qt; ++kt) {
     const float4 t = __ldcs(src + static_cast<int64_t>(kt) * T * (DH / 4));
@@ -132,11 +137,57 @@ attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, i
   *reinterpret_cast<uint2*>(dst) = pk;
 }
 
+// ---- per-thread phases of the main kernel: straight-line code (no branch inside the unrolled loops) ------------------
+// P phase of one 32-column chunk: s holds the raw scores on entry (-inf where the causal mask applies) and Pd (what
+// goes to shared memory) on exit;
+// pk receives P as packed bf16 pairs whose sign bit marks a dropped element. rw: the four Philox calls of the chunk.
+template <bool MASKED>
+__device__ __forceinline__ void p_chunk(float (&s)[32], uint32_t* pk, const uint32_t (&rw)[4][4], uint64_t sc2, uint64_t nl2,
+                                        uint32_t thr_hi, float f_keep) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float a, b;
+    unpack2(fma2(pack2(s[i], s[i + 1]), sc2, nl2), a, b);
+    a = ex2_approx(a);
+    b = ex2_approx(b);
+    float sa = a, sb = b;
+    if (MASKED) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
+      const uint32_t w = rw[i >> 3][(i & 7) >> 1];
+      const bool drop_a = (w << 16) < thr_hi, drop_b = w < thr_hi;
+      sa = drop_a ? -a : a;
+      sb = drop_b ? -b : b;
+      a = drop_a ? 0.f : a;
+      b = drop_b ? 0.f : b;
+    }
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(sa, sb);
+    pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+    s[i] = a * f_keep;
+    s[i + 1] = b * f_keep;
+  }
+}
+// dS phase of one chunk: s holds dP on entry and dS = P o (dP o keep * f_keep - delta) / sqrt(d) on exit.
+template <bool MASKED>
+__device__ __forceinline__ void ds_chunk(float (&s)[32], const uint32_t* pk, float ksc, float dsc) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const uint32_t w = pk[i >> 1];
+    const float xa = __uint_as_float(w << 16), xb = __uint_as_float(w & 0xffff0000u);
+    float da = s[i], db = s[i + 1];
+    if (MASKED) {
+      da = xa < 0.f ? 0.f : da;
+      db = xb < 0.f ? 0.f : db;
+    }
+    s[i] = fabsf(xa) * fmaf(da, ksc, -dsc);
+    s[i + 1] = fabsf(xb) * fmaf(db, ksc, -dsc);
+  }
+}
+
 // ---- 2. main kernel --------------------------------------------------------------------------------------------------
 struct BwdViews {
   RowView dk, dv;
 };
 
+template <bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
@@ -150,22 +201,23 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBars);
   uint64_t* kv_full = bars;            // [2]
   uint64_t* kv_empty = bars + 2;       // [2] two arrivals: last dP and last dQ share of the item
-  uint64_t* qg_full = bars + 4;        // [2]
-  uint64_t* qg_empty = bars + 6;       // [2] the tile's dK MMA is done (S, dP, dV came before it)
-  uint64_t* s_full = bars + 8;         // [2] per group from here on
-  uint64_t* s_free = bars + 10;        //     scores are in registers (one arrival per warp)
-  uint64_t* dp_full = bars + 12;
-  uint64_t* dp_free = bars + 14;       //     dP is in registers (one arrival per warp)
-  uint64_t* pd_ready = bars + 16;      //     Pd is in the group's shared-memory tile (one arrival per warp)
-  uint64_t* dv_done = bars + 18;       //     the dV MMA has read it
-  uint64_t* ds_ready = bars + 20;      //     dS is in the group's shared-memory tile (one arrival per warp)
-  uint64_t* dkq_done = bars + 22;      //     two arrivals: the dK MMA and the dQ-share MMA have read it
-  uint64_t* dq_full = bars + 24;
-  uint64_t* dq_free = bars + 26;       //     the dQ share has been copied out (one arrival per warp)
-  uint64_t* acc_full = bars + 28;      // the item's last dV / dK MMAs are done
-  uint64_t* acc_free = bars + 29;      // dV / dK have been copied out (one arrival per warp of the finishing group)
+  uint64_t* s_full = bars + 4;         // [2] per group from here on
+  uint64_t* s_free = bars + 6;         //     scores are in registers (one arrival per warp)
+  uint64_t* dp_full = bars + 8;
+  uint64_t* dp_free = bars + 10;       //     dP is in registers (one arrival per warp)
+  uint64_t* pd_ready = bars + 12;      //     Pd is in the group's shared-memory tile (one arrival per warp)
+  uint64_t* dv_done = bars + 14;       //     the dV MMA has read it
+  uint64_t* ds_ready = bars + 16;      //     dS is in the group's shared-memory tile (one arrival per warp)
+  uint64_t* dkq_done = bars + 18;      //     two arrivals: the dK MMA and the dQ-share MMA have read it
+  uint64_t* dq_full = bars + 20;
+  uint64_t* dq_free = bars + 22;       //     the dQ share has been copied out (one arrival per warp)
+  uint64_t* acc_full = bars + 24;      // the item's last dV / dK MMAs are done
+  uint64_t* acc_free = bars + 25;      // dV / dK have been copied out (one arrival per warp of the finishing group)
+  uint64_t* qg_full = bars + 26;       // [kQGStages]
+  uint64_t* qg_empty = bars + 29;      // [kQGStages] the tile's dK MMA is done (S, dP, dV came before it)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* rk_s = tmem_slot + 2;  // Philox round keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const AbortCtx ctx{abort_flag, p.fault};
@@ -173,14 +225,14 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (tid == 0) {
     for (int i = 0; i < kNumBars; ++i) {
       uint64_t* b = &bars[i];
-      const int pair = i >> 1;  // barriers come in pairs up to acc_full / acc_free
+      const int pair = i >> 1;  // the per-group barriers come in pairs
       uint32_t count = 1;       // TMA transactions and MMA commits
-      if (b == acc_free || pair == 5 || pair == 7 || pair == 8 || pair == 10 || pair == 13) count = 4;  // compute warps
-      if (pair == 1 || pair == 11) count = 2;  // kv_empty, dkq_done: two MMA issuers
-      if (b == acc_full) count = 1;
+      if (b == acc_free || pair == 3 || pair == 5 || pair == 6 || pair == 8 || pair == 11) count = 4;  // compute warps
+      if (pair == 1 || pair == 9) count = 2;  // kv_empty, dkq_done: two MMA issuers
       mbar_init(b, count);
     }
     *abort_flag = 0;
+    for (int i = 0; i < 20; ++i) rk_s[i] = p.rk[i];
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
@@ -238,8 +290,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
         if (ct.valid) {
-          const int x = ct.g & 1;
-          if (mbar_try_wait(&qg_empty[x], ((ct.g >> 1) & 1) ^ 1u)) {
+          const int x = ct.g % kQGStages;
+          if (mbar_try_wait(&qg_empty[x], ((ct.g / kQGStages) & 1) ^ 1u)) {
             mbar_expect_tx(&qg_full[x], 2 * kTileBytes);
             tma_load_4d(qg_s + x * 2 * kTileBytes, &tm_q, &qg_full[x], 0, ct.i * T, ct.bh % p.H, ct.bh / p.H);
             tma_load_4d(qg_s + x * 2 * kTileBytes + kTileBytes, &tm_g, &qg_full[x], 0, ct.i * T, ct.bh % p.H, ct.bh / p.H);
@@ -260,13 +312,14 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     while (cs.valid || cd.valid) {
       bool progress = false;
       if (cs.valid) {
-        const int x = cs.g & 1;
+        const int x = cs.g & 1, st = cs.g % kQGStages;
         const uint32_t ph = (cs.g >> 1) & 1;
-        bool ready = mbar_try_wait(&qg_full[x], ph) && mbar_try_wait(&dp_free[x], ph ^ 1u);  // dP of tile g - 2 was read
+        bool ready = mbar_try_wait(&qg_full[st], (cs.g / kQGStages) & 1) &&
+                     mbar_try_wait(&dp_free[x], ph ^ 1u);  // dP of tile g - 2 was read
         if (ready && cs.first(sched)) ready = mbar_try_wait(&kv_full[cs.ord & 1], (cs.ord >> 1) & 1);
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after_sync();
-          const uint32_t qa = smem_u32(qg_s + x * 2 * kTileBytes), ka = smem_u32(kv_s + (cs.ord & 1) * 2 * kTileBytes);
+          const uint32_t qa = smem_u32(qg_s + st * 2 * kTileBytes), ka = smem_u32(kv_s + (cs.ord & 1) * 2 * kTileBytes);
 #pragma unroll
           for (int k16 = 0; k16 < DH / 16; ++k16)
             mma_bf16_ss_elect(tmem + kColS + x * T, desc_kmajor_d(qa, k16), desc_kmajor_d(ka, k16), idesc_s, k16 > 0);
@@ -280,7 +333,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t ph = (cd.g >> 1) & 1;
         if (__all_sync(0xffffffffu, mbar_try_wait(&s_free[x], ph))) {
           tc_fence_after_sync();
-          const uint32_t ga = smem_u32(qg_s + x * 2 * kTileBytes + kTileBytes);
+          const uint32_t ga = smem_u32(qg_s + (cd.g % kQGStages) * 2 * kTileBytes + kTileBytes);
           const uint32_t va = smem_u32(kv_s + (cd.ord & 1) * 2 * kTileBytes + kTileBytes);
 #pragma unroll
           for (int k16 = 0; k16 < DH / 16; ++k16)
@@ -308,7 +361,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (ready && cv.first(sched)) ready = mbar_try_wait(acc_free, (cv.ord & 1) ^ 1u);  // previous item copied out
         if (__all_sync(0xffffffffu, ready)) {
           tc_fence_after_sync();
-          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), ga = smem_u32(qg_s + x * 2 * kTileBytes + kTileBytes);
+          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes);
+          const uint32_t ga = smem_u32(qg_s + (cv.g % kQGStages) * 2 * kTileBytes + kTileBytes);
           const uint32_t acc = cv.first(sched) ? 0u : 1u;
 #pragma unroll
           for (int k16 = 0; k16 < T / 16; ++k16)
@@ -322,13 +376,13 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int x = ck.g & 1;
         if (__all_sync(0xffffffffu, mbar_try_wait(&ds_ready[x], (ck.g >> 1) & 1))) {
           tc_fence_after_sync();
-          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), qa = smem_u32(qg_s + x * 2 * kTileBytes);
+          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), qa = smem_u32(qg_s + (ck.g % kQGStages) * 2 * kTileBytes);
           const uint32_t acc = ck.first(sched) ? 0u : 1u;
 #pragma unroll
           for (int k16 = 0; k16 < T / 16; ++k16)
             mma_bf16_ss_elect(tmem + kColDK, desc_p_transposed(wa, k16), desc_rows_as_k(qa, k16), idesc_t, k16 > 0 ? 1u : acc);
           mma_commit_elect(&dkq_done[x]);
-          mma_commit_elect(&qg_empty[x]);
+          mma_commit_elect(&qg_empty[ck.g % kQGStages]);
           if (ck.last(sched)) mma_commit_elect(acc_full);
           ck.advance(sched);
           progress = true;
@@ -367,7 +421,6 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t t_s = tmem + lane_base + kColS + grp * T;     // S, then dP
     const uint32_t t_q = tmem + lane_base + kColDQ + grp * DH;   // the tile's dQ share
     uint8_t* w_tile = w_s + grp * 2 * kTileBytes;
-    const bool masked = p.dr.train && p.dr.thr16 != 0u;
     const float f_keep = p.dr.train ? 1.f : p.dr.eval_scale;
     const uint32_t thr_hi = p.dr.thr16 << 16;
     const int ntri = p.nq * (p.nq + 1) / 2;
@@ -383,14 +436,15 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) return;
       tc_fence_after_sync();
-      float4* dst = reinterpret_cast<float4*>(dq_part + (pend_part * T + row) * DH);
+      float4* dst = reinterpret_cast<float4*>(dq_part) + pend_part * (T * DH / 4) + row;  // [16 column blocks][128 rows]
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         float t[32];
         tmem_ld_32x32f(t_q + cc * 32, t);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) __stcs(dst + cc * 8 + i, make_float4(t[4 * i], t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]));
+        for (int i = 0; i < 8; ++i)
+          __stcs(dst + (cc * 8 + i) * T, make_float4(t[4 * i], t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]));
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -408,13 +462,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // dropout random words of this thread's row, one 32-column chunk ahead of their use
         uint32_t rw[2][4][4];
         const uint64_t call0 = ((static_cast<uint64_t>(c.bh) * p.S + q_row) * p.S + static_cast<uint64_t>(c.kt) * T) >> 3;
-        if (masked) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + q, p.dr.stream_id, rw[0][q]);
-        }
-        drain_dq();
-        if (!ok) break;
-
+        if (MASKED) philox_rolled<4>(rk_s, call0, p.dr.stream_id, rw[0]);
         // ---- P from the scores; Pd to shared memory; P kept as packed bf16, sign bit set where dropped ----
         ok = mbar_wait(&s_full[grp], ph, ctx, 0x2502u);
         ok = __all_sync(0xffffffffu, ok);
@@ -431,42 +479,27 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = mbar_wait(&dkq_done[grp], ph ^ 1u, ctx, 0x2503u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const bool diag = c.i == c.kt;
+        if (c.i == c.kt) {  // causal mask: only the diagonal tile (an item's first) has columns beyond the row
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cc * 32 + i > row) s[cc][i] = -INFINITY;
+        }
         const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(-lse, -lse);
         uint32_t pk[T / 2];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          if (masked && cc + 1 < 4) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + (cc + 1) * 4 + q, p.dr.stream_id, rw[(cc + 1) & 1][q]);
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float a, b;
-            unpack2(fma2(pack2(s[cc][i], s[cc][i + 1]), sc2, nl2), a, b);
-            a = ex2_approx(a);
-            b = ex2_approx(b);
-            if (diag) {  // causal mask: only the diagonal tile has columns beyond the row
-              if (cc * 32 + i > row) a = 0.f;
-              if (cc * 32 + i + 1 > row) b = 0.f;
-            }
-            float sa = a, sb = b;  // signed copies: negative = dropped
-            if (masked) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
-              const uint32_t w = rw[cc & 1][i >> 3][(i & 7) >> 1];
-              if ((w << 16) < thr_hi) { sa = -a; a = 0.f; }
-              if (w < thr_hi) { sb = -b; b = 0.f; }
-            }
-            const __nv_bfloat162 h2 = __floats2bfloat162_rn(sa, sb);
-            pk[cc * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h2);
-            s[cc][i] = a * f_keep;
-            s[cc][i + 1] = b * f_keep;
-          }
+          if (MASKED && cc + 1 < 4) philox_rolled<4>(rk_s, call0 + (cc + 1) * 4, p.dr.stream_id, rw[(cc + 1) & 1]);
+          p_chunk<MASKED>(s[cc], pk + cc * 16, rw[cc & 1], sc2, nl2, thr_hi, f_keep);
           store_row32_sw128(w_tile, row, cc * 32, s[cc]);
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pd_ready[grp]);
+        drain_dq();  // the previous own tile's dQ share: its MMA has long finished by now
+        if (!ok) break;
 
         // ---- dS = P o (dP o keep - delta) / sqrt(d) into the same tile, once the dV MMA has read Pd ----
         ok = mbar_wait(&dp_full[grp], ph, ctx, 0x2504u);
@@ -485,14 +518,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float ksc = f_keep * p.scale;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const uint32_t w = pk[cc * 16 + (i >> 1)];
-            const float xa = __uint_as_float(w << 16), xb = __uint_as_float(w & 0xffff0000u);
-            const float da = xa < 0.f ? 0.f : s[cc][i], db = xb < 0.f ? 0.f : s[cc][i + 1];
-            s[cc][i] = fabsf(xa) * fmaf(da, ksc, -dsc);
-            s[cc][i + 1] = fabsf(xb) * fmaf(db, ksc, -dsc);
-          }
+          ds_chunk<MASKED>(s[cc], pk + cc * 16, ksc, dsc);
           store_row32_sw128(w_tile, row, cc * 32, s[cc]);
         }
         fence_proxy_async_smem();
@@ -553,7 +579,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs) {
   if (sh.d_head != DH || sh.seq % T != 0 || sh.seq < T || sh.seq > (1 << 20)) return false;
-  if (sh.batch * sh.heads * (sh.seq / T) > 0x7fffffffLL) return false;
+  const int64_t bh = sh.batch * sh.heads, items = bh * (sh.seq / T);
+  if (items * bh >= (1LL << 32)) return false;  // exactness bound of the kernels' reciprocal division by bh
   for (int i = 0; i < nptrs; ++i)
     if (!aligned16(ptrs[i])) return false;
   const int64_t* sts[4] = {sh.q_strides, sh.k_strides, sh.v_strides, sh.o_strides};
@@ -583,7 +610,9 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
     return PTJ_ERR_LAUNCH;
   const AttnParams p = make_params(sh, dr);
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
-  if (cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+  const bool masked = dr.train && dr.thr16 != 0u;
+  auto kern = masked ? attn_bwd_ws_kernel<true> : attn_bwd_ws_kernel<false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
@@ -601,8 +630,9 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
   s.total = p.nq * p.BH;
   const int grid = s.total < kNumSMs ? s.total : kNumSMs;
   s.rounds = (s.total + grid - 1) / grid;
+  s.bh_magic = static_cast<uint32_t>(((1ull << 32) + s.BH - 1) / s.BH);
   BwdViews views{make_view(dk, dsh.k_strides), make_view(dv, dsh.v_strides)};
-  attn_bwd_ws_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, tg, delta, lse2, part, views, p, s);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, tg, delta, lse2, part, views, p, s);
   PTJ_CHECK_LAUNCH();
   const int64_t total_vec = rows * (DH / 4);
   attn_dq_reduce_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, st>>>(part, make_view(dq, dsh.q_strides),

@@ -37,6 +37,7 @@ constexpr int kTmemCols = 512;
 
 struct Sched {
   int total, rounds, nq, BH;
+  uint32_t bh_magic;  // ceil(2^32 / BH): x / BH == umulhi(x, bh_magic) for every x the kernel meets (checked on the host)
 };
 
 // Position in the stream of (item, kv tile) pairs of one thread block; every role walks the same stream.
@@ -49,8 +50,9 @@ struct Cursor {
       const int pos = (n & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
       const int sp = n * static_cast<int>(gridDim.x) + pos;
       if (sp < s.total) {
-        qt = s.nq - 1 - sp / s.BH;
-        bh = sp % s.BH;
+        const int t = s.BH == 1 ? sp : static_cast<int>(__umulhi(static_cast<uint32_t>(sp), s.bh_magic));  // sp / BH
+        qt = s.nq - 1 - t;
+        bh = sp - t * s.BH;
         j = 0;
         ++ord;
         valid = true;
@@ -486,6 +488,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row
   s.total = p.nq * p.BH;
   const int grid = s.total < kNumSMs ? s.total : kNumSMs;
   s.rounds = (s.total + grid - 1) / grid;
+  s.bh_magic = static_cast<uint32_t>(((1ull << 32) + s.BH - 1) / s.BH);
   attn_fwd_ws_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p, s);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;

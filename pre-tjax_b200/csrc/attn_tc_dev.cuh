@@ -89,6 +89,40 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// NCALL consecutive counters at once, rounds in a rolled loop (small code, the calls give the instruction-level
+// parallelism), round keys read from shared memory (rk_s[2r], rk_s[2r+1]).
+template <int NCALL>
+__device__ __forceinline__ void philox_rolled(const uint32_t* rk_s, uint64_t ctr0, uint32_t stream_id, uint32_t (&out)[NCALL][4]) {
+  uint32_t c0[NCALL], c1[NCALL], c2[NCALL], c3[NCALL];
+#pragma unroll
+  for (int q = 0; q < NCALL; ++q) {
+    const uint64_t ctr = ctr0 + q;
+    c0[q] = static_cast<uint32_t>(ctr);
+    c1[q] = static_cast<uint32_t>(ctr >> 32);
+    c2[q] = stream_id;
+    c3[q] = 0x5054'4a31u;
+  }
+#pragma unroll 1
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t k0 = rk_s[2 * r], k1 = rk_s[2 * r + 1];
+#pragma unroll
+    for (int q = 0; q < NCALL; ++q) {
+      const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c0[q];
+      const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c2[q];
+      const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c1[q] ^ k0;
+      const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c3[q] ^ k1;
+      c1[q] = static_cast<uint32_t>(p1);
+      c3[q] = static_cast<uint32_t>(p0);
+      c0[q] = n0;
+      c2[q] = n2;
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < NCALL; ++q) {
+    out[q][0] = c0[q]; out[q][1] = c1[q]; out[q][2] = c2[q]; out[q][3] = c3[q];
+  }
+}
+
 // packed pairs of floats for the two-wide fp32 instructions of sm_100 (fma.rn.f32x2, add.f32x2)
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
