@@ -134,18 +134,39 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
   }
   const float inv_n = 1.f / static_cast<float>(dim), inv_nm1 = 1.f / static_cast<float>(dim - 1);
   const float n_adj = static_cast<float>(dim) * inv_nm1;
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp; row < rows;
-       row += static_cast<int64_t>(gridDim.x) * kLnWarps) {
+  // every lane always owns the same columns: its slice of gamma stays in registers for all rows
+  float gmr[NV][V];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + 32 * i;
+    if (vi < nvec) {
+      load_params<V>(gamma + vi * V, gmr[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) gmr[i][j] = 0.f;
+    }
+  }
+  const int64_t row_step = static_cast<int64_t>(gridDim.x) * kLnWarps;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp; row < rows; row += row_step) {
     const T* xr = x + row * dim;
     const T* gr = dy + row * dim;
-    float v[NV][V], u[NV][V];
+    float v[NV][V], u[NV][V], r[NV][V];
     float s = 0.f;
+    // all of the row's loads go out together (the residual-path gradient included), and the next row of this warp is
+    // pulled into L2 while this one is being processed
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + 32 * i;
       if (vi < nvec) {
         Elem<T>::load_vec(xr + vi * V, v[i]);
         Elem<T>::load_vec(gr + vi * V, u[i]);
+        if (dx_add != nullptr) Elem<T>::load_vec(dx_add + row * dim + vi * V, r[i]);
+        if (row + row_step < rows) {
+          const int64_t nxt = (row + row_step) * dim + vi * V;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x + nxt));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + nxt));
+          if (dx_add != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(dx_add + nxt));
+        }
 #pragma unroll
         for (int j = 0; j < V; ++j) s += v[i][j];
       } else {
@@ -172,8 +193,6 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + 32 * i;
       if (vi < nvec) {
-        float gm[V];
-        load_params<V>(gamma + vi * V, gm);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = (v[i][j] - mean) * rstd;
@@ -183,7 +202,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
             acc_g[slot] += u[i][j] * xh;
             acc_b[slot] += u[i][j];
           }
-          const float gh = u[i][j] * gm[j];
+          const float gh = u[i][j] * gmr[i][j];
           u[i][j] = gh;
           s1 += gh;
           s2 += gh * xh;
@@ -202,10 +221,8 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
 #pragma unroll
           for (int j = 0; j < V; ++j) o[j] = (u[i][j] - m1 - v[i][j] * m2) * rstd;
           if (dx_add != nullptr) {  // gradient arriving over the residual connection
-            float r[V];
-            Elem<T>::load_vec(dx_add + row * dim + vi * V, r);
 #pragma unroll
-            for (int j = 0; j < V; ++j) o[j] += r[j];
+            for (int j = 0; j < V; ++j) o[j] += r[i][j];
           }
           Elem<T>::store_vec(dr + vi * V, o);
         }
@@ -277,18 +294,19 @@ ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
                        int nblocks, int dim) {
-  __shared__ float red[8][33];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + lane;
+  // 8 columns x 32 row groups per block: many small blocks, each row group sums every 32nd partial row in order
+  __shared__ float red[32][9];
+  const int col = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  const int c = blockIdx.x * 8 + col;
   float s = 0.f;
   if (c < 2 * dim)
-    for (int b = warp; b < nblocks; b += 8) s += partial[static_cast<size_t>(b) * 2 * dim + c];
-  red[warp][lane] = s;
+    for (int b = grp; b < nblocks; b += 32) s += partial[static_cast<size_t>(b) * 2 * dim + c];
+  red[grp][col] = s;
   __syncthreads();
-  if (warp == 0 && c < 2 * dim) {
+  if (grp == 0 && c < 2 * dim) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    for (int w = 0; w < 32; ++w) t += red[w][col];
     if (c < dim) dgamma[c] = t; else dbeta[c - dim] = t;
   }
 }
@@ -336,7 +354,7 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
 #undef PTJ_LN_BWD
   PTJ_CHECK_LAUNCH();
   if (partial != nullptr) {
-    ln_bwd_finalize_kernel<<<static_cast<int>(ceil_div(2 * dim, 32)), 256, 0, st>>>(partial, dgamma, dbeta, grid, dim);
+    ln_bwd_finalize_kernel<<<static_cast<int>(ceil_div(2 * dim, 8)), 256, 0, st>>>(partial, dgamma, dbeta, grid, dim);
     PTJ_CHECK_LAUNCH();
   }
   return PTJ_OK;
