@@ -191,9 +191,18 @@ typedef struct {
   int64_t batch, heads, seq, d_head;
   int64_t q_strides[3], k_strides[3], v_strides[3], o_strides[3]; /* batch, head, row (elements) */
 } ptj_attn_shape;
+/* Optional: the dropout keep flags of one attention call (probability tensor [B*H, S, S], mask stream of site
+ * (seed, stream_id)), computed once and handed to both ptj_attn_fwd and ptj_attn_bwd as `keep_bits`; the kernels then
+ * skip their own Philox pass. The flags are the same ones the kernels draw when keep_bits == NULL, so results are
+ * bit-identical either way (the reference regenerates its mask in the backward kernel, model_triton.py:688).
+ * ptj_attn_keep_bits_bytes: size of the buffer (16-byte aligned), 0 when the shape / dtype does not take the
+ * tensor-core path (then pass NULL). */
+size_t ptj_attn_keep_bits_bytes(const ptj_attn_shape* shape, int dtype);
+int ptj_attn_keep_bits(uint32_t* bits, const ptj_attn_shape* shape, float p, uint64_t seed, uint32_t stream_id,
+                       int dtype, void* stream);
 int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
                  const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
-                 int dtype, void* stream);
+                 const uint32_t* keep_bits, int dtype, void* stream);
 /* dq/dk/dv use q/k/v strides of `dshape`; d_o and o use o_strides of `shape`.
  * workspace: ptj_attn_bwd_workspace_bytes(shape, dtype) bytes of device memory, 16-byte aligned, contents
  * irrelevant before and after the call (the tensor-core path keeps each KV tile's share of dQ there in fp32 and sums
@@ -203,8 +212,8 @@ size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int dtype);
 int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                  const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
                  const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
-                 uint64_t seed, uint32_t stream_id, void* workspace, size_t workspace_bytes, int dtype,
-                 void* stream);
+                 uint64_t seed, uint32_t stream_id, const uint32_t* keep_bits, void* workspace,
+                 size_t workspace_bytes, int dtype, void* stream);
 
 /* ---- optimizer -------------------------------------------------------------------------------------- */
 /* sum of squares of a float vector -> out[0] (deterministic two-stage). Replaces grads_l2norm

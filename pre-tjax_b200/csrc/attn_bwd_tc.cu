@@ -141,9 +141,10 @@ attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, i
 // P phase of one 32-column chunk: s holds the raw scores on entry (-inf where the causal mask applies) and Pd (what
 // goes to shared memory) on exit;
 // pk receives P as packed bf16 pairs whose sign bit marks a dropped element. rw: the four Philox calls of the chunk.
-template <bool MASKED>
-__device__ __forceinline__ void p_chunk(float (&s)[32], uint32_t* pk, const uint32_t (&rw)[4][4], uint64_t sc2, uint64_t nl2,
-                                        uint32_t thr_hi, float f_keep) {
+// MODE 0: no mask; 1: raw Philox words in rw; 2: precomputed keep flags of the chunk in keepw (bit i = column i).
+template <int MODE>
+__device__ __forceinline__ void p_chunk(float (&s)[32], uint32_t* pk, const uint32_t (&rw)[4][4], uint32_t keepw,
+                                        uint64_t sc2, uint64_t nl2, uint32_t thr_hi, float f_keep) {
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float a, b;
@@ -151,9 +152,16 @@ __device__ __forceinline__ void p_chunk(float (&s)[32], uint32_t* pk, const uint
     a = ex2_approx(a);
     b = ex2_approx(b);
     float sa = a, sb = b;
-    if (MASKED) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
-      const uint32_t w = rw[i >> 3][(i & 7) >> 1];
-      const bool drop_a = (w << 16) < thr_hi, drop_b = w < thr_hi;
+    if (MODE != 0) {
+      bool drop_a, drop_b;
+      if (MODE == 1) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
+        const uint32_t w = rw[i >> 3][(i & 7) >> 1];
+        drop_a = (w << 16) < thr_hi;
+        drop_b = w < thr_hi;
+      } else {
+        drop_a = (keepw & (1u << i)) == 0u;
+        drop_b = (keepw & (2u << i)) == 0u;
+      }
       sa = drop_a ? -a : a;
       sb = drop_b ? -b : b;
       a = drop_a ? 0.f : a;
@@ -187,7 +195,7 @@ struct BwdViews {
   RowView dk, dv;
 };
 
-template <bool MASKED>
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
@@ -462,7 +470,11 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // dropout random words of this thread's row, one 32-column chunk ahead of their use
         uint32_t rw[2][4][4];
         const uint64_t call0 = ((static_cast<uint64_t>(c.bh) * p.S + q_row) * p.S + static_cast<uint64_t>(c.kt) * T) >> 3;
-        if (MASKED) philox_rolled<4>(rk_s, call0, p.dr.stream_id, rw[0]);
+        if (MODE == 1) philox_rolled<4>(rk_s, call0, p.dr.stream_id, rw[0]);
+        uint4 kb = make_uint4(0u, 0u, 0u, 0u);
+        if (MODE == 2)
+          kb = __ldg(p.keep_bits + (static_cast<int64_t>(c.bh) * ntri + c.i * (c.i + 1) / 2 + c.kt) * T + row);
+        const uint32_t keepw[4] = {kb.x, kb.y, kb.z, kb.w};
         // ---- P from the scores; Pd to shared memory; P kept as packed bf16, sign bit set where dropped ----
         ok = mbar_wait(&s_full[grp], ph, ctx, 0x2502u);
         ok = __all_sync(0xffffffffu, ok);
@@ -490,8 +502,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         uint32_t pk[T / 2];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          if (MASKED && cc + 1 < 4) philox_rolled<4>(rk_s, call0 + (cc + 1) * 4, p.dr.stream_id, rw[(cc + 1) & 1]);
-          p_chunk<MASKED>(s[cc], pk + cc * 16, rw[cc & 1], sc2, nl2, thr_hi, f_keep);
+          if (MODE == 1 && cc + 1 < 4) philox_rolled<4>(rk_s, call0 + (cc + 1) * 4, p.dr.stream_id, rw[(cc + 1) & 1]);
+          p_chunk<MODE>(s[cc], pk + cc * 16, rw[cc & 1], keepw[cc], sc2, nl2, thr_hi, f_keep);
           store_row32_sw128(w_tile, row, cc * 32, s[cc]);
         }
         fence_proxy_async_smem();
@@ -518,7 +530,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float ksc = f_keep * p.scale;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          ds_chunk<MASKED>(s[cc], pk + cc * 16, ksc, dsc);
+          ds_chunk<(MODE != 0)>(s[cc], pk + cc * 16, ksc, dsc);
           store_row32_sw128(w_tile, row, cc * 32, s[cc]);
         }
         fence_proxy_async_smem();
@@ -600,18 +612,19 @@ size_t attn_bwd_tc_workspace_bytes(const ptj_attn_shape& sh) {
 
 int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
                 const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                const ptj_attn_shape& dsh, const AttnDropout& dr, void* workspace, size_t workspace_bytes,
-                cudaStream_t st) {
+                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits, void* workspace,
+                size_t workspace_bytes, cudaStream_t st) {
   if (workspace == nullptr || workspace_bytes < attn_bwd_tc_workspace_bytes(sh) || !aligned16(workspace))
     return PTJ_ERR_WORKSPACE;
   CUtensorMap tq, tk, tv, tg;
   if (!make_map(&tq, q, sh, sh.q_strides) || !make_map(&tk, k, sh, sh.k_strides) ||
       !make_map(&tv, v, sh, sh.v_strides) || !make_map(&tg, d_o, sh, sh.o_strides))
     return PTJ_ERR_LAUNCH;
-  const AttnParams p = make_params(sh, dr);
+  AttnParams p = make_params(sh, dr);
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
+  p.keep_bits = reinterpret_cast<const uint4*>(keep_bits);
   const bool masked = dr.train && dr.thr16 != 0u;
-  auto kern = masked ? attn_bwd_ws_kernel<true> : attn_bwd_ws_kernel<false>;
+  auto kern = !masked ? attn_bwd_ws_kernel<0> : (p.keep_bits != nullptr ? attn_bwd_ws_kernel<2> : attn_bwd_ws_kernel<1>);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;

@@ -28,13 +28,17 @@ int attn_bwd_simt(const void* d_o, const void* q, const void* k, const void* v, 
 
 // tcgen05 kernels: bf16, d_head == 64, seq % 128 == 0, 16-byte aligned strides.
 bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs);
+// keep_bits (optional, both directions): the call's dropout keep flags from attn_keep_bits_tc; NULL = the kernels draw
+// the same flags themselves.
+size_t attn_keep_bits_bytes(const ptj_attn_shape& sh);
+int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
+                const uint32_t* keep_bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
 // workspace: attn_bwd_tc_workspace_bytes(sh) bytes, 16-byte aligned (per-KV-tile dQ shares and per-row constants)
 size_t attn_bwd_tc_workspace_bytes(const ptj_attn_shape& sh);
 int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
                 const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                const ptj_attn_shape& dsh, const AttnDropout& dr, void* workspace, size_t workspace_bytes,
-                cudaStream_t st);
+                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits, void* workspace,
+                size_t workspace_bytes, cudaStream_t st);
 
 }  // namespace ptj

@@ -70,6 +70,8 @@ struct Cursor {
   }
 };
 
+// MODE 0: no dropout mask; 1: Philox drawn in the kernel; 2: precomputed keep flags (p.keep_bits).
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const RowView out, float* __restrict__ row_max,
@@ -259,7 +261,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t t_o = tmem + lane_base + kSBufs * T + grp * DH;  // this group's output accumulator
     uint8_t* p_tile = p_s + grp * 2 * kTileBytes;
-    const bool masked = p.dr.train && p.dr.thr16 != 0u;
     const float f_eval = p.dr.train ? 1.f : p.dr.eval_scale;  // evaluation: P * (1 - p), applied to the final rows
     const uint32_t thr_hi = p.dr.thr16 << 16;
 
@@ -289,10 +290,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // 32-column chunk ahead of their use (the first chunk while the score MMA may still be running)
         uint32_t rw[2][4][4];  // raw words of the four Philox calls of a 32-column chunk, drawn one chunk ahead
         const uint64_t call0 = ((static_cast<uint64_t>(c.bh) * p.S + q_row) * p.S + static_cast<uint64_t>(c.j) * T) >> 3;
-        if (masked) {
+        if (MODE == 1) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + q, p.dr.stream_id, rw[0][q]);
         }
+        uint4 kb = make_uint4(0u, 0u, 0u, 0u);
+        if (MODE == 2)
+          kb = __ldg(p.keep_bits + (static_cast<int64_t>(c.bh) * (p.nq * (p.nq + 1) / 2) + c.qt * (c.qt + 1) / 2 + c.j) * T + row);
+        const uint32_t keepw[4] = {kb.x, kb.y, kb.z, kb.w};
         ok = mbar_wait(&s_full[sb], (c.g / kSBufs) & 1, ctx, 0x1303u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -345,7 +350,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         uint64_t rp[2] = {0ull, 0ull};  // two packed running sums (four chains)
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          if (masked && cc + 1 < 4) {
+          if (MODE == 1 && cc + 1 < 4) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + (cc + 1) * 4 + q, p.dr.stream_id, rw[(cc + 1) & 1][q]);
           }
@@ -356,10 +361,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             a = ex2_approx(a);
             b = ex2_approx(b);
             rp[(i >> 1) & 1] = add2(rp[(i >> 1) & 1], pack2(a, b));
-            if (masked) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
+            if (MODE == 1) {  // 16-bit lanes of word (i % 8) / 2 of call i / 8: low half = even element, high half = odd
               const uint32_t w = rw[cc & 1][i >> 3][(i & 7) >> 1];
               if ((w << 16) < thr_hi) a = 0.f;
               if (w < thr_hi) b = 0.f;
+            } else if (MODE == 2) {
+              if ((keepw[cc] & (1u << i)) == 0u) a = 0.f;
+              if ((keepw[cc] & (2u << i)) == 0u) b = 0.f;
             }
             s[cc][i] = a;
             s[cc][i + 1] = b;
@@ -469,16 +477,53 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
+// Keep flags of the attention-probability dropout for one call, computed once and shared by the forward and the
+// backward kernel: word c of the uint4 at ((bh * ntri + qt (qt + 1) / 2 + kt) * 128 + row) holds the flags of
+// columns 32 c .. 32 c + 31 of row `row` of tile (qt, kt); ntri = nq (nq + 1) / 2. One thread per word.
+__global__ void __launch_bounds__(256)
+attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, int S, int nq, int64_t total_words) {
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (w >= total_words) return;
+  const int cc = static_cast<int>(w & 3), row = static_cast<int>((w >> 2) & (T - 1));
+  const int64_t tile = w >> 9;  // bh * ntri + tri
+  const int ntri = nq * (nq + 1) / 2;
+  const int64_t bh = tile / ntri;
+  const int tri = static_cast<int>(tile % ntri);
+  int qt = static_cast<int>((sqrtf(8.f * tri + 1.f) - 1.f) * 0.5f);
+  while ((qt + 1) * (qt + 2) / 2 <= tri) ++qt;
+  while (qt * (qt + 1) / 2 > tri) --qt;
+  const int kt = tri - qt * (qt + 1) / 2;
+  const uint64_t idx0 = (static_cast<uint64_t>(bh) * S + static_cast<uint64_t>(qt) * T + row) * S +
+                        static_cast<uint64_t>(kt) * T + cc * 32;
+  bits[w] = keep_bits32(dr, idx0);
+}
+
 }  // namespace
 
+size_t attn_keep_bits_bytes(const ptj_attn_shape& sh) {
+  const int64_t nq = sh.seq / T;
+  return static_cast<size_t>(sh.batch * sh.heads * (nq * (nq + 1) / 2) * T) * 16;
+}
+
+int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
+  const int64_t words = static_cast<int64_t>(attn_keep_bits_bytes(sh) / 4);
+  attn_keep_bits_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, st>>>(bits, dr, static_cast<int>(sh.seq),
+                                                                                    static_cast<int>(sh.seq / T), words);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
+                const uint32_t* keep_bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   if (!make_map(&tq, q, sh, sh.q_strides) || !make_map(&tk, k, sh, sh.k_strides) || !make_map(&tv, v, sh, sh.v_strides))
     return PTJ_ERR_LAUNCH;
-  const AttnParams p = make_params(sh, dr);
+  AttnParams p = make_params(sh, dr);
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
-  if (cudaFuncSetAttribute(attn_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+  p.keep_bits = reinterpret_cast<const uint4*>(keep_bits);
+  const bool masked = dr.train && dr.thr16 != 0u;
+  auto kern = !masked ? attn_fwd_ws_kernel<0> : (keep_bits != nullptr ? attn_fwd_ws_kernel<2> : attn_fwd_ws_kernel<1>);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
@@ -489,7 +534,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row
   const int grid = s.total < kNumSMs ? s.total : kNumSMs;
   s.rounds = (s.total + grid - 1) / grid;
   s.bh_magic = static_cast<uint32_t>(((1ull << 32) + s.BH - 1) / s.BH);
-  attn_fwd_ws_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p, s);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p, s);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

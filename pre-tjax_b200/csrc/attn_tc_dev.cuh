@@ -29,6 +29,7 @@ struct AttnParams {
   float scale;       // 1 / sqrt(d_head)
   AttnDropout dr;
   uint32_t rk[20];   // Philox round keys of dr.seed (round r uses rk[2r], rk[2r+1]): the same for every call
+  const uint4* keep_bits;  // optional precomputed keep flags, one uint4 per (batch*head, tile, row): see attn_keep_bits_tc
   unsigned int* fault;
 };
 

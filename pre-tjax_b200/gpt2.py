@@ -184,7 +184,9 @@ class Gpt2Step:
             q, k, v = (qkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
             a["attn"] = torch.empty((T, D), device=x.device, dtype=self.dtype)
             o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
-            a["m"], a["l"] = ops.attn_fwd(q, k, v, o4, train, s_attn, p=p)
+            # the layer's attention-dropout keep flags are drawn once and shared by the forward and backward kernels
+            a["keep"] = ops.attn_keep_bits(q, k, v, o4, s_attn, p=p) if (train and p > 0.0) else None
+            a["m"], a["l"] = ops.attn_fwd(q, k, v, o4, train, s_attn, p=p, keep_bits=a["keep"])
             a["x_mid"] = ops.gemm(a["attn"], g("w_o"), epilogue=_lib.EPI_DROPOUT_RESID, aux=x,
                                   dropout_args=(p, train, s_res1, 0))
             a["ln2"] = ops.t_layernorm_fwd_t((g("g2"), g("b2")), a["x_mid"])
@@ -244,7 +246,7 @@ class Gpt2Step:
             dq, dk, dv = (dqkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
             o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
             do4 = d_attn.view(B, S, H, dh).permute(0, 2, 1, 3)
-            ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p)
+            ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p, keep_bits=a.get("keep"))
             self._wgrad(dqkv, a["ln1"], G("w_qkv").view(3 * D, D))
             d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
             dx = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx)

@@ -249,7 +249,26 @@ def _attn_shape(B, H, N, D, q, k, v, o_strides):
     return s
 
 
-def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None):
+def attn_keep_bits(q, k, v, out, seed, stream_id=0, p=None, bits=None):
+    """Dropout keep flags of one attention call, to be passed to attn_fwd and attn_bwd (`keep_bits=`) so that the mask
+    is drawn once instead of in each kernel. Returns None when the call would not take the tensor-core path or when
+    there is nothing to drop. `bits`: optional int32 tensor to reuse."""
+    B, H, N, D = q.shape
+    p = DROPOUT_RATE if p is None else p
+    if p <= 0.0:
+        return None
+    sh = _attn_shape(B, H, N, D, q, k, v, out.stride()[:3])
+    need = int(_lib.lib().ptj_attn_keep_bits_bytes(ctypes.byref(sh), _dt(q)))
+    if need == 0:
+        return None
+    if bits is None or bits.numel() * bits.element_size() < need:
+        bits = torch.empty(need // 4, device=q.device, dtype=torch.int32)
+    _lib.check(_lib.lib().ptj_attn_keep_bits(_ptr(bits), ctypes.byref(sh), p, _seed(seed), stream_id, _dt(q), _stream()),
+               "ptj_attn_keep_bits")
+    return bits
+
+
+def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None, keep_bits=None):
     """q,k,v,out: [B,H,N,D] strided views (D contiguous). Returns (row_max, row_sum) float32 [B,H,N]."""
     B, H, N, D = q.shape
     m = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
@@ -257,7 +276,8 @@ def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None):
     sh = _attn_shape(B, H, N, D, q, k, v, out.stride()[:3])
     p = DROPOUT_RATE if p is None else p
     _lib.check(_lib.lib().ptj_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m), _ptr(l), ctypes.byref(sh), p,
-                                       int(bool(train)), _seed(seed), stream_id, _dt(q), _stream()), "ptj_attn_fwd")
+                                       int(bool(train)), _seed(seed), stream_id, _ptr(keep_bits), _dt(q), _stream()),
+               "ptj_attn_fwd")
     return m, l
 
 
@@ -274,7 +294,7 @@ def attn_bwd_workspace(nbytes, device):
     return buf
 
 
-def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None, workspace=None):
+def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None, workspace=None, keep_bits=None):
     """workspace: optional uint8 tensor of at least ptj_attn_bwd_workspace_bytes; by default one buffer per
     (device, stream) is kept and reused."""
     B, H, N, D = q.shape
@@ -290,7 +310,7 @@ def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None
     _lib.check(
         _lib.lib().ptj_attn_bwd(_ptr(d_o), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(m), _ptr(l), _ptr(dq), _ptr(dk),
                                 _ptr(dv), ctypes.byref(sh), ctypes.byref(dsh), p, int(bool(train)), _seed(seed),
-                                stream_id, wptr, wbytes, _dt(q), _stream()), "ptj_attn_bwd")
+                                stream_id, _ptr(keep_bits), wptr, wbytes, _dt(q), _stream()), "ptj_attn_bwd")
 
 
 def t_scaled_dot_prod_attn_fwd3_t(qkv: torch.Tensor, mask: torch.Tensor = None, train=True, p_gen_aux=None):

@@ -92,3 +92,37 @@ def test_tensor_core_and_cuda_core_kernels_agree(ops, monkeypatch):
     out_cc, _ = ops.t_scaled_dot_prod_attn_fwd3_t(qkv[:, :, :, :192].contiguous(), None, True, 1)
     assert rel_err(out_tc[:, :, :192], out_cc) < TOL  # causal: the first 192 rows do not see the rest
     ops.DROPOUT_RATE = 0.1
+
+
+def test_keep_bits_handed_over_match_the_in_kernel_mask():
+    """ptj_attn_keep_bits draws the call's dropout flags once; forward and backward given those flags must return
+    exactly what they return when they draw the mask themselves, and the flags must equal the oracle's mask stream."""
+    ops = pkg("operators")
+    B, H, S, D, p, seed = 2, 3, 384, 64, 0.25, 77
+    ops.DROPOUT_RATE = p
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, H, 3, S, D, generator=g).bfloat16().cuda()
+    q, k, v = qkv.unbind(dim=2)
+    do4 = torch.randn(B, H, S, D, generator=g).bfloat16().cuda()
+    res = []
+    for use_bits in (False, True):
+        o4 = torch.empty(B, H, S, D, device="cuda", dtype=torch.bfloat16)
+        dq, dk, dv = (torch.empty(B, H, S, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        bits = ops.attn_keep_bits(q, k, v, o4, seed) if use_bits else None
+        assert (bits is not None) == use_bits
+        m, l = ops.attn_fwd(q, k, v, o4, True, seed, keep_bits=bits)
+        ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, seed, keep_bits=bits)
+        res.append((o4, m, l, dq, dk, dv, bits))
+    torch.cuda.synchronize()
+    assert ops.last_kernel_fault() == 0
+    for a, b in zip(res[0][:6], res[1][:6]):
+        assert torch.equal(a, b)
+    # layout: uint4 per (batch*head, tile (qt, kt) in triangular order, row); word c = columns 32c..32c+31
+    bits = res[1][6].cpu().numpy().view("uint32").reshape(B * H, 6, 128, 4)
+    mask = philox.keep_mask(seed, 0, B * H * S * S, p).reshape(B * H, S, S)
+    for bh, qt, kt, row, c in ((0, 0, 0, 5, 0), (3, 2, 1, 127, 3), (5, 1, 1, 64, 2), (2, 2, 0, 0, 1)):
+        word = int(bits[bh, qt * (qt + 1) // 2 + kt, row, c])
+        want = mask[bh, qt * 128 + row, kt * 128 + c * 32: kt * 128 + c * 32 + 32]
+        got = [(word >> i) & 1 for i in range(32)]
+        assert got == [int(x) for x in want]
+    ops.DROPOUT_RATE = 0.1
