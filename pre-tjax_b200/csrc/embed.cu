@@ -171,6 +171,45 @@ colsum_stage1_kernel(const T* __restrict__ x, float* __restrict__ partial, int64
   for (int j = 0; j < V; ++j)
     if (c0 + j < cols) out[c0 + j] = s[j];
 }
+// stage 1, vector path: a block of 8 warps owns 32 column groups of 16 bytes (a warp reads 512 contiguous bytes of a
+// row) and one chunk of rows; warp w takes rows r0 + w, r0 + w + 8, ...; the eight per-warp sums are added in warp
+// order through shared memory, so the result depends only on the shapes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_stage1_rows_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols, int64_t ld,
+                          int64_t chunk) {
+  constexpr int V = Elem<T>::kVec;
+  __shared__ float red[8][32][V + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c0 = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * V;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * chunk;
+  const int64_t r1 = r0 + chunk < rows ? r0 + chunk : rows;
+  float s[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) s[j] = 0.f;
+  if (c0 < cols) {
+#pragma unroll 4
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      float v[V];
+      Elem<T>::load_vec(x + r * ld + c0, v);  // may read padding columns (ld is a multiple of the vector), never writes them
+#pragma unroll
+      for (int j = 0; j < V; ++j) s[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) red[warp][lane][j] = s[j];
+  __syncthreads();
+  // 32 x V sums to write: thread t takes element t (and t + 256, ...) and adds the eight warps in order
+  float* out = partial + static_cast<int64_t>(blockIdx.y) * cols;
+  for (int e = threadIdx.x; e < 32 * V; e += 256) {
+    const int g = e / V, j = e - g * V;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][g][j];
+    const int64_t c = (static_cast<int64_t>(blockIdx.x) * 32 + g) * V + j;
+    if (c < cols) out[c] = t;
+  }
+}
 // stage 2: a block owns 32 columns; its 8 warps sum strided subsets of the chunk rows, added in warp order.
 __global__ void __launch_bounds__(256)
 colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t cols, int nchunks) {
@@ -190,9 +229,12 @@ colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out,
   }
 }
 
+// Narrow matrices (the hidden-size bias gradients) split the rows of a chunk over a block's warps; wide ones (the
+// vocabulary) have enough columns to fill the machine with one thread per column group.
+inline bool colsum_split_rows(int64_t cols) { return cols <= 8192; }
 inline int colsum_chunks(int64_t rows, int64_t cols) {
-  // enough row chunks to fill the machine (about 8 blocks of 128 threads per SM), at least 32 rows per chunk
-  const int64_t strips = ceil_div(ceil_div(cols, 8), 128);
+  // enough row chunks to fill the machine (about 8 blocks per SM), at least 32 rows per chunk
+  const int64_t strips = colsum_split_rows(cols) ? ceil_div(ceil_div(cols, 4), 32) : ceil_div(ceil_div(cols, 8), 128);
   int64_t want = ceil_div(static_cast<int64_t>(kNumSMs) * 8, strips);
   const int64_t max_chunks = ceil_div(rows, 32);
   if (want > max_chunks) want = max_chunks;
@@ -312,11 +354,14 @@ extern "C" int ptj_colsum(const void* x, float* out, float* scratch, size_t scra
   const bool vec = aligned16(x) && ld % V == 0 && ceil_div(cols, V) * V <= ld;
   const int64_t groups = vec ? ceil_div(cols, V) : cols;
   dim3 grid(static_cast<unsigned>(ceil_div(groups, 128)), static_cast<unsigned>(nchunks));
+  dim3 grid_rows(static_cast<unsigned>(ceil_div(groups, 32)), static_cast<unsigned>(nchunks));
   if (dtype == PTJ_F32) {
-    if (vec) colsum_stage1_kernel<float, true><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    if (vec && colsum_split_rows(cols)) colsum_stage1_rows_kernel<float><<<grid_rows, 256, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    else if (vec) colsum_stage1_kernel<float, true><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
     else colsum_stage1_kernel<float, false><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
   } else {
-    if (vec) colsum_stage1_kernel<__nv_bfloat16, true><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    if (vec && colsum_split_rows(cols)) colsum_stage1_rows_kernel<__nv_bfloat16><<<grid_rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    else if (vec) colsum_stage1_kernel<__nv_bfloat16, true><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
     else colsum_stage1_kernel<__nv_bfloat16, false><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
   }
   PTJ_CHECK_LAUNCH();

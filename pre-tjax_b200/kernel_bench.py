@@ -155,6 +155,10 @@ def main():
         m, l = ops.attn_fwd(q, k, v, o4, True, 5, p=0.1)
         add("attention fwd  B*H=%d S=1024 d=64 dropout 0.1" % (B * H), time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1)), flops=fl_attn)
         add("attention bwd  (dQ, dK, dV; recompute) dropout 0.1", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1)), flops=2.5 * fl_attn)
+        bits = ops.attn_keep_bits(q, k, v, o4, 5, p=0.1)
+        add("attention keep flags of one call (Philox, 16-bit lanes)", time_us(lambda: ops.attn_keep_bits(q, k, v, o4, 5, p=0.1, bits=bits)))
+        add("attention fwd  dropout 0.1, keep flags given", time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits)), flops=fl_attn)
+        add("attention bwd  dropout 0.1, keep flags given", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1, keep_bits=bits)), flops=2.5 * fl_attn)
         add("attention fwd  no dropout", time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.0)), flops=fl_attn)
         add("attention bwd  no dropout", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.0)), flops=2.5 * fl_attn)
 
