@@ -68,6 +68,15 @@ size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim);
 int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
                       float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
                       int64_t dim, int dtype, void* stream);
+/* ptj_layernorm_bwd with a second output: dx_dropped = dropout(dx) for the mask stream of site (seed, stream_id) over
+ * the contiguous [rows, dim] tensor, i.e. exactly what ptj_dropout(dx, NULL, dx_dropped, ...) would write, without a
+ * second pass over dx (the reference runs t_dropout_bkwd as its own kernel, model_triton.py:153). dx must be given;
+ * rows must be 16-byte aligned with dim a multiple of the 16-byte vector and at most 8 x 32 vectors
+ * (else PTJ_ERR_UNSUPPORTED: call ptj_layernorm_bwd and ptj_dropout). */
+int ptj_layernorm_bwd_dropout(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                              void* dx_dropped, float* dgamma, float* dbeta, float* scratch, size_t scratch_floats,
+                              int64_t rows, int64_t dim, float p, int train, uint64_t seed, uint32_t stream_id,
+                              int dtype, void* stream);
 
 /* LayerNorm backward that needs no scratch buffer from the caller. It has no counterpart in the reference: it
  * exists for callers that cannot allocate device memory themselves, e.g. code running inside a process whose GPU

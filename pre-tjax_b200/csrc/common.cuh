@@ -31,6 +31,7 @@ template <> struct Elem<float> {
   static constexpr int kVec = 4;  // elements per 16-byte vector
   static __device__ __forceinline__ float load(const float* p) { return *p; }
   static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float round(float v) { return v; }  // value as it will be stored
   static __device__ __forceinline__ void load_vec(const float* p, float (&v)[4]) {
     float4 t = *reinterpret_cast<const float4*>(p);
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
@@ -43,6 +44,7 @@ template <> struct Elem<__nv_bfloat16> {
   static constexpr int kVec = 8;
   static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
   static __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&v)[8]) {
     uint4 t = *reinterpret_cast<const uint4*>(p);
     const uint32_t w[4] = {t.x, t.y, t.z, t.w};

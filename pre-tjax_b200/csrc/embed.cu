@@ -87,26 +87,42 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
       __syncthreads();  // previous batch fully consumed
       pos_s[threadIdx.x] = pos;
       const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
-      for (int r = warp; r < n; r += 8) {
-        const int64_t row = static_cast<int64_t>(pos_s[r]) * dim;
+      // four rows per step: their loads are independent, the additions keep the row order
+      for (int r0 = warp; r0 < n; r0 += 32) {
+        float x[4][NV][8];
+        int64_t rows4[4];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int v = lane + 32 * i;
-          if (v < nvec) {
-            float x[8];
-            if (sizeof(T) == 2) {
-              Elem<__nv_bfloat16>::load_vec(reinterpret_cast<const __nv_bfloat16*>(dy) + row + v * 8, x);
-            } else {
-              float lo[4], hi[4];
-              Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + row + v * 8, lo);
-              Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + row + v * 8 + 4, hi);
+        for (int u = 0; u < 4; ++u) {
+          const int r = r0 + 8 * u;
+          rows4[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
 #pragma unroll
-              for (int e = 0; e < 4; ++e) { x[e] = lo[e]; x[4 + e] = hi[e]; }
+          for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (rows4[u] >= 0 && v < nvec) {
+              if (sizeof(T) == 2) {
+                Elem<__nv_bfloat16>::load_vec(reinterpret_cast<const __nv_bfloat16*>(dy) + rows4[u] + v * 8, x[u][i]);
+              } else {
+                float lo[4], hi[4];
+                Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + rows4[u] + v * 8, lo);
+                Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + rows4[u] + v * 8 + 4, hi);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { x[u][i][e] = lo[e]; x[u][i][4 + e] = hi[e]; }
+              }
             }
-            uint32_t keep = 0xffu;
-            if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(row + v * 8) >> 3, thr);
+          }
+        }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
+        for (int u = 0; u < 4; ++u) {
+          if (rows4[u] < 0) continue;
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+              uint32_t keep = 0xffu;
+              if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(rows4[u] + v * 8) >> 3, thr);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[u][i][e] * k_all : 0.f;
+            }
           }
         }
       }

@@ -111,13 +111,25 @@ ln_fwd_generic_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
+// Optional second output of the backward kernel: dropout (mask stream of site (seed, stream_id), element index =
+// row * dim + column, i.e. the stream ptj_dropout uses on the contiguous [rows, dim] tensor) applied to dx, so that the
+// consumer of "dropout backward of dx" needs no separate pass over dx.
+struct LnMask {
+  void* out;
+  uint32_t thr;
+  float eval_scale;
+  int train;
+  uint64_t seed;
+  uint32_t stream_id;
+};
+
 // dx and the per-block partial sums of dgamma / dbeta in one pass over (dy, x). The running column sums live in
 // shared memory (one private strip per warp, laid out [slot][lane] so accesses are conflict-free) rather than in
 // registers: the kernel is latency-bound, and the lower register count doubles the number of resident warps.
 template <typename T, int NV>
 __global__ void __launch_bounds__(kLnThreads, (NV * Elem<T>::kVec <= 32) ? 2 : 1)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
-              const T* dx_add, T* dx, float* __restrict__ partial, int64_t rows, int dim) {
+              const T* dx_add, T* dx, float* __restrict__ partial, int64_t rows, int dim, const LnMask mk) {
   constexpr int V = Elem<T>::kVec;
   constexpr int kSlots = NV * V * 32;   // per-warp accumulator slots per quantity
   extern __shared__ float sm_acc[];     // [kLnWarps][2][kSlots]
@@ -225,6 +237,19 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
             for (int j = 0; j < V; ++j) o[j] += r[i][j];
           }
           Elem<T>::store_vec(dr + vi * V, o);
+          if (mk.out != nullptr) {  // second output: dropout applied to dx as stored (rounded to T), see LnMask
+            T* mr = static_cast<T*>(mk.out) + row * dim;
+            const uint64_t idx = static_cast<uint64_t>(row) * dim + static_cast<uint64_t>(vi) * V;
+            uint32_t keep = 0xffu;
+            if (mk.train && mk.thr != 0u)
+              keep = dropout_keep_bits8(mk.seed, mk.stream_id, idx >> 3, mk.thr) >> (idx & 7);
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              const float r = Elem<T>::round(o[j]);
+              o[j] = mk.train ? (((keep >> j) & 1u) ? r : 0.f) : r * mk.eval_scale;
+            }
+            Elem<T>::store_vec(mr + vi * V, o);
+          }
         }
       }
     }
@@ -332,10 +357,10 @@ int launch_fwd(const T* x, const float* gamma, const float* beta, T* y, int64_t 
 
 template <typename T>
 int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* dx, float* dgamma, float* dbeta,
-               float* scratch, int64_t rows, int dim, cudaStream_t st) {
+               float* scratch, int64_t rows, int dim, const LnMask& mk, cudaStream_t st) {
   constexpr int V = Elem<T>::kVec;
   const bool vec_ok = dim % V == 0 && aligned16(x) && aligned16(dy) && (dx == nullptr || aligned16(dx)) &&
-                      (dx_add == nullptr || aligned16(dx_add)) && aligned16(gamma);
+                      (dx_add == nullptr || aligned16(dx_add)) && aligned16(gamma) && (mk.out == nullptr || aligned16(mk.out));
   const int nv = vec_ok ? static_cast<int>(ceil_div(dim / V, 32)) : 99;
   const int grid = ln_bwd_grid(rows);
   float* partial = dgamma != nullptr ? scratch : nullptr;
@@ -344,11 +369,12 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
   case NV:                                                                                               \
     if (smem > 48 * 1024)                                                                                \
       cudaFuncSetAttribute(ln_bwd_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    ln_bwd_kernel<T, NV><<<grid, kLnThreads, smem, st>>>(dy, x, gamma, dx_add, dx, partial, rows, dim);           \
+    ln_bwd_kernel<T, NV><<<grid, kLnThreads, smem, st>>>(dy, x, gamma, dx_add, dx, partial, rows, dim, mk);       \
     break;
   switch (nv) {
     PTJ_LN_BWD(1) PTJ_LN_BWD(2) PTJ_LN_BWD(3) PTJ_LN_BWD(4) PTJ_LN_BWD(5) PTJ_LN_BWD(6) PTJ_LN_BWD(7) PTJ_LN_BWD(8)
     default:
+      if (mk.out != nullptr) return PTJ_ERR_UNSUPPORTED;  // the masked output needs vector-aligned rows of <= 8 x 32 vectors
       ln_bwd_generic_kernel<T><<<grid, kLnThreads, 0, st>>>(dy, x, gamma, dx_add, dx, partial, rows, dim);
   }
 #undef PTJ_LN_BWD
@@ -384,12 +410,13 @@ extern "C" size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim) {
   return static_cast<size_t>(ln_bwd_grid(rows)) * 2 * static_cast<size_t>(dim);
 }
 
-extern "C" int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
-                                 float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
-                                 int64_t dim, int dtype, void* stream) {
+static int layernorm_bwd_impl(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                              float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
+                              int64_t dim, const LnMask& mk, int dtype, void* stream) {
   if (rows < 0 || dim < 1 || dim > (1 << 20)) return PTJ_ERR_BAD_SHAPE;
   if ((dgamma == nullptr) != (dbeta == nullptr)) return PTJ_ERR_BAD_SHAPE;
   if (!dy || !x || !gamma) return PTJ_ERR_BAD_SHAPE;
+  if (mk.out != nullptr && dx == nullptr) return PTJ_ERR_BAD_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (rows == 0) {
     if (dgamma) {
@@ -403,14 +430,31 @@ extern "C" int ptj_layernorm_bwd(const void* dy, const void* x, const float* gam
   if (dtype == PTJ_F32)
     return launch_bwd(static_cast<const float*>(dy), static_cast<const float*>(x), gamma,
                       static_cast<const float*>(dx_add), static_cast<float*>(dx), dgamma, dbeta, scratch, rows, (int)dim,
-                      st);
+                      mk, st);
   if (dtype == PTJ_BF16)
     return launch_bwd(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma,
                       static_cast<const __nv_bfloat16*>(dx_add), static_cast<__nv_bfloat16*>(dx), dgamma, dbeta, scratch,
-                      rows, (int)dim, st);
+                      rows, (int)dim, mk, st);
   return PTJ_ERR_DTYPE;
 }
 
+extern "C" int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                                 float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
+                                 int64_t dim, int dtype, void* stream) {
+  const LnMask none{nullptr, 0u, 1.f, 0, 0ull, 0u};
+  return layernorm_bwd_impl(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, scratch_floats, rows, dim, none, dtype,
+                            stream);
+}
+
+extern "C" int ptj_layernorm_bwd_dropout(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
+                                         void* dx_dropped, float* dgamma, float* dbeta, float* scratch,
+                                         size_t scratch_floats, int64_t rows, int64_t dim, float p, int train,
+                                         uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
+  if (!dx_dropped || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
+  const LnMask mk{dx_dropped, dropout_threshold16(p), 1.f - p, train, seed, stream_id};
+  return layernorm_bwd_impl(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, scratch_floats, rows, dim, mk, dtype,
+                            stream);
+}
 // ---- LayerNorm backward for callers that must not allocate ------------------------------------------------------
 // The partial column sums of ptj_layernorm_bwd normally live in a scratch buffer the caller allocates. Some callers
 // cannot do that: code that runs inside a process whose device memory was handed out up front to another allocator

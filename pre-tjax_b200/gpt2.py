@@ -218,7 +218,11 @@ class Gpt2Step:
         self._head_wgrad(dlogits, acts["x_f"], grads["w_emb"])
         ready(["b_head"])
         d = self._dgrad(dlogits, w["w_emb"], cols=V)
-        dx = self._ln_bwd(d, w["g_f"], acts["x_last"], grads["g_f"], grads["b_f"])
+        # every LayerNorm backward also writes dropout(dx) for the residual branch that consumes it next
+        fuse = D % 8 == 0 and D <= (2048 if self.dtype == torch.bfloat16 else 1024)
+        s_next = seeds[3 * cfg.layers] if cfg.layers > 0 else 0  # last layer's second residual dropout
+        dx, dy = self._ln_bwd(d, w["g_f"], acts["x_last"], grads["g_f"], grads["b_f"],
+                              dropped=(train, s_next, p) if (fuse and cfg.layers > 0) else None)
         ready(["g_f", "b_f"])
 
         for l in reversed(range(cfg.layers)):
@@ -227,17 +231,20 @@ class Gpt2Step:
             g = lambda n: w[f"l{l}.{n}"]
             G = lambda n: grads[f"l{l}.{n}"]
             # x_next = x_mid + dropout(W2 gelu(W1 ln2(x_mid) + b1f) + b2f)
-            dy = ops.dropout(dx, train, s_res2, p=p)
+            if dy is None:
+                dy = ops.dropout(dx, train, s_res2, p=p)
             ops.colsum(dy, out=G("b2f"))
             self._wgrad(dy, a["h_act"], G("w2"))
             dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
             ops.colsum(dh_pre, out=G("b1f"))
             self._wgrad(dh_pre, a["ln2"], G("w1"))
             d_ln2 = self._dgrad(dh_pre, g("w1"))
-            dx = self._ln_bwd(d_ln2, g("g2"), a["x_mid"], G("g2"), G("b2"), dx_add=dx)
+            dx, dy = self._ln_bwd(d_ln2, g("g2"), a["x_mid"], G("g2"), G("b2"), dx_add=dx,
+                                  dropped=(train, s_res1, p) if fuse else None)
             ready([f"l{l}.{n}" for n in ("b2f", "w2", "b1f", "w1", "g2", "b2")])
             # x_mid = x + dropout(attn(ln1(x)) W_o^T)
-            dy = ops.dropout(dx, train, s_res1, p=p)
+            if dy is None:
+                dy = ops.dropout(dx, train, s_res1, p=p)
             self._wgrad(dy, a["attn"], G("w_o"))
             d_attn = self._dgrad(dy, g("w_o"))
             dqkv = torch.empty((T, 3 * D), device=dy.device, dtype=self.dtype)
@@ -249,7 +256,9 @@ class Gpt2Step:
             ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p, keep_bits=a.get("keep"))
             self._wgrad(dqkv, a["ln1"], G("w_qkv").view(3 * D, D))
             d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
-            dx = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx)
+            s_prev = seeds[3 * l] if l > 0 else 0  # the layer below's second residual dropout consumes this dx
+            dx, dy = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx,
+                                  dropped=(train, s_prev, p) if (fuse and l > 0) else None)
             ready([f"l{l}.{n}" for n in ("w_o", "w_qkv", "g1", "b1")])
 
         # embedding + positions; the scatter accumulates onto the LM-head weight gradient (tied weights)
@@ -263,10 +272,11 @@ class Gpt2Step:
         ops.gemm(dlogits, x_f, a_kmajor=False, b_kmajor=False, M=V, N=x_f.shape[1], K=T, lda=dlogits.stride(0),
                  ldb=x_f.stride(0), out=out)
 
-    def _ln_bwd(self, dy, gamma, x, dgamma_out, dbeta_out, dx_add=None):
-        dx, _, _ = ops.layernorm_bwd(dy, (gamma, None), x, want_dx=True, want_dp=True, dx_add=dx_add,
-                                     dgamma_out=dgamma_out, dbeta_out=dbeta_out)
-        return dx
+    def _ln_bwd(self, dy, gamma, x, dgamma_out, dbeta_out, dx_add=None, dropped=None):
+        """Returns (dx, dropout(dx) or None)."""
+        res = ops.layernorm_bwd(dy, (gamma, None), x, want_dx=True, want_dp=True, dx_add=dx_add,
+                                dgamma_out=dgamma_out, dbeta_out=dbeta_out, dropped=dropped)
+        return res[0], (res[3] if dropped is not None else None)
 
     # -- loss + gradients --
     def loss_and_grads(self, w: Weights, grads: dict, y: torch.Tensor, train: bool, seeds: Sequence[int],

@@ -193,6 +193,17 @@ def main():
         sh = torch.zeros(n, device=dev, dtype=torch.bfloat16)
         add("adamw fused (+bf16 shadow) 124M params", time_us(lambda: lib.check(lib.lib().ptj_adamw(p_.data_ptr(), g_.data_ptr(), m_.data_ptr(), v_.data_ptr(), sh.data_ptr(), n, 0, 0, 0, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, 0, 0.0, st()), "adamw"), reps=r5), nbytes=n * 30)
         add("grad sum of squares 124M", time_us(lambda: ptj.optimizer.sumsq(g_), reps=r5), nbytes=n * 4)
+        del p_, g_, m_, v_, sh
+        # embedding backward on Zipf(1.1) token ids (the most frequent token makes a run of several hundred rows)
+        gz = torch.Generator().manual_seed(0)
+        wz = torch.arange(1, V, dtype=torch.float64).pow(-1.1)
+        ids = (torch.searchsorted(torch.cumsum(wz / wz.sum(), 0), torch.rand((B, S), generator=gz, dtype=torch.float64))
+               .clamp_(max=V - 2) + 1).to(torch.int32).to(dev)
+        spos = torch.sort(ids.reshape(-1), stable=True).indices.to(torch.int32)
+        dwe, dwp, dy_e = torch.zeros(V, D, device=dev), torch.zeros(S, D, device=dev), bf(T, D)
+        add("embedding backward (scatter by token run + positions), Zipf ids, dropout 0.1",
+            time_us(lambda: ops.embed_bwd(dy_e, ids, dwe, dwp, True, True, 3, sorted_pos=spos, p=0.1), reps=r5),
+            nbytes=T * D * 2 * 2)
 
     print(f"# peaks ({label}): {peak_tf} TFLOP/s bf16, {peak_gbs} GB/s", flush=True)
     if out_json:

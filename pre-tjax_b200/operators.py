@@ -68,9 +68,11 @@ def t_layernorm_fwd_t(layer_params, x: torch.Tensor) -> torch.Tensor:
 
 
 def layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=True, dx_add=None, dgamma_out=None,
-                  dbeta_out=None):
+                  dbeta_out=None, dropped=None):
     """Fused LayerNorm backward: (dx or None, dgamma or None, dbeta or None); dx_add is added onto dx.
-    dgamma_out / dbeta_out: optional float32 destinations (e.g. views of a flat gradient buffer)."""
+    dgamma_out / dbeta_out: optional float32 destinations (e.g. views of a flat gradient buffer).
+    dropped = (train, seed, p[, stream_id]): additionally return, as a fourth value, dropout(dx) for that mask site
+    (what t_dropout of dx would give), written by the same kernel."""
     x = _cuda(x, "x")
     dy = _cuda(dloss_dx, "dloss_dx")
     if dy.dtype != x.dtype:
@@ -88,6 +90,16 @@ def layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=True, dx_add=
         scratch = torch.empty(max(n_scratch, 1), device=x.device, dtype=torch.float32)
     if dx_add is not None:
         dx_add = _cuda(dx_add, "dx_add")
+    if dropped is not None:
+        train, seed, p = dropped[:3]
+        stream_id = dropped[3] if len(dropped) > 3 else 0
+        dxd = torch.empty_like(x)
+        _lib.check(
+            _lib.lib().ptj_layernorm_bwd_dropout(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx_add), _ptr(dx), _ptr(dxd),
+                                                 _ptr(dg), _ptr(db), _ptr(scratch), n_scratch, rows, dim,
+                                                 DROPOUT_RATE if p is None else p, int(bool(train)), _seed(seed),
+                                                 stream_id, _dt(x), _stream()), "ptj_layernorm_bwd_dropout")
+        return dx, dg, db, dxd
     _lib.check(
         _lib.lib().ptj_layernorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx_add), _ptr(dx), _ptr(dg), _ptr(db),
                                      _ptr(scratch), n_scratch, rows, dim, _dt(x), _stream()),

@@ -297,3 +297,26 @@ def test_colsum_and_sumsq(ops, rows, cols):
     opt = pkg("optimizer")
     s = opt.sumsq(gpu(x).view(-1))
     check(s.reshape(()), (x.double() ** 2).sum().reshape(()), F32_TOL)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm_backward_with_fused_dropout_output(dtype):
+    """ptj_layernorm_bwd_dropout: dx, dgamma, dbeta equal the plain call bit for bit, and the extra output equals
+    ptj_dropout applied to that dx (training mask and evaluation scaling)."""
+    ops = pkg("operators")
+    g = torch.Generator().manual_seed(3)
+    rows, dim = 300, 768
+    x = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    dy = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    add = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    gamma = (1 + 0.1 * torch.randn(dim, generator=g)).cuda()
+    for train in (True, False):
+        dx0, dg0, db0 = ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add)
+        dx1, dg1, db1, dxd = ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add, dropped=(train, 41, 0.3, 2))
+        assert torch.equal(dx0, dx1) and torch.equal(dg0, dg1) and torch.equal(db0, db1)
+        ref = ops.dropout(dx0, train, 41, stream_id=2, p=0.3)
+        assert torch.equal(dxd, ref)
+        if train:
+            kept = float((dxd != 0).float().mean())
+            assert abs(kept - 0.7) < 0.01
