@@ -480,22 +480,38 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // Keep flags of the attention-probability dropout for one call, computed once and shared by the forward and the
 // backward kernel: word c of the uint4 at ((bh * ntri + qt (qt + 1) / 2 + kt) * 128 + row) holds the flags of
 // columns 32 c .. 32 c + 31 of row `row` of tile (qt, kt); ntri = nq (nq + 1) / 2. One thread per word.
-__global__ void __launch_bounds__(256)
-attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, int S, int nq, int64_t total_words) {
-  const int64_t w = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (w >= total_words) return;
-  const int cc = static_cast<int>(w & 3), row = static_cast<int>((w >> 2) & (T - 1));
-  const int64_t tile = w >> 9;  // bh * ntri + tri
+struct RoundKeys {
+  uint32_t k[20];
+};
+__global__ void __launch_bounds__(512)
+attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, const RoundKeys rk, int S, int nq) {
+  // one block per tile (its position is decoded once), one thread per word: 128 rows x 4 words
   const int ntri = nq * (nq + 1) / 2;
+  const int64_t tile = blockIdx.x;  // bh * ntri + tri
   const int64_t bh = tile / ntri;
   const int tri = static_cast<int>(tile % ntri);
   int qt = static_cast<int>((sqrtf(8.f * tri + 1.f) - 1.f) * 0.5f);
   while ((qt + 1) * (qt + 2) / 2 <= tri) ++qt;
   while (qt * (qt + 1) / 2 > tri) --qt;
   const int kt = tri - qt * (qt + 1) / 2;
+  const int cc = threadIdx.x & 3, row = threadIdx.x >> 2;
   const uint64_t idx0 = (static_cast<uint64_t>(bh) * S + static_cast<uint64_t>(qt) * T + row) * S +
                         static_cast<uint64_t>(kt) * T + cc * 32;
-  bits[w] = keep_bits32(dr, idx0);
+  // four Philox calls (round keys from the kernel parameters), eight 16-bit lanes each: bit e of a call's byte is set
+  // when lane e (low half of word e / 2 for even e, high half for odd e) is >= the threshold
+  const uint32_t thr_hi = dr.thr16 << 16;
+  uint32_t word = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w[4];
+    philox_rk(rk.k, (idx0 >> 3) + q, dr.stream_id, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      word |= ((w[e] << 16) >= thr_hi ? 1u : 0u) << (8 * q + 2 * e);
+      word |= (w[e] >= thr_hi ? 1u : 0u) << (8 * q + 2 * e + 1);
+    }
+  }
+  bits[tile * 512 + threadIdx.x] = word;
 }
 
 }  // namespace
@@ -506,9 +522,14 @@ size_t attn_keep_bits_bytes(const ptj_attn_shape& sh) {
 }
 
 int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
-  const int64_t words = static_cast<int64_t>(attn_keep_bits_bytes(sh) / 4);
-  attn_keep_bits_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, st>>>(bits, dr, static_cast<int>(sh.seq),
-                                                                                    static_cast<int>(sh.seq / T), words);
+  const int64_t tiles = static_cast<int64_t>(attn_keep_bits_bytes(sh) / 2048);
+  RoundKeys rk;
+  for (int r = 0; r < 10; ++r) {
+    rk.k[2 * r] = static_cast<uint32_t>(dr.seed) + static_cast<uint32_t>(r) * 0x9E3779B9u;
+    rk.k[2 * r + 1] = static_cast<uint32_t>(dr.seed >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
+  }
+  attn_keep_bits_kernel<<<static_cast<unsigned>(tiles), 512, 0, st>>>(bits, dr, rk, static_cast<int>(sh.seq),
+                                                                      static_cast<int>(sh.seq / T));
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

@@ -58,7 +58,7 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
 // vector = one Philox call), and the 8 per-warp partial rows are added in warp order at the end. One block, fixed
 // order, no atomics => every table row is reproducible. Frequent tokens (a Zipf head) make runs of ~1000 rows.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
@@ -87,41 +87,55 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
       __syncthreads();  // previous batch fully consumed
       pos_s[threadIdx.x] = pos;
       const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
-      // four rows per step: their loads are independent, the additions keep the row order
-      for (int r0 = warp; r0 < n; r0 += 32) {
-        float x[4][NV][8];
-        int64_t rows4[4];
+      // several rows per step: their loads are independent (kept as raw 16-byte pieces until they are added, in row
+      // order, so the sums do not depend on the grouping)
+      constexpr int U = sizeof(T) == 2 ? 4 : 2;    // rows per step
+      constexpr int PV = sizeof(T) == 2 ? 1 : 2;   // 16-byte pieces per 8-element vector
+      for (int r0 = warp; r0 < n; r0 += 8 * U) {
+        uint4 raw[U][NV][PV];
+        int64_t rows_u[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
           const int r = r0 + 8 * u;
-          rows4[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
+          rows_u[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
 #pragma unroll
           for (int i = 0; i < NV; ++i) {
             const int v = lane + 32 * i;
-            if (rows4[u] >= 0 && v < nvec) {
-              if (sizeof(T) == 2) {
-                Elem<__nv_bfloat16>::load_vec(reinterpret_cast<const __nv_bfloat16*>(dy) + rows4[u] + v * 8, x[u][i]);
-              } else {
-                float lo[4], hi[4];
-                Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + rows4[u] + v * 8, lo);
-                Elem<float>::load_vec(reinterpret_cast<const float*>(dy) + rows4[u] + v * 8 + 4, hi);
+            if (rows_u[u] >= 0 && v < nvec) {
+              const uint4* src = reinterpret_cast<const uint4*>(dy + rows_u[u] + v * 8);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { x[u][i][e] = lo[e]; x[u][i][4 + e] = hi[e]; }
-              }
+              for (int q = 0; q < PV; ++q) raw[u][i][q] = src[q];
             }
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (rows4[u] < 0) continue;
+        for (int u = 0; u < U; ++u) {
+          if (rows_u[u] < 0) continue;
 #pragma unroll
           for (int i = 0; i < NV; ++i) {
             const int v = lane + 32 * i;
             if (v < nvec) {
-              uint32_t keep = 0xffu;
-              if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(rows4[u] + v * 8) >> 3, thr);
+              float x[8];
+              if (sizeof(T) == 2) {
+                const uint32_t w[4] = {raw[u][i][0].x, raw[u][i][0].y, raw[u][i][0].z, raw[u][i][0].w};
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[u][i][e] * k_all : 0.f;
+                for (int e = 0; e < 4; ++e) {
+                  x[2 * e] = __uint_as_float(w[e] << 16);
+                  x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                }
+              } else {
+#pragma unroll
+                for (int q = 0; q < PV; ++q) {
+                  x[4 * q] = __uint_as_float(raw[u][i][q].x);
+                  x[4 * q + 1] = __uint_as_float(raw[u][i][q].y);
+                  x[4 * q + 2] = __uint_as_float(raw[u][i][q].z);
+                  x[4 * q + 3] = __uint_as_float(raw[u][i][q].w);
+                }
+              }
+              uint32_t keep = 0xffu;
+              if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(rows_u[u] + v * 8) >> 3, thr);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
             }
           }
         }
