@@ -15,9 +15,9 @@
 //   warp 0      one thread issues the TMA copies: K_j, V_j of an item (2 buffers), Q_i and dO_i of a tile (3 stages)
 //   warp 1      issues S = Q_i K_j^T and dP = dO_i V_j^T (dP goes into the columns S occupied once the scores have
 //               been read out)
-//   warp 2      issues dV += Pd^T dO_i and dK += dS^T Q_i for every tile in stream order (one issuer keeps the
-//               accumulation order fixed)
-//   warp 3      issues the dQ share dS K_j
+//   warp 2      issues dV += Pd^T dO_i for every tile in stream order
+//   warp 3      issues dK += dS^T Q_i in stream order, then the tile's dQ share dS K_j (one issuer per accumulator
+//               keeps the accumulation order fixed)
 //   warps 4..7 / 8..11  two compute groups; group x takes the tiles of the block's tile stream with g % 2 == x, so one
 //               group's exponentials overlap the other's loads, stores and barriers. Thread t owns query row t of
 //               the tile (tensor-memory lane t). It forms P (kept as packed bf16 whose sign bit marks a dropped
@@ -216,13 +216,13 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* pd_ready = bars + 12;      //     Pd is in the group's shared-memory tile (one arrival per warp)
   uint64_t* dv_done = bars + 14;       //     the dV MMA has read it
   uint64_t* ds_ready = bars + 16;      //     dS is in the group's shared-memory tile (one arrival per warp)
-  uint64_t* dkq_done = bars + 18;      //     two arrivals: the dK MMA and the dQ-share MMA have read it
+  uint64_t* dkq_done = bars + 18;      //     the dK and dQ-share MMAs (one issuer, one commit) have read it
   uint64_t* dq_full = bars + 20;
   uint64_t* dq_free = bars + 22;       //     the dQ share has been copied out (one arrival per warp)
-  uint64_t* acc_full = bars + 24;      // the item's last dV / dK MMAs are done
+  uint64_t* acc_full = bars + 24;      // the item's last dV and last dK MMAs are done (two arrivals)
   uint64_t* acc_free = bars + 25;      // dV / dK have been copied out (one arrival per warp of the finishing group)
   uint64_t* qg_full = bars + 26;       // [kQGStages]
-  uint64_t* qg_empty = bars + 29;      // [kQGStages] the tile's dK MMA is done (S, dP, dV came before it)
+  uint64_t* qg_empty = bars + 29;      // [kQGStages] the tile's dV and dK MMAs are done (two arrivals; S, dP came before)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* rk_s = tmem_slot + 2;  // Philox round keys
@@ -236,7 +236,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int pair = i >> 1;  // the per-group barriers come in pairs
       uint32_t count = 1;       // TMA transactions and MMA commits
       if (b == acc_free || pair == 3 || pair == 5 || pair == 6 || pair == 8 || pair == 11) count = 4;  // compute warps
-      if (pair == 1 || pair == 9) count = 2;  // kv_empty, dkq_done: two MMA issuers
+      if (pair == 1 || b == acc_full || i >= 29) count = 2;  // kv_empty, acc_full, qg_empty[]: two MMA commits each
       mbar_init(b, count);
     }
     *abort_flag = 0;
@@ -355,62 +355,53 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (__any_sync(0xffffffffu, stalled(progress, t_idle, 0x2201u))) break;
     }
   } else if (warp == 2) {
-    // ---------------------------------------------------------------- MMA issuer: dV += Pd^T dO and dK += dS^T Q
-    // Two sequences over the stream; each accumulates in stream order, whichever operand is ready goes first.
-    Cursor cv, ck;
-    cv.init(sched);
-    ck.init(sched);
-    long long t_idle = clock64();
-    while (cv.valid || ck.valid) {
-      bool progress = false;
-      if (cv.valid) {
-        const int x = cv.g & 1;
-        bool ready = mbar_try_wait(&pd_ready[x], (cv.g >> 1) & 1);
-        if (ready && cv.first(sched)) ready = mbar_try_wait(acc_free, (cv.ord & 1) ^ 1u);  // previous item copied out
-        if (__all_sync(0xffffffffu, ready)) {
-          tc_fence_after_sync();
-          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes);
-          const uint32_t ga = smem_u32(qg_s + (cv.g % kQGStages) * 2 * kTileBytes + kTileBytes);
-          const uint32_t acc = cv.first(sched) ? 0u : 1u;
-#pragma unroll
-          for (int k16 = 0; k16 < T / 16; ++k16)
-            mma_bf16_ss_elect(tmem + kColDV, desc_p_transposed(wa, k16), desc_rows_as_k(ga, k16), idesc_t, k16 > 0 ? 1u : acc);
-          mma_commit_elect(&dv_done[x]);
-          cv.advance(sched);
-          progress = true;
-        }
-      }
-      if (ck.valid && (!cv.valid || ck.g < cv.g)) {
-        const int x = ck.g & 1;
-        if (__all_sync(0xffffffffu, mbar_try_wait(&ds_ready[x], (ck.g >> 1) & 1))) {
-          tc_fence_after_sync();
-          const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), qa = smem_u32(qg_s + (ck.g % kQGStages) * 2 * kTileBytes);
-          const uint32_t acc = ck.first(sched) ? 0u : 1u;
-#pragma unroll
-          for (int k16 = 0; k16 < T / 16; ++k16)
-            mma_bf16_ss_elect(tmem + kColDK, desc_p_transposed(wa, k16), desc_rows_as_k(qa, k16), idesc_t, k16 > 0 ? 1u : acc);
-          mma_commit_elect(&dkq_done[x]);
-          mma_commit_elect(&qg_empty[ck.g % kQGStages]);
-          if (ck.last(sched)) mma_commit_elect(acc_full);
-          ck.advance(sched);
-          progress = true;
-        }
-      }
-      if (__any_sync(0xffffffffu, stalled(progress, t_idle, 0x2301u))) break;
-    }
-  } else if (warp == 3) {
-    // ---------------------------------------------------------------- MMA issuer: the tile's dQ share dS K_j
+    // ---------------------------------------------------------------- MMA issuer: dV += Pd^T dO (stream order)
     Cursor c;
     c.init(sched);
     bool ok = true;
     while (c.valid && ok) {
-      const int x = c.g & 1;
-      const uint32_t ph = (c.g >> 1) & 1;
-      const bool w = mbar_wait(&ds_ready[x], ph, ctx, 0x2401u) && mbar_wait(&dq_free[x], ph ^ 1u, ctx, 0x2402u);
+      const int x = c.g & 1, st = c.g % kQGStages;
+      bool w = mbar_wait(&pd_ready[x], (c.g >> 1) & 1, ctx, 0x2301u);
+      if (w && c.first(sched)) w = mbar_wait(acc_free, (c.ord & 1) ^ 1u, ctx, 0x2302u);  // previous item copied out
       ok = __all_sync(0xffffffffu, w);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), ka = smem_u32(kv_s + (c.ord & 1) * 2 * kTileBytes);
+      const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), ga = smem_u32(qg_s + st * 2 * kTileBytes + kTileBytes);
+      const uint32_t acc = c.first(sched) ? 0u : 1u;
+#pragma unroll
+      for (int k16 = 0; k16 < T / 16; ++k16)
+        mma_bf16_ss_elect(tmem + kColDV, desc_p_transposed(wa, k16), desc_rows_as_k(ga, k16), idesc_t, k16 > 0 ? 1u : acc);
+      mma_commit_elect(&dv_done[x]);
+      mma_commit_elect(&qg_empty[st]);
+      if (c.last(sched)) mma_commit_elect(acc_full);
+      c.advance(sched);
+    }
+  } else if (warp == 3) {
+    // ---------------------------------------------------------------- MMA issuer: dK += dS^T Q (stream order) and the
+    // tile's dQ share dS K_j; both read dS, so one warp issues them back to back
+    Cursor c;
+    c.init(sched);
+    bool ok = true;
+    while (c.valid && ok) {
+      const int x = c.g & 1, st = c.g % kQGStages;
+      const uint32_t ph = (c.g >> 1) & 1;
+      bool w = mbar_wait(&ds_ready[x], ph, ctx, 0x2401u);
+      // the first dK of an item overwrites the accumulator: the previous item must have been copied out (the dV
+      // issuer waits for the same barrier)
+      if (w && c.first(sched)) w = mbar_wait(acc_free, (c.ord & 1) ^ 1u, ctx, 0x2403u);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t wa = smem_u32(w_s + x * 2 * kTileBytes), qa = smem_u32(qg_s + st * 2 * kTileBytes);
+      const uint32_t ka = smem_u32(kv_s + (c.ord & 1) * 2 * kTileBytes);
+      const uint32_t acc = c.first(sched) ? 0u : 1u;
+#pragma unroll
+      for (int k16 = 0; k16 < T / 16; ++k16)
+        mma_bf16_ss_elect(tmem + kColDK, desc_p_transposed(wa, k16), desc_rows_as_k(qa, k16), idesc_t, k16 > 0 ? 1u : acc);
+      mma_commit_elect(&qg_empty[st]);
+      if (c.last(sched)) mma_commit_elect(acc_full);
+      ok = __all_sync(0xffffffffu, mbar_wait(&dq_free[x], ph ^ 1u, ctx, 0x2402u));  // previous own share copied out
+      if (!ok) break;
 #pragma unroll
       for (int k16 = 0; k16 < T / 16; ++k16)
         mma_bf16_ss_elect(tmem + kColDQ + x * DH, desc_p_kmajor(wa, k16), desc_rows_as_k(ka, k16), idesc_q, k16 > 0);
