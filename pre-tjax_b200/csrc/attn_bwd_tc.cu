@@ -531,14 +531,18 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         pend_part = static_cast<int64_t>(c.bh) * ntri + c.i * (c.i + 1) / 2 + c.kt;
         pend_g = c.g;
 
-        if (c.last(sched)) {  // the item's dV and dK are complete once the MMAs issued so far have run
-          ok = mbar_wait(acc_full, c.ord & 1, ctx, 0x2506u);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
+        if (c.last(sched)) {
+          // The item ends with this tile. Its last dV MMA is already complete (dv_done was awaited before the dS phase),
+          // so dV is copied out first, while the last dK MMA is still running; dK follows once acc_full says so.
           const int64_t kv_row = static_cast<int64_t>(c.kt) * T + row;
 #pragma unroll
           for (int which = 0; which < 2; ++which) {
+            if (which == 1) {
+              ok = mbar_wait(acc_full, c.ord & 1, ctx, 0x2506u);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+            }
+            tc_fence_after_sync();
             const RowView& view = which == 0 ? outv.dv : outv.dk;
             __nv_bfloat16* dst = view.row(c.bh / p.H, c.bh % p.H, kv_row);
 #pragma unroll
@@ -555,6 +559,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               }
             }
           }
+          if (!ok) break;
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_free);
