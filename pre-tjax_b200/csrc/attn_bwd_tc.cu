@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(256)
 attn_bwd_prep_kernel(const RowView d_o, const RowView o_view, const float* __restrict__ row_max,
                      const float* __restrict__ row_sum, float* __restrict__ delta, float* __restrict__ lse2, int S, int H,
                      int64_t rows) {
+  grid_dep_sync();
   const int64_t r = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 3;
   const int part = threadIdx.x & 7;
   float acc = 0.f;
@@ -113,6 +114,7 @@ attn_bwd_prep_kernel(const RowView d_o, const RowView o_view, const float* __res
 // float4 over kt; consecutive threads take consecutive rows.
 __global__ void __launch_bounds__(256)
 attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, int H, int nq, int64_t total_vec) {
+  grid_dep_sync();
   const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (v >= total_vec) return;
   const int row = static_cast<int>(v % T);
@@ -254,6 +256,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);  // Q K^T and dO V^T
   constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);   // Pd^T dO and dS^T Q
@@ -630,7 +633,7 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
   float* delta = part + static_cast<int64_t>(p.BH) * (p.nq * (p.nq + 1) / 2) * T * DH;
   float* lse2 = delta + rows;
   const RowView g_view = make_view(d_o, sh.o_strides), o_view = make_view(o, sh.o_strides);
-  attn_bwd_prep_kernel<<<static_cast<unsigned>((rows * 8 + 255) / 256), 256, 0, st>>>(g_view, o_view, row_max, row_sum,
+  launch_k(attn_bwd_prep_kernel, static_cast<unsigned>((rows * 8 + 255) / 256), 256, 0, st, g_view, o_view, row_max, row_sum,
                                                                                      delta, lse2, p.S, p.H, rows);
   PTJ_CHECK_LAUNCH();
   Sched s;
@@ -641,10 +644,10 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
   s.rounds = (s.total + grid - 1) / grid;
   s.bh_magic = static_cast<uint32_t>(((1ull << 32) + s.BH - 1) / s.BH);
   BwdViews views{make_view(dk, dsh.k_strides), make_view(dv, dsh.v_strides)};
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, tg, delta, lse2, part, views, p, s);
+  launch_k(kern, grid, kThreads, kSmemBytes, st, tq, tk, tv, tg, delta, lse2, part, views, p, s);
   PTJ_CHECK_LAUNCH();
   const int64_t total_vec = rows * (DH / 4);
-  attn_dq_reduce_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, st>>>(part, make_view(dq, dsh.q_strides),
+  launch_k(attn_dq_reduce_kernel, static_cast<unsigned>((total_vec + 255) / 256), 256, 0, st, part, make_view(dq, dsh.q_strides),
                                                                                         p.S, p.H, p.nq, total_vec);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;

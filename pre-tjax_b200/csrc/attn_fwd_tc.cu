@@ -126,6 +126,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem = *tmem_slot;
 
   // the copy / MMA warps hand most of their registers to the softmax warps (whole groups of four warps switch together)
@@ -485,6 +486,7 @@ struct RoundKeys {
 };
 __global__ void __launch_bounds__(512)
 attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, const RoundKeys rk, int S, int nq) {
+  grid_dep_sync();
   // one block per tile (its position is decoded once), one thread per word: 128 rows x 4 words
   const int ntri = nq * (nq + 1) / 2;
   const int64_t tile = blockIdx.x;  // bh * ntri + tri
@@ -528,7 +530,7 @@ int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropou
     rk.k[2 * r] = static_cast<uint32_t>(dr.seed) + static_cast<uint32_t>(r) * 0x9E3779B9u;
     rk.k[2 * r + 1] = static_cast<uint32_t>(dr.seed >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
   }
-  attn_keep_bits_kernel<<<static_cast<unsigned>(tiles), 512, 0, st>>>(bits, dr, rk, static_cast<int>(sh.seq),
+  launch_k(attn_keep_bits_kernel, static_cast<unsigned>(tiles), 512, 0, st, bits, dr, rk, static_cast<int>(sh.seq),
                                                                       static_cast<int>(sh.seq / T));
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
@@ -555,7 +557,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row
   const int grid = s.total < kNumSMs ? s.total : kNumSMs;
   s.rounds = (s.total + grid - 1) / grid;
   s.bh_magic = static_cast<uint32_t>(((1ull << 32) + s.BH - 1) / s.BH);
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p, s);
+  launch_k(kern, grid, kThreads, kSmemBytes, st, tq, tk, tv, make_view(o, sh.o_strides), row_max, row_sum, p, s);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

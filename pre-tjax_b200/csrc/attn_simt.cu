@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ o,
                      float* __restrict__ row_max, float* __restrict__ row_sum, const ptj_attn_shape sh, float scale,
                      AttnDropout dr) {
+  grid_dep_sync();
   __shared__ float qs[kWarpsPerBlock][kMaxD];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int64_t S = sh.seq, D = sh.d_head;
@@ -79,6 +80,7 @@ attn_bwd_simt_kernel(const T* __restrict__ d_o, const T* __restrict__ q, const T
                      const T* __restrict__ v, const T* __restrict__ o, const float* __restrict__ row_max,
                      const float* __restrict__ row_sum, T* __restrict__ dq, T* __restrict__ dk, T* __restrict__ dv,
                      const ptj_attn_shape sh, const ptj_attn_shape dsh, float scale, AttnDropout dr) {
+  grid_dep_sync();
   __shared__ float xs[kWarpsPerBlock][kMaxD];  // MODE 0: q row;  MODE 1: k row
   __shared__ float ys[kWarpsPerBlock][kMaxD];  // MODE 0: dO row; MODE 1: v row
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -202,11 +204,11 @@ int attn_fwd_simt(const void* q, const void* k, const void* v, void* o, float* r
   const float scale = 1.f / sqrtf(static_cast<float>(sh.d_head));
   const int grid = simt_grid(sh.batch * sh.heads * sh.seq);
   if (dtype == PTJ_F32)
-    attn_fwd_simt_kernel<float><<<grid, kWarpsPerBlock * 32, 0, st>>>(
+    launch_k(attn_fwd_simt_kernel<float>, grid, kWarpsPerBlock * 32, 0, st, 
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<float*>(o),
         row_max, row_sum, sh, scale, dr);
   else
-    attn_fwd_simt_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, st>>>(
+    launch_k(attn_fwd_simt_kernel<__nv_bfloat16>, grid, kWarpsPerBlock * 32, 0, st, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
         static_cast<__nv_bfloat16*>(o), row_max, row_sum, sh, scale, dr);
   PTJ_CHECK_LAUNCH();
@@ -219,12 +221,12 @@ static int bwd_simt_typed(const void* d_o, const void* q, const void* k, const v
                           const ptj_attn_shape& sh, const ptj_attn_shape& dsh, const AttnDropout& dr, cudaStream_t st) {
   const float scale = 1.f / sqrtf(static_cast<float>(sh.d_head));
   const int grid = simt_grid(sh.batch * sh.heads * sh.seq);
-  attn_bwd_simt_kernel<T, 0><<<grid, kWarpsPerBlock * 32, 0, st>>>(
+  launch_k(attn_bwd_simt_kernel<T, 0>, grid, kWarpsPerBlock * 32, 0, st, 
       static_cast<const T*>(d_o), static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
       static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv), sh, dsh,
       scale, dr);
   PTJ_CHECK_LAUNCH();
-  attn_bwd_simt_kernel<T, 1><<<grid, kWarpsPerBlock * 32, 0, st>>>(
+  launch_k(attn_bwd_simt_kernel<T, 1>, grid, kWarpsPerBlock * 32, 0, st, 
       static_cast<const T*>(d_o), static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
       static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv), sh, dsh,
       scale, dr);

@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/ptj_b200.h"
 
@@ -20,6 +21,40 @@ extern void count_launch(int n);
       return PTJ_ERR_LAUNCH;                                 \
     }                                                        \
   } while (0)
+
+// Programmatic dependent launch: every kernel of this library is launched so that its blocks may become resident while
+// the previous kernel of the stream is still draining, and calls grid_dep_sync() before its first access to global
+// memory. The call (1) lets the NEXT kernel's blocks start their own set-up once all blocks of this one have reached
+// this point, and (2) waits until every earlier kernel of the stream has completed and its writes are visible.
+// Kernels that allocate tensor memory call it only after their allocation, so a dependent block can never hold
+// tensor memory that a block of an earlier, still running kernel is waiting for. PTJ_PDL=0 in the environment turns
+// the launch attribute off (plain stream order; the device-side call is then a no-op).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PTJ_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+__device__ __forceinline__ void grid_dep_sync() {
+  asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // errors surface through cudaPeekAtLastError
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == PTJ_BF16 ? 2 : 4; }

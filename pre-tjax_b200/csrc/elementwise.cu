@@ -18,6 +18,7 @@ inline int ew_grid(int64_t nvec) {
 template <typename T, int OP>
 __global__ void __launch_bounds__(kEwThreads)
 gelu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n, bool vec) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -42,6 +43,7 @@ template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
 dropout_kernel(const T* __restrict__ x, const T* __restrict__ resid, T* __restrict__ y, int64_t n, bool vec,
                uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -72,6 +74,7 @@ dropout_kernel(const T* __restrict__ x, const T* __restrict__ resid, T* __restri
 
 __global__ void __launch_bounds__(kEwThreads)
 cast_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n, bool vec) {
+  grid_dep_sync();
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t nvec = vec ? n / 8 : 0;
@@ -88,7 +91,7 @@ cast_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int6
 template <typename T, int OP>
 int launch_gelu(const void* a, const void* b, void* out, int64_t n, cudaStream_t st) {
   const bool vec = aligned16(a) && aligned16(out) && (OP == 0 || aligned16(b));
-  gelu_kernel<T, OP><<<ew_grid(n / Elem<T>::kVec), kEwThreads, 0, st>>>(
+  launch_k(gelu_kernel<T, OP>, ew_grid(n / Elem<T>::kVec), kEwThreads, 0, st, 
       static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n, vec);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
@@ -128,11 +131,11 @@ extern "C" int ptj_dropout(const void* x, const void* residual, void* y, int64_t
   const bool vec = aligned16(x) && aligned16(y) && (residual == nullptr || aligned16(residual));
   const uint32_t thr = dropout_threshold16(p);
   if (dtype == PTJ_F32) {
-    dropout_kernel<float><<<ew_grid(n / 4), kEwThreads, 0, st>>>(
+    launch_k(dropout_kernel<float>, ew_grid(n / 4), kEwThreads, 0, st, 
         static_cast<const float*>(x), static_cast<const float*>(residual), static_cast<float*>(y), n, vec, thr,
         1.f - p, train, seed, stream_id);
   } else if (dtype == PTJ_BF16) {
-    dropout_kernel<__nv_bfloat16><<<ew_grid(n / 8), kEwThreads, 0, st>>>(
+    launch_k(dropout_kernel<__nv_bfloat16>, ew_grid(n / 8), kEwThreads, 0, st, 
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
         static_cast<__nv_bfloat16*>(y), n, vec, thr, 1.f - p, train, seed, stream_id);
   } else {
@@ -147,7 +150,7 @@ extern "C" int ptj_cast_f32_to_bf16(const float* src, void* dst_bf16, int64_t n,
   if (n == 0) return PTJ_OK;
   if (!src || !dst_bf16) return PTJ_ERR_BAD_SHAPE;
   const bool vec = aligned16(src) && aligned16(dst_bf16);
-  cast_kernel<<<ew_grid(n / 8), kEwThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(cast_kernel, ew_grid(n / 8), kEwThreads, 0, static_cast<cudaStream_t>(stream), 
       src, static_cast<__nv_bfloat16*>(dst_bf16), n, vec);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;

@@ -12,6 +12,7 @@ __global__ void __launch_bounds__(256)
 embed_fwd_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ w_emb, const TW* __restrict__ w_pos,
                  T* __restrict__ y, int64_t tokens, int64_t seq, int dim, int64_t vocab, float scale, uint32_t thr,
                  float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  grid_dep_sync();
   const int64_t total = tokens * dim;
   for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x * 4) {
@@ -39,6 +40,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t batch, int64_t seq, int dim,
                uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  grid_dep_sync();
   const int64_t total = seq * dim;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -62,6 +64,7 @@ __global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
+  grid_dep_sync();
   extern __shared__ float part[];  // [8][dim]
   __shared__ int32_t pos_s[256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -165,6 +168,7 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
 
 // rows of the table that no token hit are zeroed when not accumulating
 __global__ void zero_kernel(float* __restrict__ p, int64_t n) {
+  grid_dep_sync();
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x)
     p[i] = 0.f;
@@ -176,6 +180,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 colsum_stage1_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols, int64_t ld,
                      int64_t chunk) {
+  grid_dep_sync();
   constexpr int V = VEC ? Elem<T>::kVec : 1;
   const int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // column group
   const int64_t c0 = g * V;
@@ -208,6 +213,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_stage1_rows_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols, int64_t ld,
                           int64_t chunk) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   __shared__ float red[8][32][V + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -243,6 +249,7 @@ colsum_stage1_rows_kernel(const T* __restrict__ x, float* __restrict__ partial, 
 // stage 2: a block owns 32 columns; its 8 warps sum strided subsets of the chunk rows, added in warp order.
 __global__ void __launch_bounds__(256)
 colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t cols, int nchunks) {
+  grid_dep_sync();
   __shared__ float red[8][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
@@ -290,7 +297,7 @@ int launch_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_p
   {                                                                                                              \
     if (smem > 48 * 1024)                                                                                        \
       cudaFuncSetAttribute(embed_bwd_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    embed_bwd_kernel<T, NV><<<grid, 256, smem, st>>>(static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, tokens, \
+    launch_k(embed_bwd_kernel<T, NV>, grid, 256, smem, st, static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, tokens, \
                                                      dim, vocab, scale, thr, eval_scale, train, seed, stream_id); \
   }
   if (nv <= 1) PTJ_EMB(1) else if (nv <= 2) PTJ_EMB(2) else if (nv <= 4) PTJ_EMB(4) else if (nv <= 8) PTJ_EMB(8) else PTJ_EMB(16)
@@ -316,7 +323,7 @@ extern "C" int ptj_embed_fwd(const int32_t* ids, const void* w_emb, const void* 
   const float scale = sqrtf(static_cast<float>(dim));
   const uint32_t thr = dropout_threshold16(p);
 #define PTJ_EMBED(TW, T)                                                                                      \
-  embed_fwd_kernel<TW, T><<<grid, 256, 0, st>>>(ids, static_cast<const TW*>(w_emb), static_cast<const TW*>(w_pos), \
+  launch_k(embed_fwd_kernel<TW, T>, grid, 256, 0, st, ids, static_cast<const TW*>(w_emb), static_cast<const TW*>(w_pos), \
                                                 static_cast<T*>(y), tokens, seq, (int)dim, vocab, scale, thr,  \
                                                 1.f - p, train, seed, stream_id)
   if (wdtype == PTJ_F32 && dtype == PTJ_F32) PTJ_EMBED(float, float);
@@ -342,7 +349,7 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
   const float scale = sqrtf(static_cast<float>(dim));
   const uint32_t thr = dropout_threshold16(p);
   if (!accumulate) {
-    zero_kernel<<<flat_grid(vocab * dim, 256 * 4), 256, 0, st>>>(d_w_emb, vocab * dim);
+    launch_k(zero_kernel, flat_grid(vocab * dim, 256 * 4), 256, 0, st, d_w_emb, vocab * dim);
     PTJ_CHECK_LAUNCH();
   }
   const int grid_e = flat_grid(tokens, 1);  // one block per sorted position (only run heads do work)
@@ -352,14 +359,14 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
                                 stream_id, grid_e, st) != PTJ_OK)
       return PTJ_ERR_LAUNCH;
     PTJ_CHECK_LAUNCH();
-    pos_bwd_kernel<float><<<grid_p, 256, 0, st>>>(static_cast<const float*>(dy), d_w_pos, batch, seq, (int)dim, thr,
+    launch_k(pos_bwd_kernel<float>, grid_p, 256, 0, st, static_cast<const float*>(dy), d_w_pos, batch, seq, (int)dim, thr,
                                                   1.f - p, train, seed, stream_id);
   } else {
     if (launch_embed_bwd<__nv_bfloat16>(dy, ids, sorted_pos, d_w_emb, tokens, (int)dim, vocab, scale, thr, 1.f - p, train,
                                         seed, stream_id, grid_e, st) != PTJ_OK)
       return PTJ_ERR_LAUNCH;
     PTJ_CHECK_LAUNCH();
-    pos_bwd_kernel<__nv_bfloat16><<<grid_p, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dy), d_w_pos, batch, seq,
+    launch_k(pos_bwd_kernel<__nv_bfloat16>, grid_p, 256, 0, st, static_cast<const __nv_bfloat16*>(dy), d_w_pos, batch, seq,
                                                           (int)dim, thr, 1.f - p, train, seed, stream_id);
   }
   PTJ_CHECK_LAUNCH();
@@ -386,16 +393,16 @@ extern "C" int ptj_colsum(const void* x, float* out, float* scratch, size_t scra
   dim3 grid(static_cast<unsigned>(ceil_div(groups, 128)), static_cast<unsigned>(nchunks));
   dim3 grid_rows(static_cast<unsigned>(ceil_div(groups, 32)), static_cast<unsigned>(nchunks));
   if (dtype == PTJ_F32) {
-    if (vec && colsum_split_rows(cols)) colsum_stage1_rows_kernel<float><<<grid_rows, 256, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
-    else if (vec) colsum_stage1_kernel<float, true><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
-    else colsum_stage1_kernel<float, false><<<grid, 128, 0, st>>>(static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    if (vec && colsum_split_rows(cols)) launch_k(colsum_stage1_rows_kernel<float>, grid_rows, 256, 0, st, static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    else if (vec) launch_k(colsum_stage1_kernel<float, true>, grid, 128, 0, st, static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
+    else launch_k(colsum_stage1_kernel<float, false>, grid, 128, 0, st, static_cast<const float*>(x), scratch, rows, cols, ld, chunk);
   } else {
-    if (vec && colsum_split_rows(cols)) colsum_stage1_rows_kernel<__nv_bfloat16><<<grid_rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
-    else if (vec) colsum_stage1_kernel<__nv_bfloat16, true><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
-    else colsum_stage1_kernel<__nv_bfloat16, false><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    if (vec && colsum_split_rows(cols)) launch_k(colsum_stage1_rows_kernel<__nv_bfloat16>, grid_rows, 256, 0, st, static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    else if (vec) launch_k(colsum_stage1_kernel<__nv_bfloat16, true>, grid, 128, 0, st, static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
+    else launch_k(colsum_stage1_kernel<__nv_bfloat16, false>, grid, 128, 0, st, static_cast<const __nv_bfloat16*>(x), scratch, rows, cols, ld, chunk);
   }
   PTJ_CHECK_LAUNCH();
-  colsum_stage2_kernel<<<static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st>>>(scratch, out, cols, nchunks);
+  launch_k(colsum_stage2_kernel, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, scratch, out, cols, nchunks);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

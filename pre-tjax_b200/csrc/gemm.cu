@@ -112,6 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles = p.num_m * p.num_n;
@@ -320,6 +321,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
   tc_fence_after_sync();
+  grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
@@ -465,6 +467,7 @@ template <typename TOut, int W>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restrict__ c, const float* __restrict__ bias, int64_t M,
                      int64_t N, int64_t ldc, int split_k, int accumulate) {
+  grid_dep_sync();
   const int64_t total = M * N;
   for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * W; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x * W) {
@@ -497,6 +500,7 @@ template <typename TOut>
 __global__ void __launch_bounds__(128)
 gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t sam, int64_t sak, int64_t sbn,
                  int64_t sbk, int64_t M, int64_t N, int64_t K, const EpilogueParams ep) {
+  grid_dep_sync();
   __shared__ float As[SM_BK][SM_BM + 4];
   __shared__ float Bs[SM_BK][SM_BN + 4];
   const int tid = threadIdx.x;
@@ -549,7 +553,7 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
   }
   const int total = p.num_m * p.num_n * p.split_k;
   const int grid = total < kNumSMs ? total : kNumSMs;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+  launch_k(kern, grid, kGemmThreads, Cfg::kSmemBytes, st, ta, tb, p);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
@@ -565,11 +569,11 @@ int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int6
   const int acc = epilogue == PTJ_EPI_ACCUM;
   const int g = static_cast<int>(blocks);
   if (out_dtype == PTJ_F32) {
-    if (w4) splitk_reduce_kernel<float, 4><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
-    else splitk_reduce_kernel<float, 1><<<g, 256, 0, st>>>(workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+    if (w4) launch_k(splitk_reduce_kernel<float, 4>, g, 256, 0, st, workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
+    else launch_k(splitk_reduce_kernel<float, 1>, g, 256, 0, st, workspace, static_cast<float*>(c), bias, M, N, ldc, split_k, acc);
   } else {
-    if (w4) splitk_reduce_kernel<__nv_bfloat16, 4><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
-    else splitk_reduce_kernel<__nv_bfloat16, 1><<<g, 256, 0, st>>>(workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    if (w4) launch_k(splitk_reduce_kernel<__nv_bfloat16, 4>, g, 256, 0, st, workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
+    else launch_k(splitk_reduce_kernel<__nv_bfloat16, 1>, g, 256, 0, st, workspace, static_cast<__nv_bfloat16*>(c), bias, M, N, ldc, split_k, 0);
   }
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
@@ -590,13 +594,15 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParam
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
@@ -667,10 +673,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
     dim3 grid(static_cast<unsigned>(ceil_div(N, SM_BN)), static_cast<unsigned>(ceil_div(M, SM_BM)));
     if (grid.y > 65535) return PTJ_ERR_BAD_SHAPE;
     if (out_dtype == PTJ_F32)
-      gemm_simt_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b), sam, sak,
+      launch_k(gemm_simt_kernel<float>, grid, 128, 0, st, static_cast<const float*>(a), static_cast<const float*>(b), sam, sak,
                                                     sbn, sbk, M, N, K, ep);
     else
-      gemm_simt_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b),
+      launch_k(gemm_simt_kernel<__nv_bfloat16>, grid, 128, 0, st, static_cast<const float*>(a), static_cast<const float*>(b),
                                                             sam, sak, sbn, sbk, M, N, K, ep);
     PTJ_CHECK_LAUNCH();
     return PTJ_OK;

@@ -38,6 +38,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kLnThreads, NV <= 4 ? 4 : 2)
 ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               T* __restrict__ y, int64_t rows, int dim) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   const int lane = threadIdx.x & 31;
   const int nvec = dim / V;
@@ -94,6 +95,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLnThreads)
 ln_fwd_generic_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                       const float* __restrict__ beta, T* __restrict__ y, int64_t rows, int dim) {
+  grid_dep_sync();
   __shared__ float red[33];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + row * dim;
@@ -130,6 +132,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kLnThreads, (NV * Elem<T>::kVec <= 32) ? 2 : 1)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
               const T* dx_add, T* dx, float* __restrict__ partial, int64_t rows, int dim, const LnMask mk) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   constexpr int kSlots = NV * V * 32;   // per-warp accumulator slots per quantity
   extern __shared__ float sm_acc[];     // [kLnWarps][2][kSlots]
@@ -273,6 +276,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLnThreads)
 ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                       const T* dx_add, T* dx, float* __restrict__ partial, int64_t rows, int dim) {
+  grid_dep_sync();
   __shared__ float red[33];
   float* out = partial ? partial + static_cast<size_t>(blockIdx.x) * 2 * dim : nullptr;
   if (out)
@@ -319,6 +323,7 @@ ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
                        int nblocks, int dim) {
+  grid_dep_sync();
   // 8 columns x 32 row groups per block: many small blocks, each row group sums every 32nd partial row in order
   __shared__ float red[32][9];
   const int col = threadIdx.x & 7, grp = threadIdx.x >> 3;
@@ -342,12 +347,12 @@ int launch_fwd(const T* x, const float* gamma, const float* beta, T* y, int64_t 
   const bool vec_ok = dim % V == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   const int nv = vec_ok ? static_cast<int>(ceil_div(dim / V, 32)) : 99;
   const int grid = ln_grid(rows);
-#define PTJ_LN_FWD(NV) case NV: ln_fwd_kernel<T, NV><<<grid, kLnThreads, 0, st>>>(x, gamma, beta, y, rows, dim); break;
+#define PTJ_LN_FWD(NV) case NV: launch_k(ln_fwd_kernel<T, NV>, grid, kLnThreads, 0, st, x, gamma, beta, y, rows, dim); break;
   switch (nv) {
     PTJ_LN_FWD(1) PTJ_LN_FWD(2) PTJ_LN_FWD(3) PTJ_LN_FWD(4) PTJ_LN_FWD(5) PTJ_LN_FWD(6) PTJ_LN_FWD(7) PTJ_LN_FWD(8)
     default: {
       const int g = static_cast<int>(rows < kNumSMs * 8 ? rows : kNumSMs * 8);
-      ln_fwd_generic_kernel<T><<<g, kLnThreads, 0, st>>>(x, gamma, beta, y, rows, dim);
+      launch_k(ln_fwd_generic_kernel<T>, g, kLnThreads, 0, st, x, gamma, beta, y, rows, dim);
     }
   }
 #undef PTJ_LN_FWD
@@ -369,18 +374,18 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
   case NV:                                                                                               \
     if (smem > 48 * 1024)                                                                                \
       cudaFuncSetAttribute(ln_bwd_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    ln_bwd_kernel<T, NV><<<grid, kLnThreads, smem, st>>>(dy, x, gamma, dx_add, dx, partial, rows, dim, mk);       \
+    launch_k(ln_bwd_kernel<T, NV>, grid, kLnThreads, smem, st, dy, x, gamma, dx_add, dx, partial, rows, dim, mk);       \
     break;
   switch (nv) {
     PTJ_LN_BWD(1) PTJ_LN_BWD(2) PTJ_LN_BWD(3) PTJ_LN_BWD(4) PTJ_LN_BWD(5) PTJ_LN_BWD(6) PTJ_LN_BWD(7) PTJ_LN_BWD(8)
     default:
       if (mk.out != nullptr) return PTJ_ERR_UNSUPPORTED;  // the masked output needs vector-aligned rows of <= 8 x 32 vectors
-      ln_bwd_generic_kernel<T><<<grid, kLnThreads, 0, st>>>(dy, x, gamma, dx_add, dx, partial, rows, dim);
+      launch_k(ln_bwd_generic_kernel<T>, grid, kLnThreads, 0, st, dy, x, gamma, dx_add, dx, partial, rows, dim);
   }
 #undef PTJ_LN_BWD
   PTJ_CHECK_LAUNCH();
   if (partial != nullptr) {
-    ln_bwd_finalize_kernel<<<static_cast<int>(ceil_div(2 * dim, 8)), 256, 0, st>>>(partial, dgamma, dbeta, grid, dim);
+    launch_k(ln_bwd_finalize_kernel, static_cast<int>(ceil_div(2 * dim, 8)), 256, 0, st, partial, dgamma, dbeta, grid, dim);
     PTJ_CHECK_LAUNCH();
   }
   return PTJ_OK;

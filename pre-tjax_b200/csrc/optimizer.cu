@@ -19,6 +19,7 @@ inline int opt_grid(int64_t nvec) {
 
 __global__ void __launch_bounds__(kOptThreads)
 sumsq_stage1_kernel(const float* __restrict__ x, float* __restrict__ partial, int64_t n) {
+  grid_dep_sync();
   __shared__ float red[33];
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -35,6 +36,7 @@ sumsq_stage1_kernel(const float* __restrict__ x, float* __restrict__ partial, in
 }
 __global__ void __launch_bounds__(1024)
 sumsq_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks) {
+  grid_dep_sync();
   __shared__ float red[33];
   float s = 0.f;
   for (int i = threadIdx.x; i < nblocks; i += blockDim.x) s += partial[i];
@@ -47,6 +49,7 @@ adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restri
              __nv_bfloat16* __restrict__ shadow, int64_t n, const int64_t* __restrict__ seg_start,
              const uint8_t* __restrict__ seg_decay, int nseg, float lr, float beta1, float beta2, float eps, float wd,
              float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ sumsq, float max_norm) {
+  grid_dep_sync();
   __shared__ int64_t s_start[kMaxSegments + 1];
   __shared__ uint8_t s_decay[kMaxSegments];
   if (nseg > 0) {  // the segment tables may be null when there are no segments
@@ -119,9 +122,9 @@ extern "C" int ptj_sumsq(const float* x, float* out, float* scratch, size_t scra
   }
   if (!scratch || scratch_floats < ptj_sumsq_scratch_floats(n)) return PTJ_ERR_WORKSPACE;
   const int grid = opt_grid(n / 4);
-  sumsq_stage1_kernel<<<grid, kOptThreads, 0, st>>>(x, scratch, n);
+  launch_k(sumsq_stage1_kernel, grid, kOptThreads, 0, st, x, scratch, n);
   PTJ_CHECK_LAUNCH();
-  sumsq_stage2_kernel<<<1, 1024, 0, st>>>(scratch, out, grid);
+  launch_k(sumsq_stage2_kernel, 1, 1024, 0, st, scratch, out, grid);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
@@ -140,7 +143,7 @@ extern "C" int ptj_adamw(float* p, const float* g, float* m, float* v, void* sha
   // bias corrections in double on the host: 1 - b^t loses all precision in float for t beyond a few thousand
   const float inv_bc1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta1), static_cast<double>(t))));
   const float inv_bc2 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta2), static_cast<double>(t))));
-  adamw_kernel<<<opt_grid(n / 4), kOptThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(adamw_kernel, opt_grid(n / 4), kOptThreads, 0, static_cast<cudaStream_t>(stream), 
       p, g, m, v, static_cast<__nv_bfloat16*>(shadow_bf16), n, seg_start, seg_decay, nseg, lr, beta1, beta2, eps,
       weight_decay, inv_bc1, inv_bc2, grad_scale, sumsq, max_norm);
   PTJ_CHECK_LAUNCH();

@@ -102,6 +102,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 log_softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t cols, int64_t ld_x,
                        int64_t ld_y, bool vec) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   __shared__ float red[33];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -127,6 +128,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 log_softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx, int64_t rows,
                        int64_t cols, int64_t ld, bool vec) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   __shared__ float red[33];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -163,6 +165,7 @@ log_softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
 }
 
 __global__ void count_valid_kernel(const int32_t* __restrict__ labels, int64_t rows, float* __restrict__ n_valid) {
+  grid_dep_sync();
   __shared__ float red[33];
   float c = 0.f;
   for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) c += labels[i] != 0 ? 1.f : 0.f;
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(kRowThreads)
 cross_entropy_kernel(const int32_t* __restrict__ labels, const T* logits, T* dlogits,
                      float* __restrict__ row_stats, const float* __restrict__ n_valid, int64_t rows, int64_t cols,
                      int64_t ld, bool vec) {
+  grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   __shared__ float red[33];
   __shared__ int64_t red_arg[kRowThreads / 32];
@@ -230,6 +234,7 @@ cross_entropy_kernel(const int32_t* __restrict__ labels, const T* logits, T* dlo
 
 __global__ void ce_finalize_kernel(const float* __restrict__ row_stats, const float* __restrict__ n_valid,
                                    int64_t rows, float* __restrict__ out3) {
+  grid_dep_sync();
   __shared__ float red[33];
   float l = 0.f, h = 0.f;
   for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) {
@@ -267,10 +272,10 @@ extern "C" int ptj_log_softmax_fwd(const void* x, void* y, int64_t rows, int64_t
   if (!x || !y) return PTJ_ERR_BAD_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == PTJ_F32) {
-    log_softmax_fwd_kernel<float><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(log_softmax_fwd_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const float*>(x), static_cast<float*>(y), rows, cols, ld_x, ld_y, same_phase<float>(x, ld_x, y, ld_y));
   } else if (dtype == PTJ_BF16) {
-    log_softmax_fwd_kernel<__nv_bfloat16><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(log_softmax_fwd_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, cols, ld_x, ld_y,
         same_phase<__nv_bfloat16>(x, ld_x, y, ld_y));
   } else {
@@ -288,11 +293,11 @@ extern "C" int ptj_log_softmax_bwd(const void* dy, const void* x, void* dx, int6
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == PTJ_F32) {
     const bool vec = same_phase<float>(x, ld, dy, ld) && same_phase<float>(x, ld, dx, ld);
-    log_softmax_bwd_kernel<float><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(log_softmax_bwd_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<float*>(dx), rows, cols, ld, vec);
   } else if (dtype == PTJ_BF16) {
     const bool vec = same_phase<__nv_bfloat16>(x, ld, dy, ld) && same_phase<__nv_bfloat16>(x, ld, dx, ld);
-    log_softmax_bwd_kernel<__nv_bfloat16><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(log_softmax_bwd_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(dx),
         rows, cols, ld, vec);
   } else {
@@ -310,20 +315,20 @@ extern "C" int ptj_cross_entropy(const int32_t* labels, const void* logits, void
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (count_in_kernel) {
-    count_valid_kernel<<<1, 1024, 0, st>>>(labels, rows, n_valid);
+    launch_k(count_valid_kernel, 1, 1024, 0, st, labels, rows, n_valid);
     PTJ_CHECK_LAUNCH();
   }
   if (dtype == PTJ_F32) {
-    cross_entropy_kernel<float><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(cross_entropy_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         labels, static_cast<const float*>(logits), static_cast<float*>(dlogits), row_stats, n_valid, rows, cols, ld,
         same_phase<float>(logits, ld, dlogits, ld));
   } else {
-    cross_entropy_kernel<__nv_bfloat16><<<row_grid(rows), kRowThreads, 0, st>>>(
+    launch_k(cross_entropy_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
         labels, static_cast<const __nv_bfloat16*>(logits), static_cast<__nv_bfloat16*>(dlogits), row_stats, n_valid,
         rows, cols, ld, same_phase<__nv_bfloat16>(logits, ld, dlogits, ld));
   }
   PTJ_CHECK_LAUNCH();
-  ce_finalize_kernel<<<1, 1024, 0, st>>>(row_stats, n_valid, rows, out3);
+  launch_k(ce_finalize_kernel, 1, 1024, 0, st, row_stats, n_valid, rows, out3);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
