@@ -218,4 +218,49 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   return fmaf(0.5f * x, dt, fmaf(0.5f, t, 0.5f));
 }
 
+// Two-wide forms for the bf16 GEMM epilogues (hardware tanh, packed fp32 arithmetic: half the issue slots).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ void gelu_tanh_x2(float& x0, float& x1) {
+  const float k = 0.7978845608028654f, kc = 0.7978845608028654f * 0.044715f;
+  const uint64_t x = f2_pack(x0, x1);
+  const uint64_t u = f2_mul(x, f2_fma(f2_mul(x, x), f2_pack(kc, kc), f2_pack(k, k)));
+  float u0, u1;
+  f2_unpack(u, u0, u1);
+  const uint64_t t = f2_pack(tanh_sel<true>(u0), tanh_sel<true>(u1));
+  const uint64_t hx = f2_mul(x, f2_pack(0.5f, 0.5f));
+  f2_unpack(f2_fma(hx, t, hx), x0, x1);
+}
+// g *= gelu'(x) for two elements
+__device__ __forceinline__ void gelu_tanh_grad_mul_x2(float& g0, float& g1, float xa, float xb) {
+  const float k = 0.7978845608028654f, kc = 0.7978845608028654f * 0.044715f;
+  const uint64_t x = f2_pack(xa, xb);
+  const uint64_t x2 = f2_mul(x, x);
+  const uint64_t u = f2_mul(x, f2_fma(x2, f2_pack(kc, kc), f2_pack(k, k)));
+  float u0, u1;
+  f2_unpack(u, u0, u1);
+  const uint64_t t = f2_pack(tanh_sel<true>(u0), tanh_sel<true>(u1));
+  const uint64_t one = f2_pack(1.f, 1.f), half = f2_pack(0.5f, 0.5f);
+  const uint64_t nt = f2_mul(t, f2_pack(-1.f, -1.f));
+  const uint64_t dt = f2_mul(f2_fma(nt, t, one), f2_fma(x2, f2_pack(3.f * kc, 3.f * kc), f2_pack(k, k)));
+  const uint64_t d = f2_fma(f2_mul(x, half), dt, f2_fma(half, t, half));
+  f2_unpack(f2_mul(f2_pack(g0, g1), d), g0, g1);
+}
+
 }  // namespace ptj

@@ -22,18 +22,28 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kEpilogueWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+#ifndef PTJ_GEMM_EPI_WARPS
+#define PTJ_GEMM_EPI_WARPS 8
+#endif
+constexpr int kEpilogueWarps = PTJ_GEMM_EPI_WARPS;     // a multiple of 4: warp w may only read tensor-memory lanes 32*(w%4)..
+constexpr int kWarpsPerQuarter = kEpilogueWarps / 4;   // these warps share a lane quarter and take its 32-column chunks in turn
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, the rest: epilogue
+constexpr int kSmemLimit = 227 * 1024;
+static_assert(kStripBytes % 512 == 0, "tile stores with the 64-byte swizzle need 512-byte aligned strips");
+constexpr int chunks_per_warp(int bn) { return (bn / 32 + kWarpsPerQuarter - 1) / kWarpsPerQuarter; }
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStripsBytes + 1024 + kBarrierBytes;
+  static constexpr int kBiasBytes = kEpilogueWarps * chunks_per_warp(BN) * 128;  // each epilogue warp's bias slices
+  static constexpr int kFixedBytes = kStripsBytes + kBiasBytes + 1024 + kBarrierBytes;
+  static constexpr int kFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kFit < 6 ? kFit : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
   static constexpr int kTmemCols = 512;     // two accumulator buffers, the second at column 256
   static constexpr int kAccStride = 256;
 };
@@ -44,21 +54,66 @@ struct GemmParams {
   int num_m, num_n, num_kb, split_k;
   float* workspace;  // [split_k, M, N] partial sums when split_k > 1
   int out_bf16;
-  int debug;  // timing experiments only (results are garbage): 1 = no TMA copies, 2 = no MMAs
+  int tma_store;  // outputs leave through tensor-map tile stores (bf16 output, 16-byte aligned rows, K not split)
+  int debug;  // timing experiments only (results are garbage), bits: 1 = no TMA copies, 2 = no MMAs, 4 = no epilogue
   unsigned int* fault;
 };
+
+// Tensor maps of the outputs (C and, for the GELU epilogue, the saved pre-activation): boxes of 32 rows x 32 bf16,
+// 64-byte swizzle.
+struct alignas(64) StoreMaps {
+  CUtensorMap c, x;
+};
+
+// One 32 x 32 bf16 block, one row per lane, leaves through the tensor map: rows are parked densely (64 bytes each) in
+// the warp's strip (swizzled) and ONE lane issues an asynchronous tile store, so no warp waits on the memory system. The strip
+// may only be rewritten after bulk_wait_read_all() by that lane. All lanes must call.
+__device__ __forceinline__ void warp_store_block_tma(uint8_t* strip, const CUtensorMap* map, int64_t row0, int64_t n0,
+                                                     const float (&v)[32], int lane) {
+  // 64-byte swizzle of the tensor map: the 16-byte piece q of row r lies at piece q ^ ((r >> 1) & 3), which also makes
+  // the eight lanes of a store phase hit eight different bank groups (the strip starts on a 512-byte boundary)
+  uint8_t* mine = strip + lane * 64;
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(mine + ((q ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map, strip, static_cast<int>(n0), static_cast<int>(row0));
+    bulk_commit_group();
+  }
+}
 
 // Epilogue of one 32-row x 32-column block of an accumulator tile (one row per lane): arithmetic per thread, stores
 // through the warp's staging strip when the block is full and rows are 16-byte aligned, else per thread.
 template <typename TOut>
 __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t* strip, int64_t row0, int64_t row,
-                                              int64_t n0, float (&acc)[32], int lane) {
-  const bool inside = epilogue_pre<TOut, 32>(ep, row, n0, acc);
+                                              int64_t n0, float (&acc)[32], int lane, const float* bias_s,
+                                              const StoreMaps* maps) {
+  // (warp-uniform) only full-width blocks: at a ragged right edge the tile store was seen to write the whole 16-byte
+  // piece that holds the last valid column, i.e. up to seven padding columns
+  const bool use_tma = maps != nullptr && sizeof(TOut) == 2 && row0 < ep.M && n0 + 32 <= ep.N;
+  if (maps != nullptr) {
+    // the previous block's tile store must have read the strip before anything overwrites it
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+  }
+  const bool inside = epilogue_pre<TOut, 32>(ep, row, n0, acc, bias_s);
   TOut* c = static_cast<TOut*>(ep.c);
   TOut* aux_out = static_cast<TOut*>(ep.aux_out);
   const bool want_pre = ep.mode == PTJ_EPI_GELU && aux_out != nullptr;
   const bool staged = ep.vec_ok && n0 + 32 <= ep.N;  // warp-uniform
-  if (want_pre) {
+  if (want_pre && use_tma) {
+    warp_store_block_tma(strip, &maps->x, row0, n0, acc, lane);
+  } else if (want_pre) {
     if (staged) warp_store_block<TOut>(strip, aux_out, ep.ldc, row0, n0, ep.M, acc, lane);
     else if (inside) store_row<TOut, 32>(aux_out + row * ep.ldc, n0, ep.N, false, acc);
   }
@@ -68,6 +123,14 @@ __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t*
     else if (inside) load_row<TOut, 32>(static_cast<const TOut*>(sp) + row * ep.ldc, n0, ep.N, false, side);
   }
   if (inside) epilogue_post<TOut, 32>(ep, row, n0, acc, side);
+  if (use_tma) {
+    if (want_pre) {
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+    }
+    warp_store_block_tma(strip, &maps->c, row0, n0, acc, lane);
+    return;
+  }
   if (staged) warp_store_block<TOut>(strip, c, ep.ldc, row0, n0, ep.M, acc, lane);
   else if (inside) store_row<TOut, 32>(c + row * ep.ldc, n0, ep.N, false, acc);
 }
@@ -75,12 +138,13 @@ __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t*
 template <int BN, bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ StoreMaps smaps, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes);
+  float* bias_smem = reinterpret_cast<float*>(strips + Cfg::kStripsBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes + Cfg::kBiasBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + Cfg::kStages;
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -126,11 +190,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const int split = item / tiles, tile = item - split * tiles;
         const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
-        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
+        if (p.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0101u)) { ok = false; break; }
-          if (p.debug == 1) {
+          if (p.debug & 1) {
             mbar_arrive(&full[stage]);
             if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
             continue;
@@ -165,8 +232,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
         const int split = item / tiles;
-        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
+        if (p.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        }
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
         if (!mbar_wait(&tmem_empty[buf], aphase ^ 1u, ctx, 0x0201u)) { ok = false; break; }
@@ -183,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                             : smem_desc_sw128(sa + k4 * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? smem_desc_sw128(sb + k4 * 32, 16, 1024)
                                             : smem_desc_sw128(sb + k4 * 2048, 8192, 1024);
-            if (p.debug != 2) mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+            if (!(p.debug & 2)) mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
@@ -193,8 +263,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int half = (warp - 2) >> 2;  // two warps share a lane quarter and split the tile's columns
-    constexpr int kChunks = BN / 64;   // 32-column chunks per warp
+    const int sub = (warp - 2) >> 2;   // position among the warps that share this lane quarter
+    constexpr int kChunks = chunks_per_warp(BN);  // this warp takes chunks sub, sub + kWarpsPerQuarter, ...
     int it = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
@@ -202,6 +272,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
+      float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
+      const bool bias_staged = (p.ep.tune & 1) && p.ep.bias != nullptr && p.split_k == 1;
+      if (bias_staged) {
+        // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) {
+          const int64_t n = static_cast<int64_t>(n_blk) * BN + (sub + j * kWarpsPerQuarter) * 32 + lane;
+          wbias[j * 32 + lane] = n < p.N ? __ldg(p.ep.bias + n) : 0.f;
+        }
+        __syncwarp();
+      }
       ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0301u);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
@@ -209,17 +291,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int64_t row0 = static_cast<int64_t>(m_blk) * BM + quarter * 32;
       const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(buf * Cfg::kAccStride + half * (BN / 2));
+                             static_cast<uint32_t>(buf * Cfg::kAccStride);
 #pragma unroll 1
-      for (int chunk = 0; chunk < kChunks; ++chunk) {
+      for (int chunk = 0; chunk < ((p.debug & 4) ? 0 : kChunks); ++chunk) {
+        const int col = (sub + chunk * kWarpsPerQuarter) * 32;  // first column of this chunk within the tile
+        if (col >= BN) break;
         uint32_t r[32];
-        tmem_ld_32x32(taddr + chunk * 32, r);
+        tmem_ld_32x32(taddr + col, r);
         tmem_ld_wait();
         float acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + half * (BN / 2) + chunk * 32;
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
         uint8_t* strip = strips + (warp - 2) * kStripBytes;
+        const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
           if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
@@ -230,15 +315,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
           }
         } else if (p.out_bf16) {
-          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane);
+          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane, bias_c, p.tma_store ? &smaps : nullptr);
         } else {
-          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane);
+          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
+    if (lane == 0) bulk_wait_all();  // this lane's tile stores are complete before the block may exit
   }
 
   __syncwarp();
@@ -266,13 +352,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // "accumulator drained" barrier. No TMA multicast is used anywhere.
 template <int BN>
 struct PairCfg {
-  static constexpr int kStages = BN == 256 ? 6 : 8;
   static constexpr int kABytes = BM * BK * 2;        // per CTA: 128 rows of A
   static constexpr int kBBytes = (BN / 2) * BK * 2;  // per CTA: half of the tile's B rows
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStripsBytes + 1024 + kBarrierBytes;
+  static constexpr int kBiasBytes = kEpilogueWarps * chunks_per_warp(BN) * 128;  // each epilogue warp's bias slices
+  static constexpr int kFixedBytes = kStripsBytes + kBiasBytes + 1024 + kBarrierBytes;
+  static constexpr int kFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kFit < 6 ? kFit : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
   static constexpr int kTmemCols = 512;
   static constexpr int kAccStride = 256;
 };
@@ -280,13 +369,14 @@ struct PairCfg {
 template <int BN, bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const GemmParams p) {
+                    const __grid_constant__ StoreMaps smaps, const GemmParams p) {
   using Cfg = PairCfg<BN>;
   constexpr int HB = BN / 2;  // B rows held by one CTA
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes);
+  float* bias_smem = reinterpret_cast<float*>(strips + Cfg::kStripsBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes + Cfg::kBiasBytes);
   uint64_t* full = bars;                      // used in the leader only
   uint64_t* empty = bars + Cfg::kStages;      // one set per CTA, both signalled by the leader's commits
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;
@@ -336,8 +426,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int item = pair; item < total && ok; item += npairs) {
         const int split = item / tiles, tile = item - split * tiles;
         const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
-        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
+        if (p.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        }
         const int m0 = m_blk * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = n_blk * BN + static_cast<int>(rank) * HB;
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -371,8 +464,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       for (int item = pair; item < total && ok; item += npairs, ++it) {
         const int split = item / tiles;
-        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
+        if (p.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        }
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
         if (!mbar_wait_cluster(&tmem_empty[buf], aphase ^ 1u, ctx, 0x0501u)) { ok = false; break; }
@@ -399,8 +495,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    constexpr int kChunks = BN / 64;
+    const int sub = (warp - 2) >> 2;
+    constexpr int kChunks = chunks_per_warp(BN);
     const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     int it = 0;
@@ -410,6 +506,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
+      float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
+      const bool bias_staged = (p.ep.tune & 1) && p.ep.bias != nullptr && p.split_k == 1;
+      if (bias_staged) {
+        // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) {
+          const int64_t n = static_cast<int64_t>(n_blk) * BN + (sub + j * kWarpsPerQuarter) * 32 + lane;
+          wbias[j * 32 + lane] = n < p.N ? __ldg(p.ep.bias + n) : 0.f;
+        }
+        __syncwarp();
+      }
       ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0601u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -417,17 +525,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * BM + static_cast<int64_t>(rank) * BM + quarter * 32;
       const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(buf * Cfg::kAccStride + half * (BN / 2));
+                             static_cast<uint32_t>(buf * Cfg::kAccStride);
 #pragma unroll 1
       for (int chunk = 0; chunk < kChunks; ++chunk) {
+        const int col = (sub + chunk * kWarpsPerQuarter) * 32;  // first column of this chunk within the tile
+        if (col >= BN) break;
         uint32_t r[32];
-        tmem_ld_32x32(taddr + chunk * 32, r);
+        tmem_ld_32x32(taddr + col, r);
         tmem_ld_wait();
         float acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + half * (BN / 2) + chunk * 32;
+        const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
         uint8_t* strip = strips + (warp - 2) * kStripBytes;
+        const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
           if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
@@ -438,15 +549,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
           }
         } else if (p.out_bf16) {
-          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane);
+          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane, bias_c, p.tma_store ? &smaps : nullptr);
         } else {
-          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane);
+          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(buf == 0 ? leader_empty0 : leader_empty1);
     }
+    if (lane == 0) bulk_wait_all();  // this lane's tile stores are complete before the block may exit
   }
 
   __syncwarp();
@@ -544,7 +656,7 @@ gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64
 }
 
 template <int BN, bool AK, bool BK_>
-int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tc_kernel<BN, AK, BK_>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -553,7 +665,7 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
   }
   const int total = p.num_m * p.num_n * p.split_k;
   const int grid = total < kNumSMs ? total : kNumSMs;
-  launch_k(kern, grid, kGemmThreads, Cfg::kSmemBytes, st, ta, tb, p);
+  launch_k(kern, grid, kGemmThreads, Cfg::kSmemBytes, st, ta, tb, sm, p);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
@@ -580,7 +692,8 @@ int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int6
 }
 
 template <int BN, bool AK, bool BK_>
-int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
+int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p,
+                   cudaStream_t st) {
   using Cfg = PairCfg<BN>;
   auto kern = gemm_tc_pair_kernel<BN, AK, BK_>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
@@ -603,7 +716,7 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParam
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, sm, p) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
@@ -657,6 +770,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   ep.bias_vec_ok = bias != nullptr && aligned16(bias);
   ep.vec_ok = aligned16(c) && (ldc * osz) % 16 == 0 && (aux == nullptr || aligned16(aux)) &&
               (aux_out == nullptr || aligned16(aux_out));
+  {
+    const char* e = getenv("PTJ_GEMM_TUNE");
+    ep.tune = e != nullptr ? atoi(e) : 11;
+  }
   if (dropout != nullptr) {
     if (!(dropout->p >= 0.f && dropout->p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
     ep.drop_thr = dropout_threshold16(dropout->p);
@@ -706,6 +823,17 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
   if (const char* e = std::getenv("PTJ_GEMM_DEBUG")) p.debug = std::atoi(e);
 
+  StoreMaps smaps{};
+  if ((ep.tune & 8) && p.out_bf16 && ep.vec_ok && split_k == 1) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+    const uint64_t str[1] = {static_cast<uint64_t>(ldc) * 2};
+    const uint32_t box[2] = {32, 32};
+    if (!make_tmap_bf16_sw64(&smaps.c, c, 2, dims, str, box)) return PTJ_ERR_LAUNCH;
+    if (epilogue == PTJ_EPI_GELU && aux_out != nullptr && !make_tmap_bf16_sw64(&smaps.x, aux_out, 2, dims, str, box))
+      return PTJ_ERR_LAUNCH;
+    p.tma_store = 1;
+  }
+
   if (use_pair_kernel(M, N, K)) {
     const int pbn = 256;
     p.num_m = static_cast<int>(ceil_div(M, 2 * BM));
@@ -725,10 +853,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
       const uint32_t box_k[2] = {64, static_cast<uint32_t>(pbn / 2)}, box_mn[2] = {64, 64};
       if (!make_tmap_bf16(&tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
     }
-    int prc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true>(ta, tb, p, st)
-                                   : launch_tc_pair<256, true, false>(ta, tb, p, st))
-                       : (b_kmajor ? launch_tc_pair<256, false, true>(ta, tb, p, st)
-                                   : launch_tc_pair<256, false, false>(ta, tb, p, st));
+    int prc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true>(ta, tb, smaps, p, st)
+                                   : launch_tc_pair<256, true, false>(ta, tb, smaps, p, st))
+                       : (b_kmajor ? launch_tc_pair<256, false, true>(ta, tb, smaps, p, st)
+                                   : launch_tc_pair<256, false, false>(ta, tb, smaps, p, st));
     if (prc != PTJ_OK) return prc;
     return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
   }
@@ -768,10 +896,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
 
   int rc;
 #define PTJ_TC(BN_)                                                              \
-  (a_kmajor ? (b_kmajor ? launch_tc<BN_, true, true>(ta, tb, p, st)              \
-                        : launch_tc<BN_, true, false>(ta, tb, p, st))            \
-            : (b_kmajor ? launch_tc<BN_, false, true>(ta, tb, p, st)             \
-                        : launch_tc<BN_, false, false>(ta, tb, p, st)))
+  (a_kmajor ? (b_kmajor ? launch_tc<BN_, true, true>(ta, tb, smaps, p, st)              \
+                        : launch_tc<BN_, true, false>(ta, tb, smaps, p, st))            \
+            : (b_kmajor ? launch_tc<BN_, false, true>(ta, tb, smaps, p, st)             \
+                        : launch_tc<BN_, false, false>(ta, tb, smaps, p, st)))
   rc = bn == 128 ? PTJ_TC(128) : (bn == 192 ? PTJ_TC(192) : PTJ_TC(256));
 #undef PTJ_TC
   if (rc != PTJ_OK) return rc;

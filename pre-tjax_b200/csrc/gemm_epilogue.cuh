@@ -21,6 +21,8 @@ struct EpilogueParams {
   int train;
   uint64_t seed;
   uint32_t stream_id;
+  int tune;              // bit 0 = bias staged in shared memory per tile, bit 1 = two-wide GELU math, bit 3 = bf16
+                         // outputs leave through tensor-map tile stores (PTJ_GEMM_TUNE overrides the default)
 };
 
 template <typename TOut, int CNT>
@@ -63,10 +65,18 @@ __device__ __forceinline__ void store_row(TOut* dst, int64_t n0, int64_t N, bool
 // rounded to the output type) which the caller may store into aux_out. epilogue_post turns acc into the values to
 // store into C. epilogue_pre returns false when the segment lies outside the matrix (nothing to compute or store).
 template <typename TOut, int CNT>
-__device__ __forceinline__ bool epilogue_pre(const EpilogueParams& ep, int64_t m, int64_t n0, float (&acc)[CNT]) {
+__device__ __forceinline__ bool epilogue_pre(const EpilogueParams& ep, int64_t m, int64_t n0, float (&acc)[CNT],
+                                             const float* bias_s = nullptr) {
   if (m >= ep.M || n0 >= ep.N) return false;
 
-  if (ep.bias != nullptr) {
+  if (bias_s != nullptr) {
+    // the tile's bias slice was staged in shared memory (zero beyond N): broadcast 16-byte reads
+#pragma unroll
+    for (int j = 0; j < CNT; j += 4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(bias_s + j);
+      acc[j] += b4.x; acc[j + 1] += b4.y; acc[j + 2] += b4.z; acc[j + 3] += b4.w;
+    }
+  } else if (ep.bias != nullptr) {
     if (ep.bias_vec_ok && n0 + CNT <= ep.N) {
 #pragma unroll
       for (int j = 0; j < CNT; j += 4) {
@@ -81,8 +91,18 @@ __device__ __forceinline__ bool epilogue_pre(const EpilogueParams& ep, int64_t m
   }
   if (ep.mode == PTJ_EPI_GELU && sizeof(TOut) == 2) {
     // the activation sees the pre-activation as stored (rounded to the output type), like a separate GELU kernel would
+    if (ep.tune & 2) {
 #pragma unroll
-    for (int j = 0; j < CNT; ++j) acc[j] = __bfloat162float(__float2bfloat16_rn(acc[j]));
+      for (int j = 0; j < CNT; j += 2) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[j], acc[j + 1]);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        acc[j] = __uint_as_float(w << 16);
+        acc[j + 1] = __uint_as_float(w & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CNT; ++j) acc[j] = __bfloat162float(__float2bfloat16_rn(acc[j]));
+    }
   }
   return true;
 }
@@ -100,11 +120,21 @@ __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t 
                                               const float (&a)[CNT]) {
   constexpr bool kFast = sizeof(TOut) == 2;  // bf16 output: hardware tanh is exact enough after rounding
   if (ep.mode == PTJ_EPI_GELU) {
+    if (kFast && (ep.tune & 2)) {
 #pragma unroll
-    for (int j = 0; j < CNT; ++j) acc[j] = gelu_tanh<kFast>(acc[j]);
+      for (int j = 0; j < CNT; j += 2) gelu_tanh_x2(acc[j], acc[j + 1]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CNT; ++j) acc[j] = gelu_tanh<kFast>(acc[j]);
+    }
   } else if (ep.mode == PTJ_EPI_GELU_BWD) {
+    if (kFast && (ep.tune & 2)) {
 #pragma unroll
-    for (int j = 0; j < CNT; ++j) acc[j] *= gelu_tanh_grad<kFast>(a[j]);
+      for (int j = 0; j < CNT; j += 2) gelu_tanh_grad_mul_x2(acc[j], acc[j + 1], a[j], a[j + 1]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CNT; ++j) acc[j] *= gelu_tanh_grad<kFast>(a[j]);
+    }
   } else if (ep.mode == PTJ_EPI_ACCUM) {
 #pragma unroll
     for (int j = 0; j < CNT; ++j) acc[j] += a[j];

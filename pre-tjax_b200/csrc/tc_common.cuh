@@ -88,6 +88,19 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Tile store shared memory -> global through the tensor map (clipped at the tensor's edges), tracked by the issuing
+// thread's bulk group. x (elements of the contiguous dimension) must start on a 16-byte boundary.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk stores have finished READING shared memory (the source may be overwritten)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk stores are complete (their writes are visible)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- tensor memory -----------------------------------------------------------------------------------------------
 // Whole-warp calls. ncols: power of two in [32, 512]. The allocated base address is written to *smem_slot.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {
@@ -324,6 +337,9 @@ EncodeTiledFn get_encode_tiled();
 // 128-byte swizzle, out-of-bounds elements read as zero. Returns false on a driver error.
 bool make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                     const uint32_t* box);
+// The same with the 64-byte swizzle (boxes whose rows are 64 bytes): the map epilogues store 32 x 32 bf16 blocks through.
+bool make_tmap_bf16_sw64(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box);
 
 }  // namespace tc
 }  // namespace ptj
