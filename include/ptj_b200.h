@@ -130,6 +130,12 @@ int ptj_cross_entropy(const int32_t* labels, const void* logits, void* dlogits, 
                       float* n_valid, int count_in_kernel, float* out3, int64_t rows, int64_t cols,
                       int64_t ld, int dtype, void* stream);
 
+/* Index of the largest of the first `cols` elements of every row (first index on ties) -> out int32[rows].
+ * Replaces the torch.argmax over a logits slice in `predict`'s greedy decoding loop
+ * (loss_and_optimizer_triton.py:203-212, the argmax at :207). */
+int ptj_argmax_rows(const void* x, int32_t* out, int64_t rows, int64_t cols, int64_t ld, int dtype,
+                    void* stream);
+
 /* ---- embedding -------------------------------------------------------------------------------------- */
 /* Replaces t_embed_fwd + positional add + dropout (model_triton.py:166-167, 2338-2341):
  * y[b,s,:] = dropout(w_emb[ids[b,s],:] * sqrt(dim) + w_pos[s,:]). Weights are `wdtype`, output `dtype`. */

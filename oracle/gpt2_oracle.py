@@ -193,6 +193,36 @@ def loss_and_grads(params, y: torch.Tensor, p: float = 0.0, train: bool = True, 
     return grads, (loss.detach(), acc, n_valid.to(loss.dtype) / labels.numel())
 
 
+# ---- evaluation / inference callers ------------------------------------------------------------------------------------
+def loss_eval(params, y: torch.Tensor, p: float):
+    """(loss, accuracy, valid fraction) with every dropout site in eval mode, i.e. scaled by 1 - p
+    (loss_and_optimizer_triton.py:221-232 with train=False)."""
+    logits = forward_gpt2(params, y[:, :-1], p, False)
+    labels = y[:, 1:]
+    loss, n_valid = avg_cross_entropy_loss(labels, logits)
+    return loss, accuracy(labels, logits), n_valid.to(loss.dtype) / labels.numel()
+
+
+def log_probs(params, y: torch.Tensor, p: float) -> torch.Tensor:
+    """[B]: sum over positions of log softmax(logits)[label] in eval mode; a padding label (0) adds +1 instead
+    (the reference's torch.where(labels != 0, elem, 1), loss_and_optimizer_triton.py:293-311)."""
+    logits = forward_gpt2(params, y[:, :-1], p, False)
+    labels = y[:, 1:].long()
+    lp = log_softmax(logits).gather(-1, labels.unsqueeze(-1)).squeeze(-1)
+    return torch.where(labels != 0, lp, torch.ones_like(lp)).sum(dim=1)
+
+
+def predict(params, batch: int, sample_len: int, start_tok: int, end_tok: int, p: float) -> torch.Tensor:
+    """Greedy decoding, full forward per new token (loss_and_optimizer_triton.py:203-212): [batch, sample_len - 1].
+    Positions where the running maximum of the ids equals end_tok, and ids equal to start_tok, become 0."""
+    ys = torch.full((batch, sample_len), start_tok, dtype=torch.int64)
+    for i in range(sample_len - 1):
+        logits = forward_gpt2(params, ys, p, False)
+        ys[:, i + 1] = torch.argmax(logits[:, i], dim=-1)
+    ys = torch.where(torch.cummax(ys, dim=1)[0] != end_tok, ys, torch.zeros_like(ys))[:, 1:]
+    return torch.where(ys != start_tok, ys, torch.zeros_like(ys))
+
+
 # ---- optimizer ---------------------------------------------------------------------------------------------------------
 def adam_w(params, grads, lr, betas, eps, moments, i, weight_decay=0.0, decay_mask=None):
     """One AdamW step with t = i + 1; returns new (params, [m, v]): loss_and_optimizer_triton.py:376-401."""

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "ptj_log_softmax_fwd": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_log_softmax_bwd": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_cross_entropy": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_int64, c_int64, c_int64, c_int, _P]),
+    "ptj_argmax_rows": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_embed_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_uint64, c_uint32,
                               c_int, c_int, _P]),
     "ptj_embed_bwd": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_uint64,

@@ -251,6 +251,22 @@ __global__ void ce_finalize_kernel(const float* __restrict__ row_stats, const fl
   }
 }
 
+// Index of the largest element of every row (first index on ties): the greedy-decoding step of `predict`
+// (loss_and_optimizer_triton.py:203-212), which the reference takes with torch.argmax over a logits slice.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+argmax_rows_kernel(const T* __restrict__ x, int32_t* __restrict__ out, int64_t rows, int64_t cols, int64_t ld) {
+  grid_dep_sync();
+  __shared__ float red[33];
+  __shared__ int64_t red_arg[kRowThreads / 32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * ld;
+    const MaxSum ms = row_max_sum<T, true>(xr, cols, head_elems(xr, cols, true), true, red, red_arg);
+    if (threadIdx.x == 0) out[row] = static_cast<int32_t>(ms.arg);
+    __syncthreads();
+  }
+}
+
 // Vector mode needs every tensor of a row to share the same distance to a 16-byte boundary.
 template <typename T>
 bool same_phase(const void* a, int64_t lda, const void* b, int64_t ldb) {
@@ -329,6 +345,25 @@ extern "C" int ptj_cross_entropy(const int32_t* labels, const void* logits, void
   }
   PTJ_CHECK_LAUNCH();
   launch_k(ce_finalize_kernel, 1, 1024, 0, st, row_stats, n_valid, rows, out3);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+extern "C" int ptj_argmax_rows(const void* x, int32_t* out, int64_t rows, int64_t cols, int64_t ld, int dtype,
+                               void* stream) {
+  if (rows < 0 || cols < 1 || cols > 0x7fffffffLL || ld < cols) return PTJ_ERR_BAD_SHAPE;
+  if (rows == 0) return PTJ_OK;
+  if (!x || !out) return PTJ_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PTJ_F32) {
+    launch_k(argmax_rows_kernel<float>, row_grid(rows), kRowThreads, 0, st, static_cast<const float*>(x), out, rows,
+             cols, ld);
+  } else if (dtype == PTJ_BF16) {
+    launch_k(argmax_rows_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st,
+             static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld);
+  } else {
+    return PTJ_ERR_DTYPE;
+  }
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

@@ -350,9 +350,9 @@ def t_scaled_dot_prod_attn_bkwd3_t(dloss_dx, acts, qkv: torch.Tensor, mask: torc
 
 
 # ---- cross entropy -----------------------------------------------------------------------------------------------------
-def cross_entropy(labels, logits, cols=None, want_grad=True, in_place=False, n_valid=None):
+def cross_entropy(labels, logits, cols=None, want_grad=True, in_place=False, n_valid=None, want_rows=False):
     """Fused CE forward(+backward). logits [rows, ld]; returns (stats float[3] = loss, accuracy, valid fraction;
-    n_valid float[1]; dlogits or None)."""
+    n_valid float[1]; dlogits or None), plus the per-row losses float[rows] (0 on padding rows) when want_rows."""
     ld = logits.shape[-1]
     cols = ld if cols is None else cols
     rows = logits.numel() // ld
@@ -369,7 +369,22 @@ def cross_entropy(labels, logits, cols=None, want_grad=True, in_place=False, n_v
         _lib.lib().ptj_cross_entropy(_ptr(labels), _ptr(logits), _ptr(dlogits), _ptr(row_stats), _ptr(n_valid),
                                      int(count), _ptr(out3), rows, cols, ld, _dt(logits), _stream()),
         "ptj_cross_entropy")
+    if want_rows:
+        return out3, n_valid, dlogits, row_stats[:rows]
     return out3, n_valid, dlogits
+
+
+def argmax_rows(x: torch.Tensor, cols=None) -> torch.Tensor:
+    """int32[rows] = index of the largest of the first `cols` elements of every row of x [rows, ld] (first index on
+    ties): the torch.argmax of the reference's greedy decoding loop (loss_and_optimizer_triton.py:207)."""
+    if not x.is_cuda:
+        raise RuntimeError("x must live on a CUDA device: there is no CPU implementation")
+    assert x.dim() == 2 and x.stride(1) == 1, "rows may be strided, elements of a row must be contiguous"
+    rows, ld = x.shape[0], x.stride(0)
+    cols = x.shape[1] if cols is None else cols
+    out = torch.empty(rows, device=x.device, dtype=torch.int32)
+    _lib.check(_lib.lib().ptj_argmax_rows(_ptr(x), _ptr(out), rows, cols, ld, _dt(x), _stream()), "ptj_argmax_rows")
+    return out
 
 
 def t_avg_cross_entropy_loss(y_labels: torch.Tensor, x_logits: torch.Tensor):

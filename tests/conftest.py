@@ -54,3 +54,8 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     a, b = a.detach().double().cpu(), b.detach().double().cpu()
     denom = float(b.abs().max())
     return float((a - b).abs().max()) / (denom if denom > 0 else 1.0)
+
+
+@pytest.fixture(scope="session")
+def eval_golden():
+    return load_golden("eval_callers.npz")

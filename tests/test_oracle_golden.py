@@ -160,3 +160,27 @@ def test_mask_statistics():
     m2 = philox.keep_mask(seed=123456790, stream_id=0, n=1 << 20, p=0.1)
     assert abs(float(np.corrcoef(m, m2)[0, 1])) < 5e-3
     assert philox.keep_mask(1, 0, 1000, 0.0).min() == 1.0
+
+
+def _tiny_params(g):
+    L = int(g["dims"][2])
+    it = iter([tt(g[f"p{i}"]) for i in range(3 + 10 * L + 2)])
+    return [[next(it), next(it)], [next(it)]] + [[next(it) for _ in range(10)] for _ in range(L)] + [[next(it), next(it)]]
+
+
+def test_eval_callers(tiny_golden, eval_golden):
+    """loss_eval / log_probs / predict restated on the CPU against the reference's own outputs (eval_callers.npz,
+    made by make_golden_eval.py): dropout 0.1 in eval mode, padding labels present, greedy decoding over 16 positions."""
+    g, e = tiny_golden, eval_golden
+    params, y, p = _tiny_params(g), tt(g["y"]), float(e["dropout"])
+    close(orc.forward_gpt2(params, y[:, :-1], p, False), tt(e["logits_eval"]))
+    loss, acc, frac = orc.loss_eval(params, y, p)
+    close(loss, tt(e["loss"]))
+    close(acc, tt(e["acc"]))
+    close(frac, tt(e["frac"]))
+    assert int((y[:, 1:] == 0).sum()) > 0  # the +1-per-padding-label rule is exercised
+    close(orc.log_probs(params, y, p), tt(e["log_probs"]))
+    params_pred = [[params[0][0], tt(e["b_head_pred"])], [tt(e["w_pos_pred"])]] + params[2:]
+    pred = orc.predict(params_pred, y.shape[0], int(g["dims"][5]), int(e["start_tok"]), int(e["end_tok"]), p)
+    assert torch.equal(pred, tt(e["predict"]))
+    assert len(set(pred[0].tolist())) > 5  # the decoded ids differ from position to position
