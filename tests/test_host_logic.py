@@ -9,6 +9,7 @@ import torch
 import torch.multiprocessing as mp
 
 from conftest import pkg
+from oracle import gpt2_oracle as orc
 
 
 def cfg_small():
@@ -170,3 +171,39 @@ def test_sharded_oracle_gradients_average_to_full_batch():
     b, _ = orc.loss_and_grads(prm, y[2:])
     for fa, fb, ff in zip((t for grp in a for t in grp), (t for grp in b for t in grp), (t for grp in full for t in grp)):
         assert torch.allclose((fa + fb) / 2, ff, atol=1e-12)
+
+
+def test_checkpoint_wire_format_round_trip(tmp_path):
+    """The file is the reference's pickle tuple (i, ds_train_rows_read, params, [m, v]) (train_gpt2_triton.py:413-419):
+    plain pickle.load, as the reference's resume code does (:277-280), must give that structure back."""
+    import pickle
+    ck = pkg("checkpoint")
+    prm = orc.init_params(40, 16, 2, 2, 32, 8, seed=3)
+    g = torch.Generator().manual_seed(4)
+    m = [[torch.randn(t.shape, generator=g) for t in grp] for grp in prm]
+    v = [[torch.rand(t.shape, generator=g) for t in grp] for grp in prm]
+    path = tmp_path / "run" / "checkpoint_7.pkl"
+    ck.save_checkpoint(str(path), 7, 1234, prm, [m, v])
+    with open(path, "rb") as f:
+        i, rows, p2, mom = pickle.load(f)
+    assert (i, rows) == (7, 1234) and len(mom) == 2
+    assert [len(grp) for grp in p2] == [2, 1, 10, 10, 2]
+    for a, b in zip([t for grp in p2 for t in grp], [t for grp in prm for t in grp]):
+        assert a.dtype == torch.float32 and a.device.type == "cpu" and torch.equal(a, b)
+    i, rows, p3, (m3, v3) = ck.load_checkpoint(str(path))
+    assert (i, rows) == (7, 1234)
+    assert all(torch.equal(a, b) for ga, gb in zip(m3, m) for a, b in zip(ga, gb))
+    assert all(torch.equal(a, b) for ga, gb in zip(v3, v) for a, b in zip(ga, gb))
+    # a file written the way the reference writes it loads as well
+    ref_style = tmp_path / "ref.pkl"
+    with open(ref_style, "wb") as f:
+        pickle.dump((3, 99, prm, [m, v]), f)
+    assert ck.load_checkpoint(str(ref_style))[:2] == (3, 99)
+    # structure errors are reported, not silently accepted
+    with pytest.raises(ValueError):
+        ck.save_checkpoint(str(tmp_path / "bad.pkl"), 0, 0, prm, [m[:-1], v])
+    with open(tmp_path / "short.pkl", "wb") as f:
+        pickle.dump((1, 2, prm), f)
+    with pytest.raises(ValueError):
+        ck.load_checkpoint(str(tmp_path / "short.pkl"))
+    assert not list(tmp_path.glob("**/*.tmp.*"))
