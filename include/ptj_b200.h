@@ -72,9 +72,13 @@ int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const v
  * the contiguous [rows, dim] tensor, i.e. exactly what ptj_dropout(dx, NULL, dx_dropped, ...) would write, without a
  * second pass over dx (the reference runs t_dropout_bkwd as its own kernel, model_triton.py:153). dx must be given;
  * rows must be 16-byte aligned with dim a multiple of the 16-byte vector and at most 8 x 32 vectors
- * (else PTJ_ERR_UNSUPPORTED: call ptj_layernorm_bwd and ptj_dropout). */
+ * (else PTJ_ERR_UNSUPPORTED: call ptj_layernorm_bwd and ptj_dropout).
+ * dropped_colsum (float[dim], may be NULL; needs dgamma/dbeta): the column sums of dx_dropped as stored, i.e. the
+ * bias gradient of the linear layer whose output went through that dropout (the db of t_linear_bkwd2_p,
+ * model_triton.py:423-434, which the reference sums in a pass of its own). */
 int ptj_layernorm_bwd_dropout(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
-                              void* dx_dropped, float* dgamma, float* dbeta, float* scratch, size_t scratch_floats,
+                              void* dx_dropped, float* dropped_colsum, float* dgamma, float* dbeta, float* scratch,
+                              size_t scratch_floats,
                               int64_t rows, int64_t dim, float p, int train, uint64_t seed, uint32_t stream_id,
                               int dtype, void* stream);
 

@@ -36,7 +36,7 @@ _SIGNATURES = {
     "ptj_layernorm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, _P]),
     "ptj_layernorm_bwd_scratch_floats": (c_size_t, [c_int64, c_int64]),
     "ptj_layernorm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int, _P]),
-    "ptj_layernorm_bwd_dropout": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_float, c_int,
+    "ptj_layernorm_bwd_dropout": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_float, c_int,
                                           c_uint64, c_uint32, c_int, _P]),
     "ptj_layernorm_bwd_noalloc_max_dim": (c_size_t, []),
     "ptj_layernorm_bwd_noalloc": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, _P]),

@@ -118,6 +118,7 @@ ln_fwd_generic_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
 // consumer of "dropout backward of dx" needs no separate pass over dx.
 struct LnMask {
   void* out;
+  float* colsum;  // optional: column sums of `out` (the bias gradient of the linear layer that produced the branch)
   uint32_t thr;
   float eval_scale;
   int train;
@@ -135,16 +136,20 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
   grid_dep_sync();
   constexpr int V = Elem<T>::kVec;
   constexpr int kSlots = NV * V * 32;   // per-warp accumulator slots per quantity
-  extern __shared__ float sm_acc[];     // [kLnWarps][2][kSlots]
+  extern __shared__ float sm_acc[];     // [kLnWarps][nq][kSlots], nq = 2 (dgamma, dbeta) or 3 (+ column sums of mk.out)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim / V;
-  float* acc_g = sm_acc + warp * 2 * kSlots;
+  const bool want_cs = partial != nullptr && mk.colsum != nullptr;
+  const int nq = want_cs ? 3 : 2;
+  float* acc_g = sm_acc + warp * nq * kSlots;
   float* acc_b = acc_g + kSlots;
+  float* acc_d = acc_b + kSlots;
   if (partial != nullptr) {
 #pragma unroll
     for (int s = 0; s < NV * V; ++s) {
       acc_g[s * 32 + lane] = 0.f;
       acc_b[s * 32 + lane] = 0.f;
+      if (want_cs) acc_d[s * 32 + lane] = 0.f;
     }
   }
   const float inv_n = 1.f / static_cast<float>(dim), inv_nm1 = 1.f / static_cast<float>(dim - 1);
@@ -249,7 +254,8 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
 #pragma unroll
             for (int j = 0; j < V; ++j) {
               const float r = Elem<T>::round(o[j]);
-              o[j] = mk.train ? (((keep >> j) & 1u) ? r : 0.f) : r * mk.eval_scale;
+              o[j] = mk.train ? (((keep >> j) & 1u) ? r : 0.f) : Elem<T>::round(r * mk.eval_scale);
+              if (want_cs) acc_d[(i * V + j) * 32 + lane] += o[j];  // the value as stored
             }
             Elem<T>::store_vec(mr + vi * V, o);
           }
@@ -260,11 +266,11 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
   if (partial == nullptr) return;
   __syncthreads();
   // fold the warps' strips in warp order (fixed order => reproducible) and scatter slots back to columns
-  float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * dim;
-  for (int t = threadIdx.x; t < 2 * kSlots; t += blockDim.x) {
+  float* out = partial + static_cast<size_t>(blockIdx.x) * nq * dim;
+  for (int t = threadIdx.x; t < nq * kSlots; t += blockDim.x) {
     float sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kLnWarps; ++w) sum += sm_acc[w * 2 * kSlots + t];
+    for (int w = 0; w < kLnWarps; ++w) sum += sm_acc[w * nq * kSlots + t];
     const int which = t / kSlots, rem = t - which * kSlots;
     const int ij = rem >> 5, ln = rem & 31;
     const int vi = ln + 32 * (ij / V);
@@ -322,22 +328,24 @@ ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
 // strided subset of the partial rows and the 8 results are added in warp order (fixed order => reproducible).
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                       int nblocks, int dim) {
+                       float* __restrict__ dsum, int nq, int nblocks, int dim) {
   grid_dep_sync();
   // 8 columns x 32 row groups per block: many small blocks, each row group sums every 32nd partial row in order
   __shared__ float red[32][9];
   const int col = threadIdx.x & 7, grp = threadIdx.x >> 3;
   const int c = blockIdx.x * 8 + col;
   float s = 0.f;
-  if (c < 2 * dim)
-    for (int b = grp; b < nblocks; b += 32) s += partial[static_cast<size_t>(b) * 2 * dim + c];
+  if (c < nq * dim)
+    for (int b = grp; b < nblocks; b += 32) s += partial[static_cast<size_t>(b) * nq * dim + c];
   red[grp][col] = s;
   __syncthreads();
-  if (grp == 0 && c < 2 * dim) {
+  if (grp == 0 && c < nq * dim) {
     float t = 0.f;
 #pragma unroll
     for (int w = 0; w < 32; ++w) t += red[w][col];
-    if (c < dim) dgamma[c] = t; else dbeta[c - dim] = t;
+    if (c < dim) dgamma[c] = t;
+    else if (c < 2 * dim) dbeta[c - dim] = t;
+    else dsum[c - 2 * dim] = t;
   }
 }
 
@@ -369,7 +377,8 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
   const int nv = vec_ok ? static_cast<int>(ceil_div(dim / V, 32)) : 99;
   const int grid = ln_bwd_grid(rows);
   float* partial = dgamma != nullptr ? scratch : nullptr;
-  const size_t smem = static_cast<size_t>(kLnWarps) * 2 * (nv <= 8 ? nv : 0) * V * 32 * sizeof(float);
+  const int nq = (partial != nullptr && mk.colsum != nullptr) ? 3 : 2;
+  const size_t smem = static_cast<size_t>(kLnWarps) * nq * (nv <= 8 ? nv : 0) * V * 32 * sizeof(float);
 #define PTJ_LN_BWD(NV)                                                                                   \
   case NV:                                                                                               \
     if (smem > 48 * 1024)                                                                                \
@@ -385,7 +394,8 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
 #undef PTJ_LN_BWD
   PTJ_CHECK_LAUNCH();
   if (partial != nullptr) {
-    launch_k(ln_bwd_finalize_kernel, static_cast<int>(ceil_div(2 * dim, 8)), 256, 0, st, partial, dgamma, dbeta, grid, dim);
+    launch_k(ln_bwd_finalize_kernel, static_cast<int>(ceil_div(nq * dim, 8)), 256, 0, st, partial, dgamma, dbeta,
+             mk.colsum, nq, grid, dim);
     PTJ_CHECK_LAUNCH();
   }
   return PTJ_OK;
@@ -410,9 +420,14 @@ extern "C" int ptj_layernorm_fwd(const void* x, const float* gamma, const float*
   return PTJ_ERR_DTYPE;
 }
 
-extern "C" size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim) {
+// floats of partial sums the backward kernel writes: one row of nq * dim per thread block
+static size_t ln_bwd_partial_floats(int64_t rows, int64_t dim, int nq) {
   if (rows <= 0 || dim <= 0) return 0;
-  return static_cast<size_t>(ln_bwd_grid(rows)) * 2 * static_cast<size_t>(dim);
+  return static_cast<size_t>(ln_bwd_grid(rows)) * nq * static_cast<size_t>(dim);
+}
+
+extern "C" size_t ptj_layernorm_bwd_scratch_floats(int64_t rows, int64_t dim) {
+  return ln_bwd_partial_floats(rows, dim, 3);  // dgamma, dbeta and the optional column sums of the dropped output
 }
 
 static int layernorm_bwd_impl(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
@@ -422,6 +437,7 @@ static int layernorm_bwd_impl(const void* dy, const void* x, const float* gamma,
   if ((dgamma == nullptr) != (dbeta == nullptr)) return PTJ_ERR_BAD_SHAPE;
   if (!dy || !x || !gamma) return PTJ_ERR_BAD_SHAPE;
   if (mk.out != nullptr && dx == nullptr) return PTJ_ERR_BAD_SHAPE;
+  if (mk.colsum != nullptr && (mk.out == nullptr || dgamma == nullptr)) return PTJ_ERR_BAD_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (rows == 0) {
     if (dgamma) {
@@ -430,7 +446,7 @@ static int layernorm_bwd_impl(const void* dy, const void* x, const float* gamma,
     }
     return PTJ_OK;
   }
-  if (dgamma && (scratch == nullptr || scratch_floats < ptj_layernorm_bwd_scratch_floats(rows, dim)))
+  if (dgamma && (scratch == nullptr || scratch_floats < ln_bwd_partial_floats(rows, dim, mk.colsum != nullptr ? 3 : 2)))
     return PTJ_ERR_WORKSPACE;
   if (dtype == PTJ_F32)
     return launch_bwd(static_cast<const float*>(dy), static_cast<const float*>(x), gamma,
@@ -446,17 +462,17 @@ static int layernorm_bwd_impl(const void* dy, const void* x, const float* gamma,
 extern "C" int ptj_layernorm_bwd(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
                                  float* dgamma, float* dbeta, float* scratch, size_t scratch_floats, int64_t rows,
                                  int64_t dim, int dtype, void* stream) {
-  const LnMask none{nullptr, 0u, 1.f, 0, 0ull, 0u};
+  const LnMask none{nullptr, nullptr, 0u, 1.f, 0, 0ull, 0u};
   return layernorm_bwd_impl(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, scratch_floats, rows, dim, none, dtype,
                             stream);
 }
 
 extern "C" int ptj_layernorm_bwd_dropout(const void* dy, const void* x, const float* gamma, const void* dx_add, void* dx,
-                                         void* dx_dropped, float* dgamma, float* dbeta, float* scratch,
+                                         void* dx_dropped, float* dropped_colsum, float* dgamma, float* dbeta, float* scratch,
                                          size_t scratch_floats, int64_t rows, int64_t dim, float p, int train,
                                          uint64_t seed, uint32_t stream_id, int dtype, void* stream) {
   if (!dx_dropped || !(p >= 0.f && p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
-  const LnMask mk{dx_dropped, dropout_threshold16(p), 1.f - p, train, seed, stream_id};
+  const LnMask mk{dx_dropped, dropped_colsum, dropout_threshold16(p), 1.f - p, train, seed, stream_id};
   return layernorm_bwd_impl(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, scratch_floats, rows, dim, mk, dtype,
                             stream);
 }
@@ -504,7 +520,7 @@ extern "C" int ptj_layernorm_bwd_noalloc(const void* dy, const void* x, const fl
                                          float* dgamma, float* dbeta, int64_t rows, int64_t dim, int dtype,
                                          void* stream) {
   if (rows < 0 || dim < 1) return PTJ_ERR_BAD_SHAPE;
-  if (dim > kStaticMaxDim || ptj_layernorm_bwd_scratch_floats(rows, dim) > kStaticScratchFloats) return PTJ_ERR_TOO_LARGE;
+  if (dim > kStaticMaxDim || ln_bwd_partial_floats(rows, dim, 2) > kStaticScratchFloats) return PTJ_ERR_TOO_LARGE;
   float* scratch = static_scratch_for_current_device();  // first call on a device resolves the address
   if (scratch == nullptr) return PTJ_ERR_DEVICE;
   return ptj_layernorm_bwd(dy, x, gamma, dx_add, dx, dgamma, dbeta, scratch, kStaticScratchFloats, rows, dim, dtype,

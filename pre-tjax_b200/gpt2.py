@@ -221,8 +221,10 @@ class Gpt2Step:
         # every LayerNorm backward also writes dropout(dx) for the residual branch that consumes it next
         fuse = D % 8 == 0 and D <= (2048 if self.dtype == torch.bfloat16 else 1024)
         s_next = seeds[3 * cfg.layers] if cfg.layers > 0 else 0  # last layer's second residual dropout
+        # ... and its column sums, which are the bias gradient of that branch's last linear layer (FFN-2)
         dx, dy = self._ln_bwd(d, w["g_f"], acts["x_last"], grads["g_f"], grads["b_f"],
-                              dropped=(train, s_next, p) if (fuse and cfg.layers > 0) else None)
+                              dropped=(train, s_next, p) if (fuse and cfg.layers > 0) else None,
+                              colsum_out=grads[f"l{cfg.layers - 1}.b2f"] if (fuse and cfg.layers > 0) else None)
         ready(["g_f", "b_f"])
 
         for l in reversed(range(cfg.layers)):
@@ -233,7 +235,7 @@ class Gpt2Step:
             # x_next = x_mid + dropout(W2 gelu(W1 ln2(x_mid) + b1f) + b2f)
             if dy is None:
                 dy = ops.dropout(dx, train, s_res2, p=p)
-            ops.colsum(dy, out=G("b2f"))
+                ops.colsum(dy, out=G("b2f"))
             self._wgrad(dy, a["h_act"], G("w2"))
             dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
             ops.colsum(dh_pre, out=G("b1f"))
@@ -258,7 +260,8 @@ class Gpt2Step:
             d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
             s_prev = seeds[3 * l] if l > 0 else 0  # the layer below's second residual dropout consumes this dx
             dx, dy = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx,
-                                  dropped=(train, s_prev, p) if (fuse and l > 0) else None)
+                                  dropped=(train, s_prev, p) if (fuse and l > 0) else None,
+                                  colsum_out=grads[f"l{l - 1}.b2f"] if (fuse and l > 0) else None)
             ready([f"l{l}.{n}" for n in ("w_o", "w_qkv", "g1", "b1")])
 
         # embedding + positions; the scatter accumulates onto the LM-head weight gradient (tied weights)
@@ -272,10 +275,11 @@ class Gpt2Step:
         ops.gemm(dlogits, x_f, a_kmajor=False, b_kmajor=False, M=V, N=x_f.shape[1], K=T, lda=dlogits.stride(0),
                  ldb=x_f.stride(0), out=out)
 
-    def _ln_bwd(self, dy, gamma, x, dgamma_out, dbeta_out, dx_add=None, dropped=None):
-        """Returns (dx, dropout(dx) or None)."""
+    def _ln_bwd(self, dy, gamma, x, dgamma_out, dbeta_out, dx_add=None, dropped=None, colsum_out=None):
+        """Returns (dx, dropout(dx) or None); colsum_out receives the column sums of dropout(dx)."""
         res = ops.layernorm_bwd(dy, (gamma, None), x, want_dx=True, want_dp=True, dx_add=dx_add,
-                                dgamma_out=dgamma_out, dbeta_out=dbeta_out, dropped=dropped)
+                                dgamma_out=dgamma_out, dbeta_out=dbeta_out, dropped=dropped,
+                                dropped_colsum_out=colsum_out if dropped is not None else None)
         return res[0], (res[3] if dropped is not None else None)
 
     # -- loss + gradients --

@@ -171,6 +171,10 @@ def main():
         n = len(xs)
         add("layernorm fwd [T,768] bf16", time_us(lambda i: ops.t_layernorm_fwd_t((g, bta), xs[i % n][0])), nbytes=2 * T * D * 2)
         add("layernorm bwd dx+dgamma+dbeta (+residual grad)", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db)), nbytes=4 * T * D * 2)
+        cs = torch.empty(D, device=dev)
+        add("layernorm bwd ... + dropout(dx) as a second output", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1))), nbytes=5 * T * D * 2)
+        add("layernorm bwd ... + dropout(dx) + its column sums", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1), dropped_colsum_out=cs)), nbytes=5 * T * D * 2)
+        add("colsum (bias grad) [T,768]", time_us(lambda i: ops.colsum(xs[i % n][0], out=cs)), nbytes=T * D * 2)
         add("dropout [T,768] (mask regenerated)", time_us(lambda i: ops.dropout(xs[i % n][0], True, 7, p=0.1)), nbytes=2 * T * D * 2)
         add("dropout + residual add [T,768]", time_us(lambda i: ops.dropout(xs[i % n][0], True, 7, residual=xs[i % n][1], p=0.1)), nbytes=3 * T * D * 2)
         del xs

@@ -68,11 +68,12 @@ def t_layernorm_fwd_t(layer_params, x: torch.Tensor) -> torch.Tensor:
 
 
 def layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=True, dx_add=None, dgamma_out=None,
-                  dbeta_out=None, dropped=None):
+                  dbeta_out=None, dropped=None, dropped_colsum_out=None):
     """Fused LayerNorm backward: (dx or None, dgamma or None, dbeta or None); dx_add is added onto dx.
     dgamma_out / dbeta_out: optional float32 destinations (e.g. views of a flat gradient buffer).
     dropped = (train, seed, p[, stream_id]): additionally return, as a fourth value, dropout(dx) for that mask site
-    (what t_dropout of dx would give), written by the same kernel."""
+    (what t_dropout of dx would give), written by the same kernel; dropped_colsum_out (float32[dim], needs want_dp)
+    receives that tensor's column sums, the bias gradient of the linear layer feeding the dropped branch."""
     x = _cuda(x, "x")
     dy = _cuda(dloss_dx, "dloss_dx")
     if dy.dtype != x.dtype:
@@ -96,7 +97,7 @@ def layernorm_bwd(dloss_dx, layer_params, x, want_dx=True, want_dp=True, dx_add=
         dxd = torch.empty_like(x)
         _lib.check(
             _lib.lib().ptj_layernorm_bwd_dropout(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx_add), _ptr(dx), _ptr(dxd),
-                                                 _ptr(dg), _ptr(db), _ptr(scratch), n_scratch, rows, dim,
+                                                 _ptr(dropped_colsum_out), _ptr(dg), _ptr(db), _ptr(scratch), n_scratch, rows, dim,
                                                  DROPOUT_RATE if p is None else p, int(bool(train)), _seed(seed),
                                                  stream_id, _dt(x), _stream()), "ptj_layernorm_bwd_dropout")
         return dx, dg, db, dxd

@@ -320,3 +320,30 @@ def test_layernorm_backward_with_fused_dropout_output(dtype):
         if train:
             kept = float((dxd != 0).float().mean())
             assert abs(kept - 0.7) < 0.01
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,dim", [(torch.float32, 768), (torch.bfloat16, 768), (torch.bfloat16, 1024),
+                                       (torch.float32, 64), (torch.bfloat16, 2048)])
+def test_layernorm_backward_fused_column_sums_of_dropped_output(dtype, dim):
+    """The optional third reduction of ptj_layernorm_bwd_dropout: column sums of the dropped output equal a float64
+    sum of that output (it is the bias gradient of the linear layer feeding the branch); the other results do not
+    change by a bit, and repeated calls give identical sums (fixed summation order)."""
+    ops = pkg("operators")
+    g = torch.Generator().manual_seed(5)
+    rows = 1000
+    x = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    dy = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    add = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    gamma = (1 + 0.1 * torch.randn(dim, generator=g)).cuda()
+    for train in (True, False):
+        dx0, dg0, db0, dxd0 = ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add, dropped=(train, 9, 0.1, 1))
+        cs = torch.full((dim,), 123.0, device="cuda")
+        dx1, dg1, db1, dxd1 = ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add, dropped=(train, 9, 0.1, 1),
+                                                dropped_colsum_out=cs)
+        assert torch.equal(dx0, dx1) and torch.equal(dg0, dg1) and torch.equal(db0, db1) and torch.equal(dxd0, dxd1)
+        ref = dxd1.double().sum(dim=0)
+        assert rel_err(cs, ref) < 1e-5
+        cs2 = torch.empty_like(cs)
+        ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add, dropped=(train, 9, 0.1, 1), dropped_colsum_out=cs2)
+        assert torch.equal(cs, cs2)
