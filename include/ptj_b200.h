@@ -103,6 +103,13 @@ int ptj_layernorm_bwd_noalloc(const void* dy, const void* x, const float* gamma,
 /* Replaces t_gelu_fwd_t (model_triton.py:254-260) and t_gelu_bkwd2_t (:296-304). */
 int ptj_gelu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream);
 int ptj_gelu_bwd(const void* dy, const void* x_preact, void* dx, int64_t n, int dtype, void* stream);
+/* t_gelu_bkwd2_t (model_triton.py:296-304) on a [rows, ld] matrix together with the column sums of its result as
+ * stored, colsum float[cols]: the hidden gradient of the FFN and the gradient of its first bias (the db of
+ * t_linear_bkwd2_p, :423-434) in one pass. dx may alias dy. scratch: ptj_colsum_scratch_floats(rows, cols) floats.
+ * Needs 16-byte aligned pointers, ld and cols multiples of the 16-byte vector and cols <= 8192, else
+ * PTJ_ERR_UNSUPPORTED (call ptj_gelu_bwd and ptj_colsum). Bit-reproducible (fixed summation order). */
+int ptj_gelu_bwd_colsum(const void* dy, const void* x_preact, void* dx, float* colsum, float* scratch,
+                        size_t scratch_floats, int64_t rows, int64_t cols, int64_t ld, int dtype, void* stream);
 
 /* ---- Dropout ---------------------------------------------------------------------------------------- */
 /* Replaces t_dropout_fwd_t (model_triton.py:1496-1506) and t_dropout_bkwd2_t (:1562-1572): the backward is the

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "ptj_layernorm_bwd_noalloc": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, _P]),
     "ptj_gelu_fwd": (c_int, [_P, _P, c_int64, c_int, _P]),
     "ptj_gelu_bwd": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
+    "ptj_gelu_bwd_colsum": (c_int, [_P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_dropout": (c_int, [_P, _P, _P, c_int64, c_float, c_int, c_uint64, c_uint32, c_int, _P]),
     "ptj_log_softmax_fwd": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_log_softmax_bwd": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),

@@ -246,6 +246,52 @@ colsum_stage1_rows_kernel(const T* __restrict__ x, float* __restrict__ partial, 
     if (c < cols) out[c] = t;
   }
 }
+// The same walk with the GELU backward folded in: dx = dy * gelu'(x) is written and the column sums of dx AS STORED
+// (rounded to T) are accumulated, i.e. one pass gives the FFN's hidden gradient and its first bias gradient
+// (t_gelu_bkwd2 followed by the db of t_linear_bkwd2_p in the reference, model_triton.py:296-304, 423-434).
+// Needs 16-byte aligned rows and cols a multiple of the vector; dx may alias dy.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_bwd_colsum_stage1_kernel(const T* dy, const T* __restrict__ x, T* dx, float* __restrict__ partial, int64_t rows,
+                              int64_t cols, int64_t ld, int64_t chunk) {
+  grid_dep_sync();
+  constexpr int V = Elem<T>::kVec;
+  constexpr bool kFast = sizeof(T) == 2;
+  __shared__ float red[8][32][V + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c0 = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * V;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * chunk;
+  const int64_t r1 = r0 + chunk < rows ? r0 + chunk : rows;
+  float s[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) s[j] = 0.f;
+  if (c0 < cols) {
+#pragma unroll 4
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      float g[V], v[V];
+      Elem<T>::load_vec(dy + r * ld + c0, g);
+      Elem<T>::load_vec(x + r * ld + c0, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        g[j] = Elem<T>::round(g[j] * gelu_tanh_grad<kFast>(v[j]));
+        s[j] += g[j];
+      }
+      Elem<T>::store_vec(dx + r * ld + c0, g);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) red[warp][lane][j] = s[j];
+  __syncthreads();
+  float* out = partial + static_cast<int64_t>(blockIdx.y) * cols;
+  for (int e = threadIdx.x; e < 32 * V; e += 256) {
+    const int gi = e / V, j = e - gi * V;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][gi][j];
+    const int64_t c = (static_cast<int64_t>(blockIdx.x) * 32 + gi) * V + j;
+    if (c < cols) out[c] = t;
+  }
+}
 // stage 2: a block owns 32 columns; its 8 warps sum strided subsets of the chunk rows, added in warp order.
 __global__ void __launch_bounds__(256)
 colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t cols, int nchunks) {
@@ -403,6 +449,32 @@ extern "C" int ptj_colsum(const void* x, float* out, float* scratch, size_t scra
   }
   PTJ_CHECK_LAUNCH();
   launch_k(colsum_stage2_kernel, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, scratch, out, cols, nchunks);
+  PTJ_CHECK_LAUNCH();
+  return PTJ_OK;
+}
+
+extern "C" int ptj_gelu_bwd_colsum(const void* dy, const void* x_preact, void* dx, float* colsum, float* scratch,
+                                   size_t scratch_floats, int64_t rows, int64_t cols, int64_t ld, int dtype,
+                                   void* stream) {
+  if (rows < 1 || cols < 1 || ld < cols) return PTJ_ERR_BAD_SHAPE;
+  if (!dy || !x_preact || !dx || !colsum) return PTJ_ERR_BAD_SHAPE;
+  if (!scratch || scratch_floats < ptj_colsum_scratch_floats(rows, cols)) return PTJ_ERR_WORKSPACE;
+  if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  const int V = dtype == PTJ_F32 ? 4 : 8;
+  if (!aligned16(dy) || !aligned16(x_preact) || !aligned16(dx) || ld % V != 0 || cols % V != 0) return PTJ_ERR_UNSUPPORTED;
+  if (!colsum_split_rows(cols)) return PTJ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nchunks = colsum_chunks(rows, cols);
+  const int64_t chunk = ceil_div(rows, nchunks);
+  dim3 grid(static_cast<unsigned>(ceil_div(cols / V, 32)), static_cast<unsigned>(nchunks));
+  if (dtype == PTJ_F32)
+    launch_k(gelu_bwd_colsum_stage1_kernel<float>, grid, 256, 0, st, static_cast<const float*>(dy),
+             static_cast<const float*>(x_preact), static_cast<float*>(dx), scratch, rows, cols, ld, chunk);
+  else
+    launch_k(gelu_bwd_colsum_stage1_kernel<__nv_bfloat16>, grid, 256, 0, st, static_cast<const __nv_bfloat16*>(dy),
+             static_cast<const __nv_bfloat16*>(x_preact), static_cast<__nv_bfloat16*>(dx), scratch, rows, cols, ld, chunk);
+  PTJ_CHECK_LAUNCH();
+  launch_k(colsum_stage2_kernel, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, scratch, colsum, cols, nchunks);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

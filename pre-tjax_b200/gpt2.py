@@ -17,6 +17,7 @@ the logits with their gradient; nothing uses atomics, so results are bit-reprodu
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
 
@@ -140,6 +141,10 @@ class Gpt2Step:
         # logits rows are padded so that every row starts on a 16-byte boundary
         self.vocab_ld = (cfg.vocab + 127) // 128 * 128
         self._ws = None
+        # FFN backward: gelu' inside the input-gradient GEMM's epilogue followed by a column-sum pass over its output
+        # (default; measured 0.1 ms per GPT-2 small step faster), or a plain GEMM followed by ONE elementwise pass that
+        # applies gelu' and sums the columns (PTJ_SPLIT_GELU_BWD=1). Same results.
+        self.split_gelu_bwd = os.environ.get("PTJ_SPLIT_GELU_BWD", "0") == "1"
 
     # -- helpers --
     def _wgrad(self, dy2d, x2d, out, accumulate=False):
@@ -237,8 +242,12 @@ class Gpt2Step:
                 dy = ops.dropout(dx, train, s_res2, p=p)
                 ops.colsum(dy, out=G("b2f"))
             self._wgrad(dy, a["h_act"], G("w2"))
-            dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
-            ops.colsum(dh_pre, out=G("b1f"))
+            if self.split_gelu_bwd and F % 8 == 0 and F <= 8192:
+                # plain product, then one elementwise pass that applies gelu' in place and sums the columns (b1f)
+                dh_pre, _ = ops.gelu_bwd_colsum(self._dgrad(dy, g("w2")), a["h_pre"], colsum_out=G("b1f"), in_place=True)
+            else:
+                dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
+                ops.colsum(dh_pre, out=G("b1f"))
             self._wgrad(dh_pre, a["ln2"], G("w1"))
             d_ln2 = self._dgrad(dh_pre, g("w1"))
             dx, dy = self._ln_bwd(d_ln2, g("g2"), a["x_mid"], G("g2"), G("b2"), dx_add=dx,

@@ -449,6 +449,21 @@ def colsum(x2d, cols=None, out=None):
     return out
 
 
+def gelu_bwd_colsum(dy2d, x_preact2d, colsum_out=None, in_place=False):
+    """(dy * gelu'(x_preact), its column sums in float32) in one pass over [rows, cols] matrices: the FFN's hidden
+    gradient and the gradient of its first bias (model_triton.py:296-304 followed by the db of :423-434)."""
+    dy, x = _cuda(dy2d, "dy"), _cuda(x_preact2d, "x_preact")
+    assert dy.dim() == 2 and dy.shape == x.shape and dy.dtype == x.dtype
+    rows, cols = dy.shape
+    dx = dy if in_place else torch.empty_like(dy)
+    out = colsum_out if colsum_out is not None else torch.empty(cols, device=dy.device, dtype=torch.float32)
+    n = _lib.lib().ptj_colsum_scratch_floats(rows, cols)
+    scratch = torch.empty(max(n, 1), device=dy.device, dtype=torch.float32)
+    _lib.check(_lib.lib().ptj_gelu_bwd_colsum(_ptr(dy), _ptr(x), _ptr(dx), _ptr(out), _ptr(scratch), n, rows, cols, cols,
+                                              _dt(dy), _stream()), "ptj_gelu_bwd_colsum")
+    return dx, out
+
+
 def last_kernel_fault() -> int:
     code = ctypes.c_uint(0)
     _lib.check(_lib.lib().ptj_last_kernel_fault(_stream(), ctypes.byref(code)), "ptj_last_kernel_fault")

@@ -53,7 +53,7 @@ def test_validation_needs_no_device(lib):
     assert lib.ptj_dropout(None, None, None, 8, ctypes.c_float(1.5), 1, 0, 0, 0, None) == -1
     assert lib.ptj_adamw(None, None, None, None, None, 6, None, None, 0, 0, 0, 0, 0, 0, 1, 1, None, 0, None) == -1
     assert lib.ptj_gemm(None, None, None, None, None, None, 8, 8, 8, 8, 8, 8, 1, 1, 1, 1, 0, None, 1, None, 0, None) == -1
-    assert lib.ptj_layernorm_bwd_scratch_floats(1024, 768) == 128 * 2 * 768
+    assert lib.ptj_layernorm_bwd_scratch_floats(1024, 768) == 128 * 3 * 768  # dgamma, dbeta, optional column sums
     assert lib.ptj_colsum_scratch_floats(0, 10) == 0
     assert lib.ptj_launch_count() == before
 

@@ -347,3 +347,24 @@ def test_layernorm_backward_fused_column_sums_of_dropped_output(dtype, dim):
         cs2 = torch.empty_like(cs)
         ops.layernorm_bwd(dy, (gamma, None), x, dx_add=add, dropped=(train, 9, 0.1, 1), dropped_colsum_out=cs2)
         assert torch.equal(cs, cs2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (77, 64), (1000, 3072), (513, 1000)])
+def test_gelu_backward_with_fused_column_sums(dtype, rows, cols):
+    """ptj_gelu_bwd_colsum: the gradient equals ptj_gelu_bwd bit for bit (also in place), the column sums equal a float64
+    sum of the stored gradient, and two calls give identical sums."""
+    ops = pkg("operators")
+    g = torch.Generator().manual_seed(rows + cols)
+    dy = torch.randn(rows, cols, generator=g).to(dtype).cuda()
+    x = (2 * torch.randn(rows, cols, generator=g)).to(dtype).cuda()
+    ref = ops.t_gelu_bkwd2_t(dy, x)
+    dx, cs = ops.gelu_bwd_colsum(dy, x)
+    assert torch.equal(dx, ref)
+    assert rel_err(cs, ref.double().sum(dim=0)) < 1e-5
+    if dtype == torch.float32:
+        assert rel_err(dx, orc.gelu_bwd(dy.double().cpu(), x.double().cpu())) < 1e-5
+    dy2 = dy.clone()
+    dx2, cs2 = ops.gelu_bwd_colsum(dy2, x, in_place=True)
+    assert dx2.data_ptr() == dy2.data_ptr() and torch.equal(dx2, ref) and torch.equal(cs2, cs)
