@@ -38,12 +38,13 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
   static constexpr int kBiasBytes = kEpilogueWarps * chunks_per_warp(BN) * 128;  // each epilogue warp's bias slices
-  static constexpr int kFixedBytes = kStripsBytes + kBiasBytes + 1024 + kBarrierBytes;
-  static constexpr int kFit = (kSmemLimit - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kFit < 6 ? kFit : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
+  static constexpr int fixed_bytes(int strip) { return kEpilogueWarps * strip + kBiasBytes + 1024 + kBarrierBytes; }
+  static constexpr int stages(int strip) {
+    const int fit = (kSmemLimit - fixed_bytes(strip)) / kStageBytes;
+    return fit < 6 ? fit : 6;
+  }
+  static constexpr int smem_bytes(int strip) { return stages(strip) * kStageBytes + fixed_bytes(strip); }
   static constexpr int kTmemCols = 512;     // two accumulator buffers, the second at column 256
   static constexpr int kAccStride = 256;
 };
@@ -55,6 +56,7 @@ struct GemmParams {
   float* workspace;  // [split_k, M, N] partial sums when split_k > 1
   int out_bf16;
   int tma_store;  // outputs leave through tensor-map tile stores (bf16 output, 16-byte aligned rows, K not split)
+  int tma_side;   // ... and the epilogue's side input arrives through tile loads, one block ahead
   int debug;  // timing experiments only (results are garbage), bits: 1 = no TMA copies, 2 = no MMAs, 4 = no epilogue
   unsigned int* fault;
 };
@@ -63,7 +65,27 @@ struct GemmParams {
 // 64-byte swizzle.
 struct alignas(64) StoreMaps {
   CUtensorMap c, x;
+  CUtensorMap s;  // the epilogue's side input (residual / saved pre-activation), same boxes
 };
+
+constexpr int kEpiBlockBytes = 2048;  // one 32 x 32 bf16 block
+
+// The side input of a warp's blocks arrives through tile loads issued one block ahead into a landing buffer behind the
+// warp's store strip, so that its latency hides under the previous block's arithmetic and the accumulator wait.
+struct SidePrefetch {
+  uint8_t* buf;    // kEpiBlockBytes, 512-byte aligned; nullptr: side inputs are read with plain loads
+  uint64_t* bar;   // completes when a block has landed
+  uint32_t waits;  // blocks waited for so far (the barrier's parity)
+};
+
+// Lane 0 requests the side-input block at (row0, n0). All lanes call.
+__device__ __forceinline__ void side_prefetch_issue(const SidePrefetch& sp, const CUtensorMap* map, int64_t row0,
+                                                    int64_t n0, int lane) {
+  if (lane == 0) {
+    mbar_expect_tx(sp.bar, kEpiBlockBytes);
+    tma_load_2d(sp.buf, map, sp.bar, static_cast<int>(n0), static_cast<int>(row0));
+  }
+}
 
 // One 32 x 32 bf16 block, one row per lane, leaves through the tensor map: rows are parked densely (64 bytes each) in
 // the warp's strip (swizzled) and ONE lane issues an asynchronous tile store, so no warp waits on the memory system. The strip
@@ -94,10 +116,11 @@ __device__ __forceinline__ void warp_store_block_tma(uint8_t* strip, const CUten
 
 // Epilogue of one 32-row x 32-column block of an accumulator tile (one row per lane): arithmetic per thread, stores
 // through the warp's staging strip when the block is full and rows are 16-byte aligned, else per thread.
-template <typename TOut>
+template <typename TOut, bool SIDE>
 __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t* strip, int64_t row0, int64_t row,
                                               int64_t n0, float (&acc)[32], int lane, const float* bias_s,
-                                              const StoreMaps* maps) {
+                                              const StoreMaps* maps, SidePrefetch& sp, const AbortCtx& ctx,
+                                              int64_t next_n0, bool& ok) {
   // (warp-uniform) only full-width blocks: at a ragged right edge the tile store was seen to write the whole 16-byte
   // piece that holds the last valid column, i.e. up to seven padding columns
   const bool use_tma = maps != nullptr && sizeof(TOut) == 2 && row0 < ep.M && n0 + 32 <= ep.N;
@@ -118,9 +141,28 @@ __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t*
     else if (inside) store_row<TOut, 32>(aux_out + row * ep.ldc, n0, ep.N, false, acc);
   }
   float side[32];
-  if (const void* sp = epilogue_side_input(ep)) {
-    if (staged) warp_load_block<TOut>(strip, static_cast<const TOut*>(sp), ep.ldc, row0, n0, ep.M, side, lane);
-    else if (inside) load_row<TOut, 32>(static_cast<const TOut*>(sp) + row * ep.ldc, n0, ep.N, false, side);
+  if (SIDE) {
+    // (warp-uniform) a block inside the matrix was requested one block ago (or at the start of the tile)
+    if (row0 < ep.M && n0 < ep.N) {
+      ok = __all_sync(0xffffffffu, mbar_wait(sp.bar, sp.waits & 1u, ctx, 0x0302u));
+      if (!ok) return;
+      ++sp.waits;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {  // this lane's row, stored with the tensor map's 64-byte swizzle
+        const uint4 t = *reinterpret_cast<const uint4*>(sp.buf + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4));
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          side[q * 8 + 2 * i] = __uint_as_float(w[i] << 16);
+          side[q * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      }
+      __syncwarp();
+      if (next_n0 >= 0 && next_n0 < ep.N) side_prefetch_issue(sp, &maps->s, row0, next_n0, lane);
+    }
+  } else if (const void* sptr = epilogue_side_input(ep)) {
+    if (staged) warp_load_block<TOut>(strip, static_cast<const TOut*>(sptr), ep.ldc, row0, n0, ep.M, side, lane);
+    else if (inside) load_row<TOut, 32>(static_cast<const TOut*>(sptr) + row * ep.ldc, n0, ep.N, false, side);
   }
   if (inside) epilogue_post<TOut, 32>(ep, row, n0, acc, side);
   if (use_tma) {
@@ -135,19 +177,24 @@ __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t*
   else if (inside) store_row<TOut, 32>(c + row * ep.ldc, n0, ep.N, false, acc);
 }
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool SIDE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ StoreMaps smaps, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
-  float* bias_smem = reinterpret_cast<float*>(strips + Cfg::kStripsBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes + Cfg::kBiasBytes);
+  // SIDE: the epilogue's side input arrives through tile loads, which takes a landing buffer per epilogue warp behind
+  // its store strip (and, for the widest tiles, a stage of the operand ring)
+  constexpr int kStrip = SIDE ? 2 * kEpiBlockBytes : kStripBytes;
+  constexpr int nst = Cfg::stages(kStrip);
+  uint8_t* strips = smem + nst * Cfg::kStageBytes;
+  float* bias_smem = reinterpret_cast<float*>(strips + kEpilogueWarps * kStrip);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + kEpilogueWarps * kStrip + Cfg::kBiasBytes);
+  uint64_t* side_bars = bars + 24;  // one per epilogue warp
   uint64_t* full = bars;
-  uint64_t* empty = bars + Cfg::kStages;
-  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* empty = bars + nst;
+  uint64_t* tmem_full = bars + 2 * nst;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -156,10 +203,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const AbortCtx ctx{abort_flag, p.fault};
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
+    for (int w = 0; w < kEpilogueWarps; ++w) mbar_init(&side_bars[w], 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], kEpilogueWarps);
@@ -168,6 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (SIDE) prefetch_tensormap(&smaps.s);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -199,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0101u)) { ok = false; break; }
           if (p.debug & 1) {
             mbar_arrive(&full[stage]);
-            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+            if (++stage == nst) { stage = 0; phase ^= 1u; }
             continue;
           }
           mbar_expect_tx(&full[stage], Cfg::kStageBytes);
@@ -219,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int h = 0; h < BN / 64; ++h)
               tma_load_2d(sb + h * 8192, &tmap_b, &full[stage], n_blk * BN + h * 64, kb * BK);
           }
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -256,7 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!(p.debug & 2)) mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
         if (ok) mma_commit(&tmem_full[buf]);
       }
@@ -267,6 +316,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     constexpr int kChunks = chunks_per_warp(BN);  // this warp takes chunks sub, sub + kWarpsPerQuarter, ...
     int it = 0;
     bool ok = true;
+    SidePrefetch sp{SIDE ? strips + (warp - 2) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - 2], 0u};
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
@@ -284,12 +334,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         __syncwarp();
       }
+      const int64_t row0 = static_cast<int64_t>(m_blk) * BM + quarter * 32;
+      const int64_t row = row0 + lane;
+      if (SIDE) {
+        // the side input of this warp's first block of the tile, requested before the accumulator is even complete
+        const int64_t nf = static_cast<int64_t>(n_blk) * BN + sub * 32;
+        if (row0 < p.M && nf < p.N) side_prefetch_issue(sp, &smaps.s, row0, nf, lane);
+      }
       ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0301u);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after_sync();
-      const int64_t row0 = static_cast<int64_t>(m_blk) * BM + quarter * 32;
-      const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * Cfg::kAccStride);
 #pragma unroll 1
@@ -303,7 +358,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
-        uint8_t* strip = strips + (warp - 2) * kStripBytes;
+        uint8_t* strip = strips + (warp - 2) * kStrip;
         const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
@@ -315,9 +370,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
           }
         } else if (p.out_bf16) {
-          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane, bias_c, p.tma_store ? &smaps : nullptr);
+          const int ncol = (sub + (chunk + 1) * kWarpsPerQuarter) * 32;  // this warp's next block of the tile, if any
+          const int64_t next_n0 = ncol < BN ? static_cast<int64_t>(n_blk) * BN + ncol : -1;
+          tile_epilogue<__nv_bfloat16, SIDE>(p.ep, strip, row0, row, n0, acc, lane, bias_c,
+                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok);
+          if (!ok) break;
         } else {
-          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr);
+          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok);
         }
       }
       tc_fence_before_sync();
@@ -356,17 +415,18 @@ struct PairCfg {
   static constexpr int kBBytes = (BN / 2) * BK * 2;  // per CTA: half of the tile's B rows
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kStripsBytes = kEpilogueWarps * kStripBytes;  // epilogue staging, one strip per warp
   static constexpr int kBiasBytes = kEpilogueWarps * chunks_per_warp(BN) * 128;  // each epilogue warp's bias slices
-  static constexpr int kFixedBytes = kStripsBytes + kBiasBytes + 1024 + kBarrierBytes;
-  static constexpr int kFit = (kSmemLimit - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kFit < 6 ? kFit : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kFixedBytes;
+  static constexpr int fixed_bytes(int strip) { return kEpilogueWarps * strip + kBiasBytes + 1024 + kBarrierBytes; }
+  static constexpr int stages(int strip) {
+    const int fit = (kSmemLimit - fixed_bytes(strip)) / kStageBytes;
+    return fit < 6 ? fit : 6;
+  }
+  static constexpr int smem_bytes(int strip) { return stages(strip) * kStageBytes + fixed_bytes(strip); }
   static constexpr int kTmemCols = 512;
   static constexpr int kAccStride = 256;
 };
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool SIDE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ StoreMaps smaps, const GemmParams p) {
@@ -374,12 +434,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int HB = BN / 2;  // B rows held by one CTA
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* strips = smem + Cfg::kStages * Cfg::kStageBytes;
-  float* bias_smem = reinterpret_cast<float*>(strips + Cfg::kStripsBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + Cfg::kStripsBytes + Cfg::kBiasBytes);
+  // SIDE: the epilogue's side input arrives through tile loads, which takes a landing buffer per epilogue warp behind
+  // its store strip (and, for the widest tiles, a stage of the operand ring)
+  constexpr int kStrip = SIDE ? 2 * kEpiBlockBytes : kStripBytes;
+  constexpr int nst = Cfg::stages(kStrip);
+  uint8_t* strips = smem + nst * Cfg::kStageBytes;
+  float* bias_smem = reinterpret_cast<float*>(strips + kEpilogueWarps * kStrip);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(strips + kEpilogueWarps * kStrip + Cfg::kBiasBytes);
+  uint64_t* side_bars = bars + 24;  // one per epilogue warp
   uint64_t* full = bars;                      // used in the leader only
-  uint64_t* empty = bars + Cfg::kStages;      // one set per CTA, both signalled by the leader's commits
-  uint64_t* tmem_full = bars + 2 * Cfg::kStages;
+  uint64_t* empty = bars + nst;      // one set per CTA, both signalled by the leader's commits
+  uint64_t* tmem_full = bars + 2 * nst;
   uint64_t* tmem_empty = tmem_full + 2;       // used in the leader only: 8 local + 8 remote epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -389,10 +454,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const AbortCtx ctx{abort_flag, p.fault};
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
+    for (int w = 0; w < kEpilogueWarps; ++w) mbar_init(&side_bars[w], 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], 2 * kEpilogueWarps);
@@ -401,6 +467,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (SIDE) prefetch_tensormap(&smaps.s);
   }
   __syncthreads();
   if (warp == 1) {
@@ -451,7 +518,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
             for (int h = 0; h < HB / 64; ++h) tma_load_2d_pair(sb + h * 8192, &tmap_b, leader_full, n0 + h * 64, kb * BK);
           }
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -488,7 +555,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           mma_commit_pair(&empty[stage], 3);  // stage free in both CTAs once these MMAs have read it
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
         if (ok) mma_commit_pair(&tmem_full[buf], 3);
       }
@@ -501,6 +568,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     int it = 0;
     bool ok = true;
+    SidePrefetch sp{SIDE ? strips + (warp - 2) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - 2], 0u};
     for (int item = pair; item < total && ok; item += npairs, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
@@ -518,12 +586,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         __syncwarp();
       }
+      const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * BM + static_cast<int64_t>(rank) * BM + quarter * 32;
+      const int64_t row = row0 + lane;
+      if (SIDE) {
+        // the side input of this warp's first block of the tile, requested before the accumulator is even complete
+        const int64_t nf = static_cast<int64_t>(n_blk) * BN + sub * 32;
+        if (row0 < p.M && nf < p.N) side_prefetch_issue(sp, &smaps.s, row0, nf, lane);
+      }
       ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0601u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * BM + static_cast<int64_t>(rank) * BM + quarter * 32;
-      const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * Cfg::kAccStride);
 #pragma unroll 1
@@ -537,7 +610,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
-        uint8_t* strip = strips + (warp - 2) * kStripBytes;
+        uint8_t* strip = strips + (warp - 2) * kStrip;
         const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
@@ -549,9 +622,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
           }
         } else if (p.out_bf16) {
-          tile_epilogue<__nv_bfloat16>(p.ep, strip, row0, row, n0, acc, lane, bias_c, p.tma_store ? &smaps : nullptr);
+          const int ncol = (sub + (chunk + 1) * kWarpsPerQuarter) * 32;  // this warp's next block of the tile, if any
+          const int64_t next_n0 = ncol < BN ? static_cast<int64_t>(n_blk) * BN + ncol : -1;
+          tile_epilogue<__nv_bfloat16, SIDE>(p.ep, strip, row0, row, n0, acc, lane, bias_c,
+                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok);
+          if (!ok) break;
         } else {
-          tile_epilogue<float>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr);
+          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok);
         }
       }
       tc_fence_before_sync();
@@ -655,17 +732,19 @@ gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64
   for (int i = 0; i < 4; ++i) epilogue_row_segment<TOut, 8>(ep, m0 + ty * 4 + i, n0 + tx * 8, acc[i]);
 }
 
-template <int BN, bool AK, bool BK_>
+template <int BN, bool AK, bool BK_, bool SIDE>
 int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_tc_kernel<BN, AK, BK_>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+  // per epilogue warp: the store strip, plus a landing buffer when side inputs arrive through tile loads
+  const int smem_bytes = Cfg::smem_bytes(SIDE ? 2 * kEpiBlockBytes : kStripBytes);
+  auto kern = gemm_tc_kernel<BN, AK, BK_, SIDE>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
   const int total = p.num_m * p.num_n * p.split_k;
   const int grid = total < kNumSMs ? total : kNumSMs;
-  launch_k(kern, grid, kGemmThreads, Cfg::kSmemBytes, st, ta, tb, sm, p);
+  launch_k(kern, grid, kGemmThreads, smem_bytes, st, ta, tb, sm, p);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
@@ -691,12 +770,13 @@ int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int6
   return PTJ_OK;
 }
 
-template <int BN, bool AK, bool BK_>
+template <int BN, bool AK, bool BK_, bool SIDE>
 int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p,
                    cudaStream_t st) {
   using Cfg = PairCfg<BN>;
-  auto kern = gemm_tc_pair_kernel<BN, AK, BK_>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+  const int smem_bytes = Cfg::smem_bytes(SIDE ? 2 * kEpiBlockBytes : kStripBytes);
+  auto kern = gemm_tc_pair_kernel<BN, AK, BK_, SIDE>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
@@ -705,7 +785,7 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -772,7 +852,7 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
               (aux_out == nullptr || aligned16(aux_out));
   {
     const char* e = getenv("PTJ_GEMM_TUNE");
-    ep.tune = e != nullptr ? atoi(e) : 11;
+    ep.tune = e != nullptr ? atoi(e) : 27;
   }
   if (dropout != nullptr) {
     if (!(dropout->p >= 0.f && dropout->p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
@@ -832,6 +912,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
     if (epilogue == PTJ_EPI_GELU && aux_out != nullptr && !make_tmap_bf16_sw64(&smaps.x, aux_out, 2, dims, str, box))
       return PTJ_ERR_LAUNCH;
     p.tma_store = 1;
+    if ((ep.tune & 16) && a_kmajor && (epilogue == PTJ_EPI_GELU_BWD || epilogue == PTJ_EPI_DROPOUT_RESID)) {
+      if (!make_tmap_bf16_sw64(&smaps.s, aux, 2, dims, str, box)) return PTJ_ERR_LAUNCH;
+      p.tma_side = 1;
+    }
   }
 
   if (use_pair_kernel(M, N, K)) {
@@ -853,10 +937,15 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
       const uint32_t box_k[2] = {64, static_cast<uint32_t>(pbn / 2)}, box_mn[2] = {64, 64};
       if (!make_tmap_bf16(&tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
     }
-    int prc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true>(ta, tb, smaps, p, st)
-                                   : launch_tc_pair<256, true, false>(ta, tb, smaps, p, st))
-                       : (b_kmajor ? launch_tc_pair<256, false, true>(ta, tb, smaps, p, st)
-                                   : launch_tc_pair<256, false, false>(ta, tb, smaps, p, st));
+    int prc;
+    if (p.tma_side)  // (A is K-major whenever tma_side is set)
+      prc = b_kmajor ? launch_tc_pair<256, true, true, true>(ta, tb, smaps, p, st)
+                     : launch_tc_pair<256, true, false, true>(ta, tb, smaps, p, st);
+    else
+      prc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true, false>(ta, tb, smaps, p, st)
+                                 : launch_tc_pair<256, true, false, false>(ta, tb, smaps, p, st))
+                     : (b_kmajor ? launch_tc_pair<256, false, true, false>(ta, tb, smaps, p, st)
+                                 : launch_tc_pair<256, false, false, false>(ta, tb, smaps, p, st));
     if (prc != PTJ_OK) return prc;
     return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
   }
@@ -896,10 +985,12 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
 
   int rc;
 #define PTJ_TC(BN_)                                                              \
-  (a_kmajor ? (b_kmajor ? launch_tc<BN_, true, true>(ta, tb, smaps, p, st)              \
-                        : launch_tc<BN_, true, false>(ta, tb, smaps, p, st))            \
-            : (b_kmajor ? launch_tc<BN_, false, true>(ta, tb, smaps, p, st)             \
-                        : launch_tc<BN_, false, false>(ta, tb, smaps, p, st)))
+  (p.tma_side ? (b_kmajor ? launch_tc<BN_, true, true, true>(ta, tb, smaps, p, st)                \
+                          : launch_tc<BN_, true, false, true>(ta, tb, smaps, p, st))              \
+   : a_kmajor ? (b_kmajor ? launch_tc<BN_, true, true, false>(ta, tb, smaps, p, st)               \
+                          : launch_tc<BN_, true, false, false>(ta, tb, smaps, p, st))             \
+              : (b_kmajor ? launch_tc<BN_, false, true, false>(ta, tb, smaps, p, st)              \
+                          : launch_tc<BN_, false, false, false>(ta, tb, smaps, p, st)))
   rc = bn == 128 ? PTJ_TC(128) : (bn == 192 ? PTJ_TC(192) : PTJ_TC(256));
 #undef PTJ_TC
   if (rc != PTJ_OK) return rc;

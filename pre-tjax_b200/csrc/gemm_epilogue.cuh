@@ -22,7 +22,8 @@ struct EpilogueParams {
   uint64_t seed;
   uint32_t stream_id;
   int tune;              // bit 0 = bias staged in shared memory per tile, bit 1 = two-wide GELU math, bit 3 = bf16
-                         // outputs leave through tensor-map tile stores (PTJ_GEMM_TUNE overrides the default)
+                         // outputs leave through tensor-map tile stores, bit 4 = side inputs arrive through tile loads one block ahead
+                         // (PTJ_GEMM_TUNE overrides the default)
 };
 
 template <typename TOut, int CNT>
