@@ -36,7 +36,7 @@ UNIT = "tokens/s"
 MICRO_BATCH = 8
 # DRAM bytes (read + write) per launch of the dominant kernel, averaged over the GEMM launches of the train step,
 # from the ncu capture summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 84.8e6  # profiles/gemm_tc_kernels_train_step_dram_traffic.md (ncu, average GEMM launch)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 84.8e6  # DRAM read + write bytes of the average GEMM launch of a step, from an ncu capture
 
 
 def zipf_ids(vocab: int, shape, seed: int, a: float = 1.1) -> torch.Tensor:

@@ -24,12 +24,14 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = os.environ.get("PTJ_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("PTJ_REFERENCE_DIR")  # a checkout of martin-kukla/pre-tjax
 OUT = Path(__file__).resolve().parent
 SAMPLE_STRIDE = 97
 
 
 def load_reference(dropout_rate: float):
+    if not REF:
+        raise SystemExit("set PTJ_REFERENCE_DIR to a checkout of martin-kukla/pre-tjax")
     if REF not in sys.path:
         sys.path.insert(0, REF)
     import model_torch_func as mtf
