@@ -186,7 +186,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ops = ptj.operators
-    tc = ptj.TrainConfig(lr=6e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip=1.0, seed=0)
+    tc = ptj.TrainConfig.benchmark_recipe(seed=0)
     trainer = ptj.Trainer(cfg, tc, device=f"cuda:{local}", world=world, rank=rank)
     n_batches = 4
     host = [zipf_ids(cfg.vocab, (MICRO_BATCH, cfg.seq + 1), seed=17 + 1000 * rank + i).pin_memory() for i in range(n_batches)]

@@ -128,12 +128,13 @@ int ptj_log_softmax_bwd(const void* dy, const void* x, void* dx, int64_t rows, i
 /* ---- cross entropy --------------------------------------------------------------------------------- */
 /* Replaces t_avg_cross_entropy_loss_bkwd3_t (loss_and_optimizer_triton.py:176-197), t_avg_cross_entropy_loss
  * (:23-32) and accuracy (:199-200). Label 0 is padding: such rows add nothing to the loss, the accuracy or the
- * token count, and get a zero gradient row.
+ * token count, and get a zero gradient row. A label outside [0, cols) (an id beyond the vocabulary, which the
+ * reference would fault on) is treated the same way and is not counted either.
  *   labels      int32[rows]
  *   logits      [rows, ld] (cols valid)
  *   dlogits     same layout, may alias logits (in place), or NULL for forward only
  *   row_stats   float[2*rows] scratch: per-row loss and per-row hit
- *   n_valid     float[1]: number of rows with label != 0. If count_in_kernel != 0 it is computed here from
+ *   n_valid     float[1]: number of rows with 0 < label < cols. If count_in_kernel != 0 it is computed here from
  *               labels, otherwise it is read (lets data-parallel callers supply the global count).
  *   out3        float[3]: mean loss, accuracy, n_valid / rows   (deterministic single-block reduction)
  */

@@ -7,8 +7,10 @@ parameter pytree of model_torch_func.py:36-43 and ``moments = [m, v]`` two pytre
 (``init_adam_w``, loss_and_optimizer_triton.py:362-363). Tensors are float32. Files written here hold CPU tensors (a
 pickle of CUDA tensors can only be opened on a machine with a GPU); ``load_checkpoint`` moves them to the device asked
 for. A ``Trainer`` keeps parameters and moments in flat buffers; ``trainer_state`` / ``load_trainer_state`` convert
-between those and the pytrees. AdamW's step count is ``i + 1`` at micro-step ``i`` (train_gpt2_triton.py:321), so a
-trainer that has taken ``t`` steps is saved as ``i = t - 1`` having been completed, and resumes at ``t``.
+between those and the pytrees. The reference increments ``i`` BEFORE it pickles (train_gpt2_triton.py:408-419): the
+saved ``i`` is the number of completed micro-steps, which is also the index of the next one, and the next AdamW call
+``adam_w_in_place(..., i)`` uses step count ``i + 1`` (:321). A trainer that has taken ``t`` steps is therefore saved
+as ``i = t`` (file name ``checkpoint_{t}.pkl`` in the reference's scheme) and a loaded ``i`` becomes ``trainer.t = i``.
 """
 from __future__ import annotations
 
@@ -73,14 +75,22 @@ def trainer_state(trainer):
 
 
 def save_trainer(path: str, trainer, ds_train_rows_read: int = 0) -> None:
-    """The trainer has completed ``trainer.t`` micro-steps, i.e. indices 0 .. t-1."""
+    """The trainer has completed ``trainer.t`` micro-steps; like the reference, which counts the step before it
+    pickles (train_gpt2_triton.py:408-419), the file stores ``i = trainer.t``."""
     params, moments = trainer_state(trainer)
-    save_checkpoint(path, trainer.t - 1, ds_train_rows_read, params, moments)
+    save_checkpoint(path, trainer.t, ds_train_rows_read, params, moments)
+
+
+def checkpoint_name(run_dir: str, trainer) -> str:
+    """The reference's file name for a checkpoint taken now: ``runs/<run>/checkpoint_<i>.pkl`` with the completed
+    step count (train_gpt2_triton.py:415)."""
+    return os.path.join(run_dir, f"checkpoint_{trainer.t}.pkl")
 
 
 def load_trainer_state(trainer, path: str) -> Tuple[int, int]:
     """Copies a checkpoint's parameters and moments into the trainer's flat buffers, refreshes the bf16 weight shadow
-    and sets the step counter so that the next step is ``i + 1``. Returns ``(i, ds_train_rows_read)``."""
+    and sets the step counter to the ``i`` completed steps, so that the next update runs AdamW with step count
+    ``i + 1`` and draws the dropout seeds of step index ``i``. Returns ``(i, ds_train_rows_read)``."""
     i, rows, params, moments = load_checkpoint(path, trainer.device)
     cur, (m, v) = trainer_state(trainer)
     check_same_structure(cur, params, "parameters")
@@ -88,6 +98,6 @@ def load_trainer_state(trainer, path: str) -> Tuple[int, int]:
         for gd, gs in zip(dst_tree, src_tree):
             for d, s in zip(gd, gs):
                 d.copy_(s.to(torch.float32))
-    trainer.t = i + 1
+    trainer.t = i
     trainer._refresh_shadow()
     return i, rows

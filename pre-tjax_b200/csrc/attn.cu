@@ -1,7 +1,5 @@
 // C entry points of causal attention: validate, then route to the tcgen05 kernels (bf16, d_head 64, seq % 128 == 0)
 // or to the exact-fp32 CUDA-core kernels (everything else).
-#include <cstdlib>
-
 #include "attn_common.cuh"
 
 using namespace ptj;
@@ -20,18 +18,11 @@ AttnDropout make_dropout(float p, int train, uint64_t seed, uint32_t stream_id) 
   d.stream_id = stream_id;
   return d;
 }
-bool force_simt() {
-  static const bool v = [] {
-    const char* e = std::getenv("PTJ_ATTN_SIMT");
-    return e != nullptr && e[0] == '1';
-  }();
-  return v;
-}
 }  // namespace
 
 extern "C" size_t ptj_attn_keep_bits_bytes(const ptj_attn_shape* shape, int dtype) {
   const void* none[1] = {nullptr};
-  if (!shape_ok(shape) || dtype != PTJ_BF16 || force_simt() || !attn_tc_supported(*shape, none, 0)) return 0;
+  if (!shape_ok(shape) || dtype != PTJ_BF16 || !attn_tc_supported(*shape, none, 0)) return 0;
   return attn_keep_bits_bytes(*shape);
 }
 
@@ -53,14 +44,14 @@ extern "C" int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const AttnDropout dr = make_dropout(p, train, seed, stream_id);
   const void* ptrs[4] = {q, k, v, o};
-  if (dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, ptrs, 4))
+  if (dtype == PTJ_BF16 && attn_tc_supported(*shape, ptrs, 4))
     return attn_fwd_tc(q, k, v, o, row_max, row_sum, keep_bits, *shape, dr, st);
   return attn_fwd_simt(q, k, v, o, row_max, row_sum, *shape, dr, dtype, st);
 }
 
 static bool bwd_uses_tc(const ptj_attn_shape* shape, int dtype) {
   const void* none[1] = {nullptr};
-  return dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, none, 0);
+  return dtype == PTJ_BF16 && attn_tc_supported(*shape, none, 0);
 }
 
 extern "C" size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int dtype) {
@@ -83,7 +74,7 @@ extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const AttnDropout dr = make_dropout(p, train, seed, stream_id);
   const void* ptrs[8] = {d_o, q, k, v, o, dq, dk, dv};
-  if (dtype == PTJ_BF16 && !force_simt() && attn_tc_supported(*shape, ptrs, 8) && attn_tc_supported(*dshape, ptrs, 0))
+  if (dtype == PTJ_BF16 && attn_tc_supported(*shape, ptrs, 8) && attn_tc_supported(*dshape, ptrs, 0))
     return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, keep_bits, workspace,
                        workspace_bytes, st);
   return attn_bwd_simt(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, dtype, st);

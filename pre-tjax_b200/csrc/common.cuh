@@ -27,15 +27,8 @@ extern void count_launch(int n);
 // memory. The call (1) lets the NEXT kernel's blocks start their own set-up once all blocks of this one have reached
 // this point, and (2) waits until every earlier kernel of the stream has completed and its writes are visible.
 // Kernels that allocate tensor memory call it only after their allocation, so a dependent block can never hold
-// tensor memory that a block of an earlier, still running kernel is waiting for. PTJ_PDL=0 in the environment turns
-// the launch attribute off (plain stream order; the device-side call is then a no-op).
-inline bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PTJ_PDL");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  return on;
-}
+// tensor memory that a block of an earlier, still running kernel is waiting for.
+constexpr bool pdl_enabled() { return true; }
 
 __device__ __forceinline__ void grid_dep_sync() {
   asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");

@@ -8,7 +8,7 @@
 // any transposed copy. Work items = output tiles x K splits, walked by a static persistent schedule.
 //
 // fp32 inputs: plain shared-memory tiled FMA kernel (exact fp32, any shape) for the fp32 parity path.
-#include <cstdlib>
+#include <atomic>
 
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
@@ -22,10 +22,7 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-#ifndef PTJ_GEMM_EPI_WARPS
-#define PTJ_GEMM_EPI_WARPS 8
-#endif
-constexpr int kEpilogueWarps = PTJ_GEMM_EPI_WARPS;     // a multiple of 4: warp w may only read tensor-memory lanes 32*(w%4)..
+constexpr int kEpilogueWarps = 8;     // a multiple of 4: warp w may only read tensor-memory lanes 32*(w%4)..
 constexpr int kWarpsPerQuarter = kEpilogueWarps / 4;   // these warps share a lane quarter and take its 32-column chunks in turn
 constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, the rest: epilogue
 constexpr int kSmemLimit = 227 * 1024;
@@ -57,7 +54,6 @@ struct GemmParams {
   int out_bf16;
   int tma_store;  // outputs leave through tensor-map tile stores (bf16 output, 16-byte aligned rows, K not split)
   int tma_side;   // ... and the epilogue's side input arrives through tile loads, one block ahead
-  int debug;  // timing experiments only (results are garbage), bits: 1 = no TMA copies, 2 = no MMAs, 4 = no epilogue
   unsigned int* fault;
 };
 
@@ -246,11 +242,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctx, 0x0101u)) { ok = false; break; }
-          if (p.debug & 1) {
-            mbar_arrive(&full[stage]);
-            if (++stage == nst) { stage = 0; phase ^= 1u; }
-            continue;
-          }
           mbar_expect_tx(&full[stage], Cfg::kStageBytes);
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
@@ -302,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                             : smem_desc_sw128(sa + k4 * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? smem_desc_sw128(sb + k4 * 32, 16, 1024)
                                             : smem_desc_sw128(sb + k4 * 2048, 8192, 1024);
-            if (!(p.debug & 2)) mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+            mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           mma_commit(&empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == nst) { stage = 0; phase ^= 1u; }
@@ -323,7 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
-      const bool bias_staged = (p.ep.tune & 1) && p.ep.bias != nullptr && p.split_k == 1;
+      const bool bias_staged = p.ep.bias != nullptr && p.split_k == 1;
       if (bias_staged) {
         // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
         __syncwarp();
@@ -348,7 +339,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * Cfg::kAccStride);
 #pragma unroll 1
-      for (int chunk = 0; chunk < ((p.debug & 4) ? 0 : kChunks); ++chunk) {
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
         const int col = (sub + chunk * kWarpsPerQuarter) * 32;  // first column of this chunk within the tile
         if (col >= BN) break;
         uint32_t r[32];
@@ -575,7 +566,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
-      const bool bias_staged = (p.ep.tune & 1) && p.ep.bias != nullptr && p.split_k == 1;
+      const bool bias_staged = p.ep.bias != nullptr && p.split_k == 1;
       if (bias_staged) {
         // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
         __syncwarp();
@@ -732,16 +723,32 @@ gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64
   for (int i = 0; i < 4; ++i) epilogue_row_segment<TOut, 8>(ep, m0 + ty * 4 + i, n0 + tx * 8, acc[i]);
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is needed once per kernel instantiation and device, not per launch.
+template <typename Kern>
+bool ensure_max_smem(Kern kern, std::atomic<uint64_t>& done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  const uint64_t bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  done.fetch_or(bit, std::memory_order_release);
+  return true;
+}
+
 template <int BN, bool AK, bool BK_, bool SIDE>
 int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   // per epilogue warp: the store strip, plus a landing buffer when side inputs arrive through tile loads
   const int smem_bytes = Cfg::smem_bytes(SIDE ? 2 * kEpiBlockBytes : kStripBytes);
   auto kern = gemm_tc_kernel<BN, AK, BK_, SIDE>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return PTJ_ERR_LAUNCH;
-  }
+  static std::atomic<uint64_t> attr_done{0};
+  if (!ensure_max_smem(kern, attr_done)) return PTJ_ERR_LAUNCH;
   const int total = p.num_m * p.num_n * p.split_k;
   const int grid = total < kNumSMs ? total : kNumSMs;
   launch_k(kern, grid, kGemmThreads, smem_bytes, st, ta, tb, sm, p);
@@ -776,10 +783,8 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps
   using Cfg = PairCfg<BN>;
   const int smem_bytes = Cfg::smem_bytes(SIDE ? 2 * kEpiBlockBytes : kStripBytes);
   auto kern = gemm_tc_pair_kernel<BN, AK, BK_, SIDE>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return PTJ_ERR_LAUNCH;
-  }
+  static std::atomic<uint64_t> attr_done{0};
+  if (!ensure_max_smem(kern, attr_done)) return PTJ_ERR_LAUNCH;
   const int total = p.num_m * p.num_n * p.split_k;
   const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
   cudaLaunchConfig_t cfg = {};
@@ -806,14 +811,9 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps
 
 // Which kernel: the CTA-pair kernel halves the shared-memory traffic per FLOP and wins wherever the main loop is
 // long (K >= 2048: weight gradients, the second FFN matrix) or the output is huge (LM head); its 256 x 256 tiles
-// quantise worse on the small N = 768 products, which stay on the single-CTA kernel. PTJ_GEMM_PAIR=0 / 1 forces it.
+// quantise worse on the small N = 768 products, which stay on the single-CTA kernel.
 bool use_pair_kernel(int64_t M, int64_t N, int64_t K) {
-  static const int forced = [] {
-    const char* e = std::getenv("PTJ_GEMM_PAIR");
-    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
-  }();
   if (M < 256 || N < 256) return false;
-  if (forced >= 0) return forced == 1;
   return K >= 2048 || N >= 8192;
 }
 
@@ -850,10 +850,6 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   ep.bias_vec_ok = bias != nullptr && aligned16(bias);
   ep.vec_ok = aligned16(c) && (ldc * osz) % 16 == 0 && (aux == nullptr || aligned16(aux)) &&
               (aux_out == nullptr || aligned16(aux_out));
-  {
-    const char* e = getenv("PTJ_GEMM_TUNE");
-    ep.tune = e != nullptr ? atoi(e) : 27;
-  }
   if (dropout != nullptr) {
     if (!(dropout->p >= 0.f && dropout->p <= 1.f)) return PTJ_ERR_BAD_SHAPE;
     ep.drop_thr = dropout_threshold16(dropout->p);
@@ -901,10 +897,9 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   p.out_bf16 = out_dtype == PTJ_BF16;
   p.fault = tc::fault_word();
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
-  if (const char* e = std::getenv("PTJ_GEMM_DEBUG")) p.debug = std::atoi(e);
 
   StoreMaps smaps{};
-  if ((ep.tune & 8) && p.out_bf16 && ep.vec_ok && split_k == 1) {
+  if (p.out_bf16 && ep.vec_ok && split_k == 1) {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
     const uint64_t str[1] = {static_cast<uint64_t>(ldc) * 2};
     const uint32_t box[2] = {32, 32};
@@ -912,7 +907,7 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
     if (epilogue == PTJ_EPI_GELU && aux_out != nullptr && !make_tmap_bf16_sw64(&smaps.x, aux_out, 2, dims, str, box))
       return PTJ_ERR_LAUNCH;
     p.tma_store = 1;
-    if ((ep.tune & 16) && a_kmajor && (epilogue == PTJ_EPI_GELU_BWD || epilogue == PTJ_EPI_DROPOUT_RESID)) {
+    if (a_kmajor && (epilogue == PTJ_EPI_GELU_BWD || epilogue == PTJ_EPI_DROPOUT_RESID)) {
       if (!make_tmap_bf16_sw64(&smaps.s, aux, 2, dims, str, box)) return PTJ_ERR_LAUNCH;
       p.tma_side = 1;
     }
@@ -960,10 +955,6 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   double best = waves_cost(256, 1.0);
   if (waves_cost(192, 1.08) < best) { bn = 192; best = waves_cost(192, 1.08); }
   if (waves_cost(128, 1.35) < best) { bn = 128; }
-  if (const char* e = std::getenv("PTJ_GEMM_BN")) {  // tuning aid
-    const int v = std::atoi(e);
-    if (v == 128 || v == 192 || v == 256) bn = v;
-  }
   p.num_n = static_cast<int>(ceil_div(N, bn));
   if (static_cast<int64_t>(p.num_m) * p.num_n * split_k > 0x7fffffffLL) return PTJ_ERR_BAD_SHAPE;
 

@@ -21,9 +21,6 @@ struct EpilogueParams {
   int train;
   uint64_t seed;
   uint32_t stream_id;
-  int tune;              // bit 0 = bias staged in shared memory per tile, bit 1 = two-wide GELU math, bit 3 = bf16
-                         // outputs leave through tensor-map tile stores, bit 4 = side inputs arrive through tile loads one block ahead
-                         // (PTJ_GEMM_TUNE overrides the default)
 };
 
 template <typename TOut, int CNT>
@@ -92,17 +89,12 @@ __device__ __forceinline__ bool epilogue_pre(const EpilogueParams& ep, int64_t m
   }
   if (ep.mode == PTJ_EPI_GELU && sizeof(TOut) == 2) {
     // the activation sees the pre-activation as stored (rounded to the output type), like a separate GELU kernel would
-    if (ep.tune & 2) {
 #pragma unroll
-      for (int j = 0; j < CNT; j += 2) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[j], acc[j + 1]);
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
-        acc[j] = __uint_as_float(w << 16);
-        acc[j + 1] = __uint_as_float(w & 0xffff0000u);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < CNT; ++j) acc[j] = __bfloat162float(__float2bfloat16_rn(acc[j]));
+    for (int j = 0; j < CNT; j += 2) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[j], acc[j + 1]);
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+      acc[j] = __uint_as_float(w << 16);
+      acc[j + 1] = __uint_as_float(w & 0xffff0000u);
     }
   }
   return true;
@@ -121,7 +113,7 @@ __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t 
                                               const float (&a)[CNT]) {
   constexpr bool kFast = sizeof(TOut) == 2;  // bf16 output: hardware tanh is exact enough after rounding
   if (ep.mode == PTJ_EPI_GELU) {
-    if (kFast && (ep.tune & 2)) {
+    if (kFast) {
 #pragma unroll
       for (int j = 0; j < CNT; j += 2) gelu_tanh_x2(acc[j], acc[j + 1]);
     } else {
@@ -129,7 +121,7 @@ __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t 
       for (int j = 0; j < CNT; ++j) acc[j] = gelu_tanh<kFast>(acc[j]);
     }
   } else if (ep.mode == PTJ_EPI_GELU_BWD) {
-    if (kFast && (ep.tune & 2)) {
+    if (kFast) {
 #pragma unroll
       for (int j = 0; j < CNT; j += 2) gelu_tanh_grad_mul_x2(acc[j], acc[j + 1], a[j], a[j + 1]);
     } else {

@@ -164,11 +164,14 @@ log_softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
   }
 }
 
-__global__ void count_valid_kernel(const int32_t* __restrict__ labels, int64_t rows, float* __restrict__ n_valid) {
+// Rows that contribute: the same predicate the cross-entropy kernel applies (a label that is not padding and lies
+// inside the vocabulary), so that the divisor always matches the rows that were summed.
+__global__ void count_valid_kernel(const int32_t* __restrict__ labels, int64_t rows, int64_t cols,
+                                   float* __restrict__ n_valid) {
   grid_dep_sync();
   __shared__ float red[33];
   float c = 0.f;
-  for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) c += labels[i] != 0 ? 1.f : 0.f;
+  for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) c += (labels[i] > 0 && labels[i] < cols) ? 1.f : 0.f;
   const float t = block_sum(c, red);  // exact: counts stay far below 2^24 per thread and in total
   if (threadIdx.x == 0) *n_valid = t;
 }
@@ -331,7 +334,7 @@ extern "C" int ptj_cross_entropy(const int32_t* labels, const void* logits, void
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (count_in_kernel) {
-    launch_k(count_valid_kernel, 1, 1024, 0, st, labels, rows, n_valid);
+    launch_k(count_valid_kernel, 1, 1024, 0, st, labels, rows, cols, n_valid);
     PTJ_CHECK_LAUNCH();
   }
   if (dtype == PTJ_F32) {

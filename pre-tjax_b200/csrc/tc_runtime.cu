@@ -1,7 +1,9 @@
 // Host-side runtime shared by the tensor-core kernels: the device fault word, the driver entry point that encodes
 // TMA tensor maps, library-level bookkeeping entry points.
 #include <atomic>
+#include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -49,10 +51,59 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// Encoded tensor maps are cached per host thread, keyed by everything that goes into the encoding (base address,
+// extents, strides, box, swizzle): a training step issues the same few hundred (tensor, box) combinations every
+// iteration, and cuTensorMapEncodeTiled costs more than the rest of a launch's host work. A map is a pure function
+// of its key (it holds no reference to the allocation's contents), so a stale entry can only be hit by a request that
+// would encode the identical map again. Direct-mapped, 2048 entries per thread.
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t dims[4];
+  uint64_t strides[3];
+  uint32_t box[4];
+  uint32_t rank_swizzle;
+  uint32_t pad;  // keeps the struct free of padding bytes, so memcmp compares only fields
+  bool operator==(const TmapKey& o) const { return std::memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+static_assert(sizeof(TmapKey) == 8 + 32 + 24 + 16 + 8, "TmapKey must have no padding");
+struct TmapEntry {
+  TmapKey key;
+  bool valid;
+  CUtensorMap map;
+};
+constexpr size_t kTmapCacheEntries = 2048;
+inline uint64_t mix64(uint64_t h, uint64_t v) {
+  h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+  return h;
+}
+}  // namespace
+
 static bool make_tmap_bf16_sw(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn enc = get_encode_tiled();
-  if (enc == nullptr) return false;
+  if (enc == nullptr || rank < 1 || rank > 4) return false;
+  TmapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.rank_swizzle = static_cast<uint32_t>(rank) | (static_cast<uint32_t>(swizzle) << 8);
+  uint64_t h = mix64(reinterpret_cast<uint64_t>(base), key.rank_swizzle);
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    h = mix64(h, dims[i] * 0x100000001B3ull + box[i]);
+    if (i + 1 < rank) {
+      key.strides[i] = strides_bytes[i];
+      h = mix64(h, strides_bytes[i]);
+    }
+  }
+  thread_local std::vector<TmapEntry> cache;
+  if (cache.empty()) cache.resize(kTmapCacheEntries);
+  TmapEntry& slot = cache[(h ^ (h >> 29)) % kTmapCacheEntries];
+  if (slot.valid && slot.key == key) {
+    *out = slot.map;
+    return true;
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bx[5], es[5];
@@ -65,7 +116,11 @@ static bool make_tmap_bf16_sw(CUtensorMap* out, const void* base, int rank, cons
   const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
                          gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  slot.key = key;
+  slot.map = *out;
+  slot.valid = true;
+  return true;
 }
 
 bool make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,

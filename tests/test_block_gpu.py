@@ -1,0 +1,123 @@
+"""Full-width transformer blocks and a long bf16 training run against the CPU oracle.
+
+* BASELINE configuration 3 as one composition: a single GPT-2-small block on [8 x 1024, 768] tokens (12 heads x 64,
+  FFN 3072), bf16, dropout 0.1 at all four sites with the oracle fed the same Philox masks, forward + backward
+  through the train-step engine; loss and every weight gradient against the fp32 oracle on bf16-rounded weights.
+  These shapes run the two-CTA GEMM kernel with every epilogue it has (dropout + residual with side-tile loads,
+  GELU', split-K weight gradients) and the tensor-core attention kernels with dropout.
+* The same at GPT-2-medium width (d_model 1024, 16 heads, FFN 4096), two layers, two sequences.
+* 200 optimizer steps of the bf16 trainer (bf16 shadow weights, tcgen05 GEMMs, tensor-core attention, clip, fused
+  AdamW with shadow refresh) within 1 % of the oracle's loss curve.
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import pkg, rel_err
+from oracle import gpt2_oracle as orc
+from oracle import philox
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2
+
+
+def flat(tree):
+    return [t for grp in tree for t in grp]
+
+
+def round_matrices(prm):
+    """Weights as the bf16 path sees them: matrices rounded to bf16, vectors (LayerNorm, biases) kept in float32."""
+    return [[t.bfloat16().float() if t.dim() > 1 else t for t in grp] for grp in prm]
+
+
+def mask_fn(seeds, p):
+    def fn(site, shape):
+        if site == "embed":
+            seed = seeds[0]
+        else:
+            l, kind = site.split(".")
+            seed = seeds[1 + 3 * int(l[1:]) + {"attn": 0, "res1": 1, "res2": 2}[kind]]
+        return torch.from_numpy(philox.keep_mask(seed, 0, math.prod(shape), p)).view(shape)
+    return fn
+
+
+def run_block(V, D, L, H, F, S, B, p, seed):
+    ops, gpt2 = pkg("operators"), pkg("gpt2")
+    ops.DROPOUT_RATE = p
+    try:
+        prm = orc.init_params(V, D, L, H, F, S, seed=seed)
+        # LayerNorm scales / shifts and biases away from their 1 / 0 start so their gradients paths carry signal
+        g = torch.Generator().manual_seed(seed + 1)
+        prm = [[t if t.dim() > 1 else t + 0.1 * torch.randn(t.shape, generator=g) for t in grp] for grp in prm]
+        y = torch.randint(1, V, (B, S + 1), generator=torch.Generator().manual_seed(seed + 2), dtype=torch.int32)
+        y[0, S // 2] = 0  # one padding label: the row is excluded from loss, accuracy and the mean's denominator
+        seeds = [9000 + 31 * i for i in range(1 + 3 * L)]
+        gp = [[(t.bfloat16() if t.dim() > 1 else t).cuda() for t in grp] for grp in prm]
+        grads, (loss, acc, frac) = gpt2.t_loss_bkwd3_t(gp, y.cuda(), None, None, True, seeds)
+        torch.cuda.synchronize()
+        assert ops.last_kernel_fault() == 0
+        ref, (rloss, racc, rfrac) = orc.loss_and_grads(round_matrices(prm), y, p=p, train=True,
+                                                       mask_fn=mask_fn(seeds, p) if p > 0 else None)
+        assert rel_err(loss, rloss) < BF16_TOL
+        assert abs(float(frac) - float(rfrac)) < 1e-6
+        names = [n for n, _ in gpt2.GPT2Config(V, D, L, H, F, S, p).param_shapes()]
+        for n, a, b in zip(names, flat(grads), flat(ref)):
+            assert rel_err(a, b) < BF16_TOL, f"gradient of {n}: {rel_err(a, b):.3e}"
+    finally:
+        ops.DROPOUT_RATE = 0.1
+
+
+def test_config3_gpt2_small_block_bf16_dropout():
+    run_block(V=1024, D=768, L=1, H=12, F=3072, S=1024, B=8, p=0.1, seed=40)
+
+
+def test_gpt2_medium_width_blocks_bf16_dropout():
+    run_block(V=1024, D=1024, L=2, H=16, F=4096, S=1024, B=2, p=0.1, seed=50)
+
+
+def markov_batches(n, V, B, S, seed):
+    """Token streams with learnable structure: with probability 0.7 the next id is a fixed function of the current
+    one, otherwise uniform. The loss falls from ln V towards the entropy of that process instead of collapsing to
+    zero, so a relative band stays meaningful for all 200 steps."""
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        y = torch.empty(B, S + 1, dtype=torch.int64)
+        y[:, 0] = torch.randint(1, V, (B,), generator=g)
+        noise = torch.randint(1, V, (B, S + 1), generator=g)
+        keep = torch.rand(B, S + 1, generator=g) < 0.7
+        for t in range(S):
+            nxt = (y[:, t] * 7 + 3) % (V - 1) + 1
+            y[:, t + 1] = torch.where(keep[:, t + 1], nxt, noise[:, t + 1])
+        out.append(y.to(torch.int32))
+    return out
+
+
+def test_loss_curve_200_steps_bf16_trainer():
+    """The benchmarked path (bf16 shadow weights, tensor-core GEMMs and attention, clip, fused AdamW) for 200 steps on
+    200 different batches: every loss within 1 % of the oracle, which keeps float32 master weights and, like the
+    trainer, evaluates the model on their bf16 rounding (matrices only)."""
+    gpt2, tr = pkg("gpt2"), pkg("trainer")
+    V, D, L, H, F, S, B = 1024, 128, 2, 2, 256, 128, 4
+    cfg = gpt2.GPT2Config(vocab=V, dim=D, layers=L, heads=H, ffn=F, seq=S, dropout=0.0)
+    prm = orc.init_params(V, D, L, H, F, S, seed=21)
+    batches = markov_batches(200, V, B, S, seed=22)
+    lr, betas, eps, wd, clip = 1e-3, (0.9, 0.95), 1e-8, 0.1, 1.0
+    tc = tr.TrainConfig(lr=lr, betas=betas, eps=eps, weight_decay=wd, clip=clip, compute_dtype=torch.bfloat16)
+    t = tr.Trainer(cfg, tc, params=prm, device="cuda")
+    gpu_losses = [float(x) for x in torch.stack([t.step(y)[0] for y in batches]).cpu()]
+    assert pkg("operators").last_kernel_fault() == 0
+
+    mom = [[[torch.zeros_like(x) for x in grp] for grp in prm] for _ in range(2)]
+    mask = orc.decay_mask(prm)
+    ref_losses, master = [], prm
+    for i, y in enumerate(batches):
+        grads, (loss, _, _) = orc.loss_and_grads(round_matrices(master), y)
+        s = orc.clip_scale(orc.grads_l2norm(grads), clip)
+        master, mom = orc.adam_w(master, [[x * s for x in grp] for grp in grads], lr, betas, eps, mom, i, wd, mask)
+        ref_losses.append(float(loss))
+    assert ref_losses[-1] < 0.5 * ref_losses[0], "the toy problem is expected to train"
+    worst = max(abs(a - b) / b for a, b in zip(gpu_losses, ref_losses))
+    assert worst < 1e-2, f"bf16 loss curve deviates by {worst:.3%}"

@@ -38,7 +38,7 @@ def _worker(rank, world, port, ret):
     try:
         ptj = pkg()
         cfg = _cfg()
-        t = ptj.Trainer(cfg, ptj.TrainConfig(seed=5), device=f"cuda:{rank}", world=world, rank=rank)
+        t = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=5), device=f"cuda:{rank}", world=world, rank=rank)
         losses = []
         for ys in _batches(cfg, 3, world):
             losses.append(float(t.step(ys[rank])[0]))
@@ -68,7 +68,7 @@ def test_two_ranks_agree_and_match_the_averaged_single_gpu_step():
     ptj = pkg()
     cfg = _cfg()
     tr = pkg("trainer")
-    ref = ptj.Trainer(cfg, ptj.TrainConfig(seed=5), device="cuda:0")
+    ref = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=5), device="cuda:0")
     ref.world = world
     for step, ys in enumerate(_batches(cfg, 3, world)):
         acc = torch.zeros_like(ref.g)

@@ -111,7 +111,7 @@ def test_train_step_full_size_is_reproducible_and_learns():
     y = torch.randint(1, cfg.vocab, (8, cfg.seq + 1), generator=g, dtype=torch.int32)
     losses = []
     for _ in range(2):
-        t = ptj.Trainer(cfg, ptj.TrainConfig(seed=3), device="cuda")
+        t = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=3), device="cuda")
         run = [float(t.step(y)[0]) for _ in range(4)]
         losses.append(run)
         final = t.p.clone()
@@ -135,7 +135,7 @@ def test_full_size_model_loss_against_cpu_oracle():
     prm = orc.init_params(cfg.vocab, cfg.dim, cfg.layers, cfg.heads, cfg.ffn, cfg.seq, seed=1)
     prm_r = [[t.bfloat16().float() if t.dim() > 1 else t for t in grp] for grp in prm]
     y = torch.randint(1, cfg.vocab, (1, cfg.seq + 1), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
-    t = ptj.Trainer(cfg, ptj.TrainConfig(seed=0), params=prm, device="cuda")
+    t = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=0), params=prm, device="cuda")
     stats = t.step(y)
     with torch.no_grad():
         logits = orc.forward_gpt2(prm_r, y[:, :-1])

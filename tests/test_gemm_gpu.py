@@ -121,3 +121,78 @@ def test_rejects_bad_arguments(ops):
         ops.gemm(a[:, 1:], a, M=64, N=64, K=56, lda=64)  # operand pointer not 16-byte aligned
     with pytest.raises(RuntimeError, match="shape"):
         ops.gemm(a, a, M=64, N=64, K=64, lda=8)  # leading dimension smaller than K
+
+
+# ---- CTA-pair kernel (M, N >= 256 and K >= 2048 or N >= 8192) ---------------------------------------------------------
+# The shapes below all route to the two-CTA kernel (256 x 256 tiles, tcgen05.mma.cta_group::2): exact multiples, a
+# ragged M and N edge, and the long-K weight-gradient form.
+PAIR_SHAPES = [(512, 768, 3072), (296, 520, 2048), (256, 256, 2048), (1024, 8200, 128)]
+
+
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
+def test_pair_kernel_layouts_and_edges(ops, a_k, b_k, M, N, K):
+    A, B = rnd(M, K, seed=11), rnd(N, K, seed=12, scale=0.25)
+    ref = A.double() @ B.double().t()
+    a_dev = (A if a_k else A.t().contiguous()).cuda()
+    b_dev = (B if b_k else B.t().contiguous()).cuda()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        guard = torch.full((M + 1, N), 5.0, device="cuda", dtype=out_dtype)  # one row beyond the ragged M edge
+        c = ops.gemm(a_dev, b_dev, a_kmajor=a_k, b_kmajor=b_k, M=M, N=N, K=K, out=guard[:M])
+        no_fault(ops)
+        assert rel_err(c.float(), ref) < (TOL if out_dtype == torch.bfloat16 else 1e-3)
+        assert float((guard[M] - 5.0).abs().max()) == 0.0, "rows beyond M must not be written"
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 768, 3072), (296, 520, 2048)])
+def test_pair_kernel_epilogues(ops, M, N, K):
+    """Every epilogue of the two-CTA kernel, including the side input that arrives through tile loads (full blocks)
+    and through plain loads (the ragged shape), against float64."""
+    lib = pkg("_lib")
+    A, W = rnd(M, K, seed=21), rnd(N, K, seed=22, scale=0.05)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(23))
+    acc = A.double() @ W.double().t() + bias.double()
+    a, w, b = A.cuda(), W.cuda(), bias.cuda()
+    assert rel_err(ops.gemm(a, w, bias=b).float(), acc) < TOL
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    act = ops.gemm(a, w, bias=b, epilogue=lib.EPI_GELU, aux_out=pre)
+    assert rel_err(pre.float(), acc) < TOL
+    assert rel_err(act.float(), orc.gelu(pre.float().cpu().double())) < TOL
+    for b_k in (True, False):  # forward form (x W^T) and input-gradient form (dy W) of the side-input epilogues
+        w_dev = w if b_k else W.t().contiguous().cuda()
+        pre_in = rnd(M, N, seed=24)
+        out = ops.gemm(a, w_dev, b_kmajor=b_k, M=M, N=N, K=K, epilogue=lib.EPI_GELU_BWD, aux=pre_in.cuda())
+        assert rel_err(out.float(), orc.gelu_bwd(A.double() @ W.double().t(), pre_in.double())) < TOL
+        p, seed = 0.3, 777
+        resid = rnd(M, N, seed=25)
+        mask = torch.from_numpy(philox.keep_mask(seed, 0, M * N, p)).view(M, N).double()
+        out = ops.gemm(a, w_dev, b_kmajor=b_k, M=M, N=N, K=K, bias=b, epilogue=lib.EPI_DROPOUT_RESID, aux=resid.cuda(),
+                       dropout_args=(p, True, seed, 0))
+        assert rel_err(out.float(), resid.double() + acc * mask) < TOL
+        out = ops.gemm(a, w_dev, b_kmajor=b_k, M=M, N=N, K=K, bias=b, epilogue=lib.EPI_DROPOUT_RESID, aux=resid.cuda(),
+                       dropout_args=(p, False, seed, 0))
+        assert rel_err(out.float(), resid.double() + acc * (1 - p)) < TOL
+    no_fault(ops)
+
+
+@pytest.mark.parametrize("split", [1, 2, 3])
+@pytest.mark.parametrize("N_out,N_in", [(768, 768), (520, 296)])
+def test_pair_kernel_weight_gradient_split_k_accumulate(ops, split, N_out, N_in):
+    """dW = dY^T X over 8192 tokens (both operands MN-major) on the two-CTA kernel: plain, split-K with the fixed-order
+    reduction, and accumulation onto existing contents (the tied embedding gradient)."""
+    lib = pkg("_lib")
+    T = 8192
+    dY, X = rnd(T, N_out, seed=31, scale=0.1), rnd(T, N_in, seed=32)
+    ref = dY.double().t() @ X.double()
+    kw = dict(a_kmajor=False, b_kmajor=False, M=N_out, N=N_in, K=T, split_k=split)
+    out = torch.empty(N_out, N_in, device="cuda", dtype=torch.float32)
+    ops.gemm(dY.cuda(), X.cuda(), out=out, **kw)
+    no_fault(ops)
+    assert rel_err(out, ref) < 1e-3
+    again = torch.empty_like(out)
+    ops.gemm(dY.cuda(), X.cuda(), out=again, **kw)
+    assert torch.equal(out, again)
+    base = torch.full_like(out, -0.5)
+    ops.gemm(dY.cuda(), X.cuda(), out=base, epilogue=lib.EPI_ACCUM, **kw)
+    assert rel_err(base, ref - 0.5) < 1e-3
+    no_fault(ops)

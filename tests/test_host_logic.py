@@ -207,3 +207,44 @@ def test_checkpoint_wire_format_round_trip(tmp_path):
     with pytest.raises(ValueError):
         ck.load_checkpoint(str(tmp_path / "short.pkl"))
     assert not list(tmp_path.glob("**/*.tmp.*"))
+
+
+def test_checkpoint_step_index_follows_the_reference(tmp_path):
+    """The reference counts a micro-step BEFORE it pickles (train_gpt2_triton.py:408-419): after N steps the file holds
+    i = N, is named checkpoint_N.pkl, and the run that resumes it calls adam_w_in_place(..., i) next, i.e. AdamW step
+    count N + 1 (:321). A trainer that loads such a file must stand at t = N completed steps, and a trainer that has
+    completed N steps must write i = N."""
+    import pickle
+    from types import SimpleNamespace
+    ck, gpt2, tr = pkg("checkpoint"), pkg("gpt2"), pkg("trainer")
+    cfg = gpt2.GPT2Config(vocab=40, dim=16, layers=2, heads=2, ffn=32, seq=8, dropout=0.0)
+    prm = orc.init_params(40, 16, 2, 2, 32, 8, seed=3)
+    zeros = lambda: [[torch.zeros_like(t) for t in grp] for grp in prm]
+    N = 5
+    # the reference's loop, reduced to its counters
+    i, rows, moments = 0, 0, [zeros(), zeros()]
+    adamw_counts = []
+    for _ in range(N):
+        adamw_counts.append(i + 1)  # adam_w_in_place(params, grads, lr, betas, eps, moments, i, ...): t = i + 1
+        i, rows = i + 1, rows + 4
+    ref_file = tmp_path / f"checkpoint_{i}.pkl"
+    with open(ref_file, "wb") as f:
+        pickle.dump((i, rows, prm, moments), f)
+    assert adamw_counts[-1] == N and i == N
+
+    lay = tr.FlatLayout.build(cfg)
+    flat = lambda: torch.zeros(lay.total)
+    stand_in = SimpleNamespace(cfg=cfg, layout=lay, p=flat(), m=flat(), v=flat(), t=0, device=torch.device("cpu"),
+                               _refresh_shadow=lambda: None)
+    assert ck.load_trainer_state(stand_in, str(ref_file)) == (N, rows)
+    assert stand_in.t == N  # Trainer.apply_update increments before use: the next AdamW step count is N + 1
+    for (name, _), t in zip(cfg.param_shapes(), [t for grp in prm for t in grp]):
+        assert torch.equal(lay.view(stand_in.p, name), t)
+    # and the other direction: N completed steps are written as i = N under the reference's file name
+    out = ck.checkpoint_name(str(tmp_path / "run"), stand_in)
+    assert out.endswith(f"checkpoint_{N}.pkl")
+    ck.save_trainer(out, stand_in, ds_train_rows_read=rows)
+    with open(out, "rb") as f:
+        i2, rows2, p2, _ = pickle.load(f)
+    assert (i2, rows2) == (N, rows)
+    assert all(torch.equal(a, b) for ga, gb in zip(p2, prm) for a, b in zip(ga, gb))

@@ -186,7 +186,7 @@ def test_trainer_single_step_matches_oracle_update():
     cfg = gpt2.GPT2Config(vocab=80, dim=32, layers=1, heads=2, ffn=64, seq=16, dropout=0.0)
     prm = orc.init_params(80, 32, 1, 2, 64, 16, seed=9)
     y = torch.randint(1, 80, (2, 17), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
-    tc = tr.TrainConfig(lr=1e-3, eps=1e-3, weight_decay=0.1, clip=0.5, compute_dtype=torch.float32)
+    tc = tr.TrainConfig(lr=1e-3, betas=(0.9, 0.95), eps=1e-3, weight_decay=0.1, clip=0.5, compute_dtype=torch.float32)
     t = tr.Trainer(cfg, tc, params=prm, device="cuda")
     t.step(y)
     grads, _ = orc.loss_and_grads(prm, y)

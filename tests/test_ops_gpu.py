@@ -172,6 +172,22 @@ def test_cross_entropy_shapes(ops, dtype, tol, rows, cols):
     check(stats[0].reshape(()), ol.reshape(()), tol)
 
 
+def test_cross_entropy_label_outside_vocabulary_is_not_counted(ops):
+    """An id beyond the vocabulary (or negative) contributes nothing and must not be counted either: the divisor is
+    the number of rows that were actually summed."""
+    rows, cols = 12, 40
+    logits = rnd(rows, cols, seed=1, scale=2.0)
+    labels = torch.randint(1, cols, (rows,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    labels[3], labels[7], labels[9] = cols, -5, 0
+    loss, n, dl = ops.t_avg_cross_entropy_loss_bkwd3_t(gpu(labels), gpu(logits))
+    clean = labels.clone()
+    clean[3] = clean[7] = 0  # the oracle's only notion of "no contribution" is the padding id
+    ol, on, odl = orc.cross_entropy_fwd_bwd(clean, logits)
+    assert int(n) == int(on) == rows - 3
+    check(loss.reshape(()), ol.reshape(()), F32_TOL)
+    check(dl, odl, F32_TOL)
+
+
 def test_cross_entropy_all_padding(ops):
     logits = gpu(rnd(4, 16, seed=1))
     labels = gpu(torch.zeros(4, dtype=torch.int32))
