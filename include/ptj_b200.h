@@ -213,6 +213,13 @@ int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const voi
  *   dtype PTJ_BF16 with d_head == 64 and seq % 128 == 0 runs the tcgen05 kernels; everything else runs the
  *   exact-fp32 SIMT kernels.
  * Backward recomputes the probabilities; it is deterministic (no atomics).
+ *
+ * row_kstart (optional, int32[batch, seq]): the first key each query row may attend to, so that row i attends keys
+ * [row_kstart[b,i], i]. This is how the masks of the reference's collator (causal x block-diagonal over packed
+ * documents x padding, tokenized_dataset.py:110-131, applied by its kernels at model_triton.py:678-681, 917-920) reach
+ * the kernels without a dense [B,N,N] tensor: a row of a packed document starts at its document's first token, a
+ * padding row gets row_kstart > i and attends nothing (zero output row, row_max 0, row_sum 1, zero gradients).
+ * NULL = plain causal attention. Forward and backward of one call must be given the same array.
  */
 typedef struct {
   int64_t batch, heads, seq, d_head;
@@ -229,7 +236,7 @@ int ptj_attn_keep_bits(uint32_t* bits, const ptj_attn_shape* shape, float p, uin
                        int dtype, void* stream);
 int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
                  const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
-                 const uint32_t* keep_bits, int dtype, void* stream);
+                 const uint32_t* keep_bits, const int32_t* row_kstart, int dtype, void* stream);
 /* dq/dk/dv use q/k/v strides of `dshape`; d_o and o use o_strides of `shape`.
  * workspace: ptj_attn_bwd_workspace_bytes(shape, dtype) bytes of device memory, 16-byte aligned, contents
  * irrelevant before and after the call (the tensor-core path keeps each KV tile's share of dQ there in fp32 and sums
@@ -239,8 +246,8 @@ size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int dtype);
 int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                  const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
                  const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
-                 uint64_t seed, uint32_t stream_id, const uint32_t* keep_bits, void* workspace,
-                 size_t workspace_bytes, int dtype, void* stream);
+                 uint64_t seed, uint32_t stream_id, const uint32_t* keep_bits, const int32_t* row_kstart,
+                 void* workspace, size_t workspace_bytes, int dtype, void* stream);
 
 /* ---- optimizer -------------------------------------------------------------------------------------- */
 /* sum of squares of a float vector -> out[0] (deterministic two-stage). Replaces grads_l2norm

@@ -82,12 +82,16 @@ def dropout(x: torch.Tensor, p: float, train: bool, mask: Optional[torch.Tensor]
     return x * mask.to(x.dtype)
 
 
-def causal_attention(q, k, v, p: float = 0.0, train: bool = True, mask: Optional[torch.Tensor] = None):
-    """q,k,v: [..., S, d]. softmax(causal(q k^T / sqrt(d)), fill -1e9) -> dropout on the probabilities -> @ v
-    (model_torch_func.py:70-78). Returns (out, probabilities before dropout)."""
+def causal_attention(q, k, v, p: float = 0.0, train: bool = True, mask: Optional[torch.Tensor] = None,
+                     attn_mask: Optional[torch.Tensor] = None):
+    """q,k,v: [..., S, d]. softmax(masked(q k^T / sqrt(d)), fill -1e9) -> dropout on the probabilities -> @ v
+    (model_torch_func.py:70-78). attn_mask: bool, broadcastable to [..., S, S], True = attend (the collator's
+    causal x block-diagonal x padding mask, tokenized_dataset.py:110-131); None = causal. A row without any True
+    gets -1e9 everywhere and therefore attends all keys uniformly, as in the reference.
+    Returns (out, probabilities before dropout)."""
     S, d = q.shape[-2], q.shape[-1]
     s = q @ k.transpose(-2, -1) / math.sqrt(d)
-    tri = torch.tril(torch.ones(S, S, dtype=torch.bool))
+    tri = torch.tril(torch.ones(S, S, dtype=torch.bool)) if attn_mask is None else attn_mask
     s = torch.where(tri, s, torch.full_like(s, -1e9))
     pr = torch.exp(log_softmax(s))
     return dropout(pr, p, train, mask) @ v, pr
@@ -104,15 +108,18 @@ def causal_attention_stats(q, k):
     return m, torch.exp(s - m.unsqueeze(-1)).sum(dim=-1)
 
 
-def causal_attention_bwd(d_out, q, k, v, p: float = 0.0, train: bool = True, mask: Optional[torch.Tensor] = None):
+def causal_attention_bwd(d_out, q, k, v, p: float = 0.0, train: bool = True, mask: Optional[torch.Tensor] = None,
+                         attn_mask: Optional[torch.Tensor] = None):
     """(dq, dk, dv): model_triton.py:801-811 with :550-577."""
     d = q.shape[-1]
-    _, pr = causal_attention(q, k, v, p, train, mask)
+    _, pr = causal_attention(q, k, v, p, train, mask, attn_mask)
     prd = dropout(pr, p, train, mask)
     dv = prd.transpose(-2, -1) @ d_out
     dprd = d_out @ v.transpose(-2, -1)
     dpr = dropout(dprd, p, train, mask)
     ds = pr * (dpr - (dpr * pr).sum(dim=-1, keepdim=True))
+    if attn_mask is not None:  # the fill value carries no gradient (model_triton.py:568): matters for rows without keys
+        ds = torch.where(attn_mask, ds, torch.zeros_like(ds))
     dq = ds @ k / math.sqrt(d)
     dk = ds.transpose(-2, -1) @ q / math.sqrt(d)
     return dq, dk, dv
@@ -148,10 +155,13 @@ def accuracy(labels: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
 
 
 # ---- the model ---------------------------------------------------------------------------------------------------------
-def forward_gpt2(params, ids: torch.Tensor, p: float = 0.0, train: bool = True, mask_fn: MaskFn = None):
+def forward_gpt2(params, ids: torch.Tensor, p: float = 0.0, train: bool = True, mask_fn: MaskFn = None,
+                 attn_mask: Optional[torch.Tensor] = None):
     """Batched forward pass: [B, S] token ids -> [B, S, V] logits (model_torch_func.py:110-133, batched directly
     instead of through vmap). mask_fn(site, shape) supplies dropout masks; sites are "embed", "l{i}.attn",
-    "l{i}.res1", "l{i}.res2"."""
+    "l{i}.res1", "l{i}.res2". attn_mask: the batch's attention mask [B, S, S] bool (y_mask of the reference,
+    shared by all heads), None = causal."""
+    am = None if attn_mask is None else attn_mask.bool().unsqueeze(1)
     mk = (lambda site, shape: mask_fn(site, shape)) if (mask_fn is not None and train) else (lambda site, shape: None)
     w_emb, b_head = params[0]
     (w_pos,) = params[1]
@@ -165,7 +175,7 @@ def forward_gpt2(params, ids: torch.Tensor, p: float = 0.0, train: bool = True, 
         # per-head projections: q_h = h W[h,0]^T etc. (model_torch_func.py:80-82)
         qkv = torch.einsum("bsd,hced->bhcse", h, w_qkv)  # [B, H, 3, S, dh]
         q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
-        a, _ = causal_attention(q, k, v, p, train, mk(f"l{i}.attn", (q.shape[0], H, q.shape[2], q.shape[2])))
+        a, _ = causal_attention(q, k, v, p, train, mk(f"l{i}.attn", (q.shape[0], H, q.shape[2], q.shape[2])), am)
         a = a.permute(0, 2, 1, 3).reshape(x.shape)  # concatenate heads along the feature axis (:88)
         a = a @ w_o.t()
         x = x + dropout(a, p, train, mk(f"l{i}.res1", x.shape))
@@ -177,11 +187,12 @@ def forward_gpt2(params, ids: torch.Tensor, p: float = 0.0, train: bool = True, 
     return x @ w_emb.t() + b_head  # tied output projection with its own bias (:132)
 
 
-def loss_and_grads(params, y: torch.Tensor, p: float = 0.0, train: bool = True, mask_fn: MaskFn = None):
+def loss_and_grads(params, y: torch.Tensor, p: float = 0.0, train: bool = True, mask_fn: MaskFn = None,
+                   attn_mask: Optional[torch.Tensor] = None):
     """(grads pytree, (loss, accuracy, valid fraction)) for y [B, S+1]: inputs y[:, :-1], labels y[:, 1:]
     (loss_and_optimizer_triton.py:221-235). Gradients come from autograd over the restated forward."""
     leaves = [[t.detach().clone().requires_grad_(True) for t in grp] for grp in params]
-    logits = forward_gpt2(leaves, y[:, :-1], p, train, mask_fn)
+    logits = forward_gpt2(leaves, y[:, :-1], p, train, mask_fn, attn_mask)
     labels = y[:, 1:]
     loss, n_valid = avg_cross_entropy_loss(labels, logits)
     flat = [t for grp in leaves for t in grp]

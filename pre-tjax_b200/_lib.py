@@ -58,10 +58,11 @@ _SIGNATURES = {
                          c_int, c_int, c_int, POINTER(DropoutArgs), c_int, _P, c_size_t, _P]),
     "ptj_attn_keep_bits_bytes": (c_size_t, [POINTER(AttnShape), c_int]),
     "ptj_attn_keep_bits": (c_int, [_P, POINTER(AttnShape), c_float, c_uint64, c_uint32, c_int, _P]),
-    "ptj_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, POINTER(AttnShape), c_float, c_int, c_uint64, c_uint32, _P, c_int, _P]),
+    "ptj_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, POINTER(AttnShape), c_float, c_int, c_uint64, c_uint32, _P, _P, c_int,
+                             _P]),
     "ptj_attn_bwd_workspace_bytes": (c_size_t, [POINTER(AttnShape), c_int]),
     "ptj_attn_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, POINTER(AttnShape), POINTER(AttnShape), c_float,
-                             c_int, c_uint64, c_uint32, _P, _P, c_size_t, c_int, _P]),
+                             c_int, c_uint64, c_uint32, _P, _P, _P, c_size_t, c_int, _P]),
     "ptj_sumsq_scratch_floats": (c_size_t, [c_int64]),
     "ptj_sumsq": (c_int, [_P, _P, _P, c_size_t, c_int64, _P]),
     "ptj_adamw": (c_int, [_P, _P, _P, _P, _P, c_int64, _P, _P, c_int, c_float, c_float, c_float, c_float, c_float,

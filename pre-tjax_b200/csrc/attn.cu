@@ -36,8 +36,7 @@ extern "C" int ptj_attn_keep_bits(uint32_t* bits, const ptj_attn_shape* shape, f
 
 extern "C" int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
                             const ptj_attn_shape* shape, float p, int train, uint64_t seed, uint32_t stream_id,
-                            const uint32_t* keep_bits,
-                            int dtype, void* stream) {
+                            const uint32_t* keep_bits, const int32_t* row_kstart, int dtype, void* stream) {
   if (!shape_ok(shape) || !q || !k || !v || !o || !row_max || !row_sum || !(p >= 0.f && p <= 1.f))
     return PTJ_ERR_BAD_SHAPE;
   if (dtype != PTJ_F32 && dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
@@ -45,8 +44,8 @@ extern "C" int ptj_attn_fwd(const void* q, const void* k, const void* v, void* o
   const AttnDropout dr = make_dropout(p, train, seed, stream_id);
   const void* ptrs[4] = {q, k, v, o};
   if (dtype == PTJ_BF16 && attn_tc_supported(*shape, ptrs, 4))
-    return attn_fwd_tc(q, k, v, o, row_max, row_sum, keep_bits, *shape, dr, st);
-  return attn_fwd_simt(q, k, v, o, row_max, row_sum, *shape, dr, dtype, st);
+    return attn_fwd_tc(q, k, v, o, row_max, row_sum, keep_bits, row_kstart, *shape, dr, st);
+  return attn_fwd_simt(q, k, v, o, row_max, row_sum, row_kstart, *shape, dr, dtype, st);
 }
 
 static bool bwd_uses_tc(const ptj_attn_shape* shape, int dtype) {
@@ -62,8 +61,8 @@ extern "C" size_t ptj_attn_bwd_workspace_bytes(const ptj_attn_shape* shape, int 
 extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                             const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
                             const ptj_attn_shape* shape, const ptj_attn_shape* dshape, float p, int train,
-                            uint64_t seed, uint32_t stream_id, const uint32_t* keep_bits, void* workspace,
-                            size_t workspace_bytes, int dtype, void* stream) {
+                            uint64_t seed, uint32_t stream_id, const uint32_t* keep_bits, const int32_t* row_kstart,
+                            void* workspace, size_t workspace_bytes, int dtype, void* stream) {
   if (!shape_ok(shape) || !shape_ok(dshape) || !d_o || !q || !k || !v || !o || !row_max || !row_sum || !dq || !dk ||
       !dv || !(p >= 0.f && p <= 1.f))
     return PTJ_ERR_BAD_SHAPE;
@@ -75,7 +74,7 @@ extern "C" int ptj_attn_bwd(const void* d_o, const void* q, const void* k, const
   const AttnDropout dr = make_dropout(p, train, seed, stream_id);
   const void* ptrs[8] = {d_o, q, k, v, o, dq, dk, dv};
   if (dtype == PTJ_BF16 && attn_tc_supported(*shape, ptrs, 8) && attn_tc_supported(*dshape, ptrs, 0))
-    return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, keep_bits, workspace,
-                       workspace_bytes, st);
-  return attn_bwd_simt(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, dtype, st);
+    return attn_bwd_tc(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, *shape, *dshape, dr, keep_bits, row_kstart,
+                       workspace, workspace_bytes, st);
+  return attn_bwd_simt(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, row_kstart, *shape, *dshape, dr, dtype, st);
 }

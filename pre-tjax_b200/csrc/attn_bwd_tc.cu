@@ -197,7 +197,9 @@ struct BwdViews {
   RowView dk, dv;
 };
 
-template <int MODE>
+// VARLEN: query row i attends keys [p.kstart[b, i], i] only (see the forward kernel); masked scores are -inf, so their
+// probabilities, and with them every product they enter, are exact zeros.
+template <int MODE, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
@@ -492,6 +494,14 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             for (int i = 0; i < 32; ++i)
               if (cc * 32 + i > row) s[cc][i] = -INFINITY;
         }
+        if (VARLEN) {  // keys before the row's document
+          const int rel = __ldg(p.kstart + static_cast<int64_t>(c.bh / p.H) * p.S + q_row) - c.kt * T;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+        }
         const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(-lse, -lse);
         uint32_t pk[T / 2];
 #pragma unroll
@@ -611,8 +621,8 @@ size_t attn_bwd_tc_workspace_bytes(const ptj_attn_shape& sh) {
 
 int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
                 const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits, void* workspace,
-                size_t workspace_bytes, cudaStream_t st) {
+                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits,
+                const int32_t* row_kstart, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (workspace == nullptr || workspace_bytes < attn_bwd_tc_workspace_bytes(sh) || !aligned16(workspace))
     return PTJ_ERR_WORKSPACE;
   CUtensorMap tq, tk, tv, tg;
@@ -622,8 +632,15 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
   AttnParams p = make_params(sh, dr);
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
   p.keep_bits = reinterpret_cast<const uint4*>(keep_bits);
+  p.kstart = row_kstart;
   const bool masked = dr.train && dr.thr16 != 0u;
-  auto kern = !masked ? attn_bwd_ws_kernel<0> : (p.keep_bits != nullptr ? attn_bwd_ws_kernel<2> : attn_bwd_ws_kernel<1>);
+  const int mode = !masked ? 0 : (p.keep_bits != nullptr ? 2 : 1);
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const float*,
+                        const float*, float*, const BwdViews, const AttnParams, const Sched);
+  static const Kern kerns[2][3] = {
+      {attn_bwd_ws_kernel<0, false>, attn_bwd_ws_kernel<1, false>, attn_bwd_ws_kernel<2, false>},
+      {attn_bwd_ws_kernel<0, true>, attn_bwd_ws_kernel<1, true>, attn_bwd_ws_kernel<2, true>}};
+  const Kern kern = kerns[row_kstart != nullptr ? 1 : 0][mode];
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;

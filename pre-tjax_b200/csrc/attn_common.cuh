@@ -20,11 +20,13 @@ struct AttnDropout {
   }
 };
 
+// row_kstart (all four paths, optional): int32[batch, seq], the first key each query row may attend to; row i then
+// attends keys [row_kstart[b, i], i] (empty when row_kstart > i: zero output row, statistics (0, 1)). NULL = 0.
 int attn_fwd_simt(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                  const ptj_attn_shape& sh, const AttnDropout& dr, int dtype, cudaStream_t st);
+                  const int32_t* row_kstart, const ptj_attn_shape& sh, const AttnDropout& dr, int dtype, cudaStream_t st);
 int attn_bwd_simt(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
-                  const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                  const ptj_attn_shape& dsh, const AttnDropout& dr, int dtype, cudaStream_t st);
+                  const float* row_sum, void* dq, void* dk, void* dv, const int32_t* row_kstart,
+                  const ptj_attn_shape& sh, const ptj_attn_shape& dsh, const AttnDropout& dr, int dtype, cudaStream_t st);
 
 // tcgen05 kernels: bf16, d_head == 64, seq % 128 == 0, 16-byte aligned strides.
 bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int nptrs);
@@ -33,12 +35,13 @@ bool attn_tc_supported(const ptj_attn_shape& sh, const void* const* ptrs, int np
 size_t attn_keep_bits_bytes(const ptj_attn_shape& sh);
 int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                const uint32_t* keep_bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st);
+                const uint32_t* keep_bits, const int32_t* row_kstart, const ptj_attn_shape& sh, const AttnDropout& dr,
+                cudaStream_t st);
 // workspace: attn_bwd_tc_workspace_bytes(sh) bytes, 16-byte aligned (per-KV-tile dQ shares and per-row constants)
 size_t attn_bwd_tc_workspace_bytes(const ptj_attn_shape& sh);
 int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
                 const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits, void* workspace,
-                size_t workspace_bytes, cudaStream_t st);
+                const ptj_attn_shape& dsh, const AttnDropout& dr, const uint32_t* keep_bits,
+                const int32_t* row_kstart, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 }  // namespace ptj

@@ -71,7 +71,11 @@ struct Cursor {
 };
 
 // MODE 0: no dropout mask; 1: Philox drawn in the kernel; 2: precomputed keep flags (p.keep_bits).
-template <int MODE>
+// VARLEN: query row i attends keys [p.kstart[b, i], i] only (packed documents / padding, the block-diagonal x causal x
+// padding masks of the reference's collator, tokenized_dataset.py:110-131); a row whose range is empty gets a zero
+// output row and the statistics (row_max, row_sum) = (0, 1). The tile stream is the causal one: keys outside a row's
+// range are masked, whole tiles outside it contribute exact zeros.
+template <int MODE, bool VARLEN>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const RowView out, float* __restrict__ row_max,
@@ -318,6 +322,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             for (int i = 0; i < 32; ++i)
               if (cc * 32 + i > row) s[cc][i] = -INFINITY;
         }
+        if (VARLEN) {  // keys before the row's document: columns below rel (any tile may hold a boundary)
+          const int rel = __ldg(p.kstart + static_cast<int64_t>(c.bh / p.H) * p.S + q_row) - c.j * T;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+        }
         float mp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains of three-input maxima
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc)
@@ -347,7 +359,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           m_ref = mloc;
           l *= alpha;
         }
-        const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_ref, -m_ref);
+        // (VARLEN: a row that has met no key yet carries m_ref = -inf; its scores are all -inf too and must give 0)
+        const float nm = (VARLEN && m_ref == -INFINITY) ? 0.f : -m_ref;
+        const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(nm, nm);
         uint64_t rp[2] = {0ull, 0ull};  // two packed running sums (four chains)
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -434,7 +448,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!ok) break;
             const float m_o = dump[DH * T + row], l_o = dump[(DH + 1) * T + row];
             const float mm = fmaxf(m_ref, m_o);
-            const float fa = ex2_approx(m_ref - mm), fb = ex2_approx(m_o - mm);
+            float fa = ex2_approx(m_ref - mm), fb = ex2_approx(m_o - mm);
+            if (VARLEN) {  // a group that met no key of this row (-inf - -inf is not a number)
+              if (m_ref == -INFINITY) fa = 0.f;
+              if (m_o == -INFINITY) fb = 0.f;
+            }
 #pragma unroll
             for (int i = 0; i < DH; ++i) o[i] = o[i] * fa + dump[i * T + row] * fb;
             l = l * fa + l_o * fb;
@@ -446,7 +464,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           ++nd;
         }
         if (mine) {
-          const float inv = f_eval / l;
+          const bool empty = VARLEN && !(l > 0.f);  // the row attends nothing: zero output, neutral statistics
+          const float inv = empty ? 0.f : f_eval / l;
           __nv_bfloat16* dst = out.row(c.bh / p.H, c.bh % p.H, q_row);
 #pragma unroll
           for (int c8 = 0; c8 < DH / 8; ++c8) {
@@ -456,8 +475,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             Elem<__nv_bfloat16>::store_vec(dst + c8 * 8, t);
           }
           const int64_t ri = static_cast<int64_t>(c.bh) * p.S + q_row;
-          row_max[ri] = m_true * kLn2;                      // acts0: row maximum of the scaled scores
-          row_sum[ri] = l * ex2_approx(m_ref - m_true);     // acts1: sum of exp(score - maximum)
+          row_max[ri] = empty ? 0.f : m_true * kLn2;                   // acts0: row maximum of the scaled scores
+          row_sum[ri] = empty ? 1.f : l * ex2_approx(m_ref - m_true);  // acts1: sum of exp(score - maximum)
         }
         have = false;
       }
@@ -537,15 +556,23 @@ int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropou
 }
 
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                const uint32_t* keep_bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
+                const uint32_t* keep_bits, const int32_t* row_kstart, const ptj_attn_shape& sh, const AttnDropout& dr,
+                cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   if (!make_map(&tq, q, sh, sh.q_strides) || !make_map(&tk, k, sh, sh.k_strides) || !make_map(&tv, v, sh, sh.v_strides))
     return PTJ_ERR_LAUNCH;
   AttnParams p = make_params(sh, dr);
   if (p.fault == nullptr) return PTJ_ERR_DEVICE;
   p.keep_bits = reinterpret_cast<const uint4*>(keep_bits);
+  p.kstart = row_kstart;
   const bool masked = dr.train && dr.thr16 != 0u;
-  auto kern = !masked ? attn_fwd_ws_kernel<0> : (keep_bits != nullptr ? attn_fwd_ws_kernel<2> : attn_fwd_ws_kernel<1>);
+  const int mode = !masked ? 0 : (keep_bits != nullptr ? 2 : 1);
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const RowView, float*, float*,
+                        const AttnParams, const Sched);
+  static const Kern kerns[2][3] = {
+      {attn_fwd_ws_kernel<0, false>, attn_fwd_ws_kernel<1, false>, attn_fwd_ws_kernel<2, false>},
+      {attn_fwd_ws_kernel<0, true>, attn_fwd_ws_kernel<1, true>, attn_fwd_ws_kernel<2, true>}};
+  const Kern kern = kerns[row_kstart != nullptr ? 1 : 0][mode];
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;

@@ -14,8 +14,8 @@ constexpr int kMaxD = 128;
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ o,
-                     float* __restrict__ row_max, float* __restrict__ row_sum, const ptj_attn_shape sh, float scale,
-                     AttnDropout dr) {
+                     float* __restrict__ row_max, float* __restrict__ row_sum, const int32_t* __restrict__ kstart,
+                     const ptj_attn_shape sh, float scale, AttnDropout dr) {
   grid_dep_sync();
   __shared__ float qs[kWarpsPerBlock][kMaxD];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -31,17 +31,20 @@ attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
     for (int d = lane; d < D; d += 32) qs[w][d] = Elem<T>::load(qr + d);
     __syncwarp();
     float m = -INFINITY, l = 0.f, acc[kMaxD / 32] = {0.f, 0.f, 0.f, 0.f};
-    for (int64_t j0 = 0; j0 <= i; j0 += 32) {
+    // the row attends keys [ks, i]: the whole causal prefix, or from its document's first token when kstart is given
+    const int64_t ks = kstart != nullptr ? kstart[b * S + i] : 0;
+    const bool empty = ks > i;  // the row attends nothing: zero output, neutral statistics
+    for (int64_t j0 = (ks > 0 ? ks : 0) / 32 * 32; j0 <= i && !empty; j0 += 32) {
       const int64_t j = j0 + lane;
       float s = -INFINITY;
-      if (j <= i) {
+      if (j <= i && j >= ks) {
         const T* kr = kb + j * sh.k_strides[2];
         float t = 0.f;
         for (int d = 0; d < D; ++d) t = fmaf(qs[w][d], Elem<T>::load(kr + d), t);
         s = t * scale;
       }
-      const float mnew = fmaxf(m, warp_max(s));
-      const float p = j <= i ? expf(s - mnew) : 0.f;
+      const float mnew = fmaxf(m, warp_max(s));  // finite: the first 32 keys visited include key ks <= i
+      const float p = (j <= i && j >= ks) ? expf(s - mnew) : 0.f;
       const float corr = expf(m - mnew);
       l = l * corr + warp_sum(p);
       const float pd = p * dr.factor(bh, S, i, j);
@@ -60,7 +63,8 @@ attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
       m = mnew;
     }
     T* orow = o + b * sh.o_strides[0] + h * sh.o_strides[1] + i * sh.o_strides[2];
-    const float inv = 1.f / l;
+    if (empty) { m = 0.f; l = 1.f; }
+    const float inv = empty ? 0.f : 1.f / l;
 #pragma unroll
     for (int t = 0; t < kMaxD / 32; ++t) {
       const int d = lane + 32 * t;
@@ -79,7 +83,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attn_bwd_simt_kernel(const T* __restrict__ d_o, const T* __restrict__ q, const T* __restrict__ k,
                      const T* __restrict__ v, const T* __restrict__ o, const float* __restrict__ row_max,
                      const float* __restrict__ row_sum, T* __restrict__ dq, T* __restrict__ dk, T* __restrict__ dv,
-                     const ptj_attn_shape sh, const ptj_attn_shape dsh, float scale, AttnDropout dr) {
+                     const int32_t* __restrict__ kstart, const ptj_attn_shape sh, const ptj_attn_shape dsh, float scale,
+                     AttnDropout dr) {
   grid_dep_sync();
   __shared__ float xs[kWarpsPerBlock][kMaxD];  // MODE 0: q row;  MODE 1: k row
   __shared__ float ys[kWarpsPerBlock][kMaxD];  // MODE 0: dO row; MODE 1: v row
@@ -107,10 +112,11 @@ attn_bwd_simt_kernel(const T* __restrict__ d_o, const T* __restrict__ q, const T
       for (int d = lane; d < D; d += 32) dl += ys[w][d] * Elem<T>::load(ob + i * sh.o_strides[2] + d);
       const float delta = warp_sum(dl);
       const float m = row_max[rid], inv_l = 1.f / row_sum[rid];
-      for (int64_t j0 = 0; j0 <= i; j0 += 32) {
+      const int64_t ks = kstart != nullptr ? kstart[b * S + i] : 0;
+      for (int64_t j0 = (ks > 0 ? ks : 0) / 32 * 32; j0 <= i; j0 += 32) {
         const int64_t j = j0 + lane;
         float ds = 0.f;
-        if (j <= i) {
+        if (j <= i && j >= ks) {
           const T* kr = kb + j * sh.k_strides[2];
           const T* vr = vb + j * sh.v_strides[2];
           float s = 0.f, dpd = 0.f;
@@ -143,7 +149,7 @@ attn_bwd_simt_kernel(const T* __restrict__ d_o, const T* __restrict__ q, const T
       for (int64_t i0 = j; i0 < S; i0 += 32) {
         const int64_t i = i0 + lane;
         float pd = 0.f, ds = 0.f;
-        if (i < S) {
+        if (i < S && (kstart == nullptr || kstart[b * S + i] <= j)) {  // query i attends key j
           const T* qr = qb + i * sh.q_strides[2];
           const T* gr = gb + i * sh.o_strides[2];
           const T* orow = ob + i * sh.o_strides[2];
@@ -199,18 +205,18 @@ inline int simt_grid(int64_t rows) {
 }  // namespace
 
 int attn_fwd_simt(const void* q, const void* k, const void* v, void* o, float* row_max, float* row_sum,
-                  const ptj_attn_shape& sh, const AttnDropout& dr, int dtype, cudaStream_t st) {
+                  const int32_t* row_kstart, const ptj_attn_shape& sh, const AttnDropout& dr, int dtype, cudaStream_t st) {
   if (sh.d_head > kMaxD) return PTJ_ERR_UNSUPPORTED;
   const float scale = 1.f / sqrtf(static_cast<float>(sh.d_head));
   const int grid = simt_grid(sh.batch * sh.heads * sh.seq);
   if (dtype == PTJ_F32)
     launch_k(attn_fwd_simt_kernel<float>, grid, kWarpsPerBlock * 32, 0, st, 
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), static_cast<float*>(o),
-        row_max, row_sum, sh, scale, dr);
+        row_max, row_sum, row_kstart, sh, scale, dr);
   else
     launch_k(attn_fwd_simt_kernel<__nv_bfloat16>, grid, kWarpsPerBlock * 32, 0, st, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
-        static_cast<__nv_bfloat16*>(o), row_max, row_sum, sh, scale, dr);
+        static_cast<__nv_bfloat16*>(o), row_max, row_sum, row_kstart, sh, scale, dr);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
@@ -218,28 +224,30 @@ int attn_fwd_simt(const void* q, const void* k, const void* v, void* o, float* r
 template <typename T>
 static int bwd_simt_typed(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                           const float* row_max, const float* row_sum, void* dq, void* dk, void* dv,
-                          const ptj_attn_shape& sh, const ptj_attn_shape& dsh, const AttnDropout& dr, cudaStream_t st) {
+                          const int32_t* row_kstart, const ptj_attn_shape& sh, const ptj_attn_shape& dsh,
+                          const AttnDropout& dr, cudaStream_t st) {
   const float scale = 1.f / sqrtf(static_cast<float>(sh.d_head));
   const int grid = simt_grid(sh.batch * sh.heads * sh.seq);
   launch_k(attn_bwd_simt_kernel<T, 0>, grid, kWarpsPerBlock * 32, 0, st, 
       static_cast<const T*>(d_o), static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
-      static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv), sh, dsh,
-      scale, dr);
+      static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv),
+      row_kstart, sh, dsh, scale, dr);
   PTJ_CHECK_LAUNCH();
   launch_k(attn_bwd_simt_kernel<T, 1>, grid, kWarpsPerBlock * 32, 0, st, 
       static_cast<const T*>(d_o), static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
-      static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv), sh, dsh,
-      scale, dr);
+      static_cast<const T*>(o), row_max, row_sum, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv),
+      row_kstart, sh, dsh, scale, dr);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
 
 int attn_bwd_simt(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* row_max,
-                  const float* row_sum, void* dq, void* dk, void* dv, const ptj_attn_shape& sh,
-                  const ptj_attn_shape& dsh, const AttnDropout& dr, int dtype, cudaStream_t st) {
+                  const float* row_sum, void* dq, void* dk, void* dv, const int32_t* row_kstart,
+                  const ptj_attn_shape& sh, const ptj_attn_shape& dsh, const AttnDropout& dr, int dtype, cudaStream_t st) {
   if (sh.d_head > kMaxD) return PTJ_ERR_UNSUPPORTED;
-  if (dtype == PTJ_F32) return bwd_simt_typed<float>(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, sh, dsh, dr, st);
-  return bwd_simt_typed<__nv_bfloat16>(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, sh, dsh, dr, st);
+  if (dtype == PTJ_F32)
+    return bwd_simt_typed<float>(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, row_kstart, sh, dsh, dr, st);
+  return bwd_simt_typed<__nv_bfloat16>(d_o, q, k, v, o, row_max, row_sum, dq, dk, dv, row_kstart, sh, dsh, dr, st);
 }
 
 }  // namespace ptj

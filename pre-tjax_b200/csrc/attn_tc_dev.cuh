@@ -30,6 +30,7 @@ struct AttnParams {
   AttnDropout dr;
   uint32_t rk[20];   // Philox round keys of dr.seed (round r uses rk[2r], rk[2r+1]): the same for every call
   const uint4* keep_bits;  // optional precomputed keep flags, one uint4 per (batch*head, tile, row): see attn_keep_bits_tc
+  const int32_t* kstart;   // optional [batch, seq]: first key a query row may attend to (document start); NULL = 0
   unsigned int* fault;
 };
 

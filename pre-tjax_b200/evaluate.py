@@ -22,19 +22,20 @@ from . import operators as ops
 from .gpt2 import Gpt2Step, Weights, _seeds_or_zero, config_from_params
 
 
-def _forward_padded(params, ids, train, p_gen_aux):
+def _forward_padded(params, ids, train, p_gen_aux, y_mask=None):
     """(logits [B*S, vocab_ld], cfg, step): the first cfg.vocab columns of a row are valid."""
     cfg = config_from_params(params, ops.DROPOUT_RATE)
     step = Gpt2Step(cfg, params[0][0].dtype)
     w = Weights.from_pytree(params, cfg, step.dtype)
-    logits, _ = step.forward(w, ids.to(torch.int32).contiguous(), train, _seeds_or_zero(p_gen_aux, cfg))
+    logits, _ = step.forward(w, ids.to(torch.int32).contiguous(), train, _seeds_or_zero(p_gen_aux, cfg),
+                             row_kstart=ops._kstart_or_none(y_mask))
     return logits, cfg, step
 
 
 def t_gpt2_forward(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
-    """logits [B, S, V] for token ids y [B, S]. y_mask must be causal and y_indices are ignored, as in the
-    reference's Triton path."""
-    logits, cfg, _ = _forward_padded(params, y, train, p_gen_aux)
+    """logits [B, S, V] for token ids y [B, S]. y_mask [B,S,S] bool: the collator's causal x block-diagonal x padding
+    mask (None = causal); y_indices are ignored, as in the reference."""
+    logits, cfg, _ = _forward_padded(params, y, train, p_gen_aux, y_mask)
     B, S = y.shape
     return logits.view(B, S, -1)[:, :, :cfg.vocab]
 
@@ -43,7 +44,7 @@ def t_loss(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
     """y [B, S+1]: inputs y[:, :-1], labels y[:, 1:]. Returns (loss, (loss, accuracy, fraction of labels != 0)),
     the shape ``_loss`` returns (loss_and_optimizer_triton.py:221-230); one fused kernel produces all three."""
     labels = y[:, 1:].contiguous()
-    logits, cfg, _ = _forward_padded(params, y[:, :-1], train, p_gen_aux)
+    logits, cfg, _ = _forward_padded(params, y[:, :-1], train, p_gen_aux, y_mask)
     stats, _, _ = ops.cross_entropy(labels, logits, cols=cfg.vocab, want_grad=False)
     return stats[0], (stats[0], stats[1], stats[2])
 
@@ -56,7 +57,7 @@ def log_probs(params, y, y_mask=None, y_indices=None):
     ``train=False``; a padding label (id 0) contributes +1, as in the reference."""
     B = y.shape[0]
     labels = y[:, 1:].contiguous()
-    logits, cfg, _ = _forward_padded(params, y[:, :-1], False, None)
+    logits, cfg, _ = _forward_padded(params, y[:, :-1], False, None, y_mask)
     _, _, _, row_loss = ops.cross_entropy(labels, logits, cols=cfg.vocab, want_grad=False, want_rows=True)
     elems = torch.where(labels.reshape(-1) != 0, -row_loss, torch.ones_like(row_loss))
     return elems.view(B, -1).sum(dim=1)

@@ -168,8 +168,10 @@ class Gpt2Step:
                         ldb=w2d.stride(0), out_dtype=self.dtype, **kw)
 
     # -- forward --
-    def forward(self, w: Weights, ids_in: torch.Tensor, train: bool, seeds: Sequence[int]):
-        """Returns (logits [B*S, vocab_ld] (first `vocab` columns valid), saved activations)."""
+    def forward(self, w: Weights, ids_in: torch.Tensor, train: bool, seeds: Sequence[int], row_kstart=None):
+        """Returns (logits [B*S, vocab_ld] (first `vocab` columns valid), saved activations).
+        row_kstart: optional int32 [B, S], first key each position attends to (packed documents / padding, see
+        operators.row_kstart_from_mask); None = plain causal attention."""
         cfg, p = self.cfg, self.cfg.dropout
         B, S = ids_in.shape
         assert S == cfg.seq, "the positional table is added without slicing: sequence length must equal cfg.seq"
@@ -177,7 +179,7 @@ class Gpt2Step:
         if not train:
             seeds = [0] * (1 + 3 * cfg.layers)
         x = ops.embed_fwd(ids_in, w["w_emb"], w["w_pos"], train, seeds[0], out_dtype=self.dtype, p=p).view(T, D)
-        acts = {"layers": []}
+        acts = {"layers": [], "row_kstart": row_kstart}
         for l in range(cfg.layers):
             s_attn, s_res1, s_res2 = seeds[1 + 3 * l: 4 + 3 * l]
             g = lambda n: w[f"l{l}.{n}"]
@@ -190,7 +192,7 @@ class Gpt2Step:
             o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
             # the layer's attention-dropout keep flags are drawn once and shared by the forward and backward kernels
             a["keep"] = ops.attn_keep_bits(q, k, v, o4, s_attn, p=p) if (train and p > 0.0) else None
-            a["m"], a["l"] = ops.attn_fwd(q, k, v, o4, train, s_attn, p=p, keep_bits=a["keep"])
+            a["m"], a["l"] = ops.attn_fwd(q, k, v, o4, train, s_attn, p=p, keep_bits=a["keep"], row_kstart=row_kstart)
             a["x_mid"] = ops.gemm(a["attn"], g("w_o"), epilogue=_lib.EPI_DROPOUT_RESID, aux=x,
                                   dropout_args=(p, train, s_res1, 0))
             a["ln2"] = ops.t_layernorm_fwd_t((g("g2"), g("b2")), a["x_mid"])
@@ -263,7 +265,8 @@ class Gpt2Step:
             dq, dk, dv = (dqkv5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
             o4 = a["attn"].view(B, S, H, dh).permute(0, 2, 1, 3)
             do4 = d_attn.view(B, S, H, dh).permute(0, 2, 1, 3)
-            ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p, keep_bits=a.get("keep"))
+            ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p, keep_bits=a.get("keep"),
+                         row_kstart=acts.get("row_kstart"))
             self._wgrad(dqkv, a["ln1"], G("w_qkv").view(3 * D, D))
             d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
             s_prev = seeds[3 * l] if l > 0 else 0  # the layer below's second residual dropout consumes this dx
@@ -292,12 +295,12 @@ class Gpt2Step:
 
     # -- loss + gradients --
     def loss_and_grads(self, w: Weights, grads: dict, y: torch.Tensor, train: bool, seeds: Sequence[int],
-                       n_valid: Optional[torch.Tensor] = None, on_ready=None, sorted_pos=None):
+                       n_valid: Optional[torch.Tensor] = None, on_ready=None, sorted_pos=None, row_kstart=None):
         """y: [B, S+1] token ids; inputs y[:, :-1], labels y[:, 1:] (loss_and_optimizer_triton.py:280-281).
         Returns float32[3] = (mean loss over labels != 0, accuracy, fraction of labels != 0)."""
         ids_in = y[:, :-1].contiguous().to(torch.int32)
         labels = y[:, 1:].contiguous().to(torch.int32)
-        logits, acts = self.forward(w, ids_in, train, seeds)
+        logits, acts = self.forward(w, ids_in, train, seeds, row_kstart=row_kstart)
         if sorted_pos is not None:
             acts["sorted_pos"] = sorted_pos
         stats, _, dlogits = ops.cross_entropy(labels, logits, cols=self.cfg.vocab, want_grad=True, in_place=True,
@@ -312,13 +315,15 @@ def _seeds_or_zero(p_gen_aux, cfg):
 
 
 def t_gpt2_forward_with_acts_t(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux=None):
-    """(logits [B,S,V], acts) (model_triton.py:2535-2539). y_mask must be causal and y_indices are ignored, as in the
-    reference's Triton path. The activations object is opaque: pass it to t_gpt2_bkwd3_p_t."""
+    """(logits [B,S,V], acts) (model_triton.py:2535-2539). y_mask [B,S,S] bool is the reference collator's mask
+    (causal, optionally x block-diagonal over packed documents x padding; None = causal); y_indices are ignored, as in
+    both of the reference's paths (the position table is added whole, :2339). The activations object is opaque: pass
+    it to t_gpt2_bkwd3_p_t."""
     cfg = config_from_params(params, ops.DROPOUT_RATE)
     step = Gpt2Step(cfg, params[0][0].dtype)
     w = Weights.from_pytree(params, cfg, step.dtype)
     ids = y.to(torch.int32).contiguous()
-    logits, acts = step.forward(w, ids, train, _seeds_or_zero(p_gen_aux, cfg))
+    logits, acts = step.forward(w, ids, train, _seeds_or_zero(p_gen_aux, cfg), row_kstart=ops._kstart_or_none(y_mask))
     B, S = ids.shape
     acts["_step"], acts["_w"], acts["_logits_padded"] = step, w, logits
     return logits.view(B, S, -1)[:, :, :cfg.vocab], acts
@@ -343,5 +348,6 @@ def t_loss_bkwd3_t(params, y, y_mask=None, y_indices=None, train=True, p_gen_aux
     step = Gpt2Step(cfg, params[0][0].dtype)
     w = Weights.from_pytree(params, cfg, step.dtype)
     grads = {n: torch.empty(s, device=y.device, dtype=torch.float32) for n, s in cfg.param_shapes()}
-    stats = step.loss_and_grads(w, grads, y, train, _seeds_or_zero(p_gen_aux, cfg))
+    stats = step.loss_and_grads(w, grads, y, train, _seeds_or_zero(p_gen_aux, cfg),
+                                row_kstart=ops._kstart_or_none(y_mask))
     return unflatten_like([grads[n] for n, _ in cfg.param_shapes()], cfg), (stats[0], stats[1], stats[2])

@@ -281,15 +281,18 @@ def attn_keep_bits(q, k, v, out, seed, stream_id=0, p=None, bits=None):
     return bits
 
 
-def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None, keep_bits=None):
-    """q,k,v,out: [B,H,N,D] strided views (D contiguous). Returns (row_max, row_sum) float32 [B,H,N]."""
+def attn_fwd(q, k, v, out, train, seed, stream_id=0, p=None, keep_bits=None, row_kstart=None):
+    """q,k,v,out: [B,H,N,D] strided views (D contiguous). Returns (row_max, row_sum) float32 [B,H,N].
+    row_kstart: optional int32 [B,N], first key each query row attends to (see row_kstart_from_mask)."""
     B, H, N, D = q.shape
+    row_kstart = _check_kstart(row_kstart, B, N, q.device)
     m = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
     l = torch.empty_like(m)
     sh = _attn_shape(B, H, N, D, q, k, v, out.stride()[:3])
     p = DROPOUT_RATE if p is None else p
     _lib.check(_lib.lib().ptj_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(m), _ptr(l), ctypes.byref(sh), p,
-                                       int(bool(train)), _seed(seed), stream_id, _ptr(keep_bits), _dt(q), _stream()),
+                                       int(bool(train)), _seed(seed), stream_id, _ptr(keep_bits), _ptr(row_kstart), _dt(q),
+                                       _stream()),
                "ptj_attn_fwd")
     return m, l
 
@@ -307,10 +310,12 @@ def attn_bwd_workspace(nbytes, device):
     return buf
 
 
-def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None, workspace=None, keep_bits=None):
+def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None, workspace=None, keep_bits=None,
+             row_kstart=None):
     """workspace: optional uint8 tensor of at least ptj_attn_bwd_workspace_bytes; by default one buffer per
-    (device, stream) is kept and reused."""
+    (device, stream) is kept and reused. row_kstart: the array the forward call was given."""
     B, H, N, D = q.shape
+    row_kstart = _check_kstart(row_kstart, B, N, q.device)
     assert d_o.stride() == o.stride(), "dO and O must share a layout"
     sh = _attn_shape(B, H, N, D, q, k, v, o.stride()[:3])
     dsh = _attn_shape(B, H, N, D, dq, dk, dv, o.stride()[:3])
@@ -323,17 +328,84 @@ def attn_bwd(d_o, q, k, v, o, m, l, dq, dk, dv, train, seed, stream_id=0, p=None
     _lib.check(
         _lib.lib().ptj_attn_bwd(_ptr(d_o), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(m), _ptr(l), _ptr(dq), _ptr(dk),
                                 _ptr(dv), ctypes.byref(sh), ctypes.byref(dsh), p, int(bool(train)), _seed(seed),
-                                stream_id, _ptr(keep_bits), wptr, wbytes, _dt(q), _stream()), "ptj_attn_bwd")
+                                stream_id, _ptr(keep_bits), _ptr(row_kstart), wptr, wbytes, _dt(q), _stream()),
+        "ptj_attn_bwd")
+
+
+def _check_kstart(row_kstart, B, N, device):
+    if row_kstart is None:
+        return None
+    if not row_kstart.is_cuda or row_kstart.dtype != torch.int32 or tuple(row_kstart.shape) != (B, N):
+        raise ValueError(f"row_kstart must be a CUDA int32 tensor of shape [{B}, {N}]")
+    return row_kstart.contiguous()
+
+
+# Dense masks are checked against the interval form the kernels work with (one host synchronisation per new mask);
+# callers that build their masks the way the reference's collator does may switch the check off.
+VERIFY_MASKS = True
+_KSTART_CACHE = {}  # (data_ptr, version, shape) -> row_kstart of the most recent masks
+
+
+def row_kstart_from_lengths(doc_lengths, seq: int, device="cuda") -> torch.Tensor:
+    """int32 [B, seq] for packed rows: doc_lengths[b] lists the lengths of the documents packed into row b, in order
+    (the x_lens / y_lens of the reference's collator, tokenized_dataset.py:206-232); positions beyond their sum are
+    padding and attend nothing. Token t of a document that starts at s gets row_kstart = s."""
+    out = torch.empty((len(doc_lengths), seq), dtype=torch.int32)
+    for b, lens in enumerate(doc_lengths):
+        pos = 0
+        for n in lens:
+            n = min(int(n), seq - pos)
+            out[b, pos:pos + n] = pos
+            pos += n
+        out[b, pos:] = torch.arange(pos, seq, dtype=torch.int32) + 1  # padding: empty range
+    return out.to(device)
+
+
+def row_kstart_from_mask(mask: torch.Tensor) -> torch.Tensor:
+    """The kernels' form of a dense attention mask [B, N, N] (True = attend) as the reference's collator builds it:
+    causal x block-diagonal over the documents packed into a row x padding (tokenized_dataset.py:110-131). Every row
+    of such a mask is an interval of keys that ends at the row's own position (or is empty, for padding rows), so
+    the mask is fully described by row_kstart[b, i] = first attended key (i + 1 for an empty row). A mask that is not
+    of this form is refused (the check costs one host synchronisation; VERIFY_MASKS = False skips it)."""
+    if mask.dim() != 3 or mask.shape[1] != mask.shape[2]:
+        raise ValueError("mask must be [B, N, N]")
+    key = (mask.data_ptr(), mask._version, tuple(mask.shape))
+    hit = _KSTART_CACHE.get(key)
+    if hit is not None:
+        return hit
+    mb = _cuda(mask, "mask").bool()
+    B, N, _ = mb.shape
+    idx = torch.arange(N, device=mb.device, dtype=torch.int32)
+    first = torch.argmax(mb.to(torch.uint8), dim=2).to(torch.int32)  # first True of a row (0 when the row has none)
+    kstart = torch.where(mb.any(dim=2), first, idx.view(1, N) + 1)
+    if VERIFY_MASKS:
+        j = idx.view(1, 1, N)
+        rebuilt = (j >= kstart.view(B, N, 1)) & (j <= idx.view(1, N, 1))
+        if not torch.equal(rebuilt, mb):
+            raise ValueError("attention mask is not causal x block-diagonal x padding: every row must attend an "
+                             "interval of keys that ends at its own position (or nothing)")
+    if len(_KSTART_CACHE) > 8:
+        _KSTART_CACHE.clear()
+    _KSTART_CACHE[key] = kstart
+    return kstart
+
+
+def _kstart_or_none(mask):
+    """None for no mask or the plain causal one (the fast path), else its row_kstart."""
+    if mask is None:
+        return None
+    ks = row_kstart_from_mask(mask)
+    return ks if bool((ks != 0).any()) else None
 
 
 def t_scaled_dot_prod_attn_fwd3_t(qkv: torch.Tensor, mask: torch.Tensor = None, train=True, p_gen_aux=None):
-    """Causal attention on qkv[B,H,3,N,D] -> (out[B,H,N,D], [row_max, row_sum, out]) (model_triton.py:706-754).
-    `mask` is accepted for signature compatibility and must be the causal mask (as the reference kernel assumes,
-    :728-731); it is never read."""
+    """Masked attention on qkv[B,H,3,N,D] -> (out[B,H,N,D], [row_max, row_sum, out]) (model_triton.py:706-754).
+    `mask` [B,N,N] bool is applied like the reference kernel applies it (:678-681): it must be causal, optionally
+    times the block-diagonal document mask and the padding mask of the reference's collator; None = causal."""
     qkv = _cuda(qkv, "qkv")
     q, k, v = qkv.unbind(dim=2)
     out = torch.empty(q.shape, device=qkv.device, dtype=qkv.dtype)
-    m, l = attn_fwd(q, k, v, out, train, p_gen_aux)
+    m, l = attn_fwd(q, k, v, out, train, p_gen_aux, row_kstart=_kstart_or_none(mask))
     return out, [m, l, out]
 
 
@@ -346,7 +418,7 @@ def t_scaled_dot_prod_attn_bkwd3_t(dloss_dx, acts, qkv: torch.Tensor, mask: torc
     d_o = _cuda(dloss_dx, "dloss_dx").to(qkv.dtype).reshape(out.shape)
     out = _cuda(out)
     dq, dk, dv = (torch.empty(q.shape, device=qkv.device, dtype=qkv.dtype) for _ in range(3))
-    attn_bwd(d_o, q, k, v, out, _cuda(m), _cuda(l), dq, dk, dv, train, p_gen_aux)
+    attn_bwd(d_o, q, k, v, out, _cuda(m), _cuda(l), dq, dk, dv, train, p_gen_aux, row_kstart=_kstart_or_none(mask))
     return dq, dk, dv
 
 

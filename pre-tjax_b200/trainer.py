@@ -246,9 +246,11 @@ class Trainer:
     def grads_pytree(self):
         return unflatten_like([self.gv[n] for n, _ in self.cfg.param_shapes()], self.cfg)
 
-    def step(self, y: torch.Tensor, lr: Optional[float] = None, train: bool = True) -> torch.Tensor:
+    def step(self, y: torch.Tensor, lr: Optional[float] = None, train: bool = True, row_kstart=None) -> torch.Tensor:
         """y: [B, S+1] int32 token ids (host, ideally pinned, or device). Returns float32[3] on the device:
-        mean loss, accuracy, fraction of non-padding labels (of this rank's micro-batch)."""
+        mean loss, accuracy, fraction of non-padding labels (of this rank's micro-batch).
+        row_kstart: optional int32 [B, S] on the device for packed / padded batches (operators.row_kstart_from_lengths
+        or row_kstart_from_mask): position i attends keys [row_kstart[b, i], i]; None = plain causal."""
         if not y.is_cuda:
             if self.ids_dev is None or self.ids_dev.shape != y.shape:
                 self.ids_dev = torch.empty(y.shape, device=self.device, dtype=torch.int32)
@@ -266,7 +268,7 @@ class Trainer:
                 n_valid = n_valid / self.world  # gradients are averaged over ranks afterwards
         on_ready = self.reducer.mark_ready if self.reducer is not None else None
         stats = self.engine.loss_and_grads(self.w, self.gv, y, train, seeds, n_valid=n_valid, on_ready=on_ready,
-                                           sorted_pos=sorted_pos)
+                                           sorted_pos=sorted_pos, row_kstart=row_kstart)
         if self.reducer is not None:
             self.reducer.finish()
         self.apply_update(lr if lr is not None else self.tc.lr)

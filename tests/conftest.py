@@ -59,3 +59,8 @@ def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
 @pytest.fixture(scope="session")
 def eval_golden():
     return load_golden("eval_callers.npz")
+
+
+@pytest.fixture(scope="session")
+def packed_golden():
+    return load_golden("packed_model.npz")

@@ -184,3 +184,26 @@ def test_eval_callers(tiny_golden, eval_golden):
     pred = orc.predict(params_pred, y.shape[0], int(g["dims"][5]), int(e["start_tok"]), int(e["end_tok"]), p)
     assert torch.equal(pred, tt(e["predict"]))
     assert len(set(pred[0].tolist())) > 5  # the decoded ids differ from position to position
+
+
+def test_packed_batch_with_document_and_padding_masks(packed_golden):
+    """Rows built by the reference's collator (several documents per row, padding tail): the oracle with the same
+    dense mask reproduces the reference's loss, accuracy and every gradient, and its attention operator pair."""
+    g = packed_golden
+    params, n = _tree_from(g, g["dims"])
+    y, mask = tt(g["y"]), tt(g["mask"])
+    assert not mask[0, 6, 5] and mask[0, 6, 6] and not mask[0, 12].any(), "document boundary and padding rows expected"
+    grads, (loss, acc, frac) = orc.loss_and_grads(params, y, attn_mask=mask)
+    close(loss, tt(g["loss"]))
+    close(acc, tt(g["acc"]))
+    close(frac, tt(g["frac"]))
+    for i, gr in enumerate(t for grp in grads for t in grp):
+        close(gr, tt(g[f"g{i}"]), 2e-5)
+    qkv, d_o = tt(g["attn_qkv"]), tt(g["attn_do"])
+    am = mask.unsqueeze(1)
+    out, _ = orc.causal_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], attn_mask=am)
+    close(out, tt(g["attn_out"]))
+    dq, dk, dv = orc.causal_attention_bwd(d_o, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], attn_mask=am)
+    close(dq, tt(g["attn_dq"]), 2e-5)
+    close(dk, tt(g["attn_dk"]), 2e-5)
+    close(dv, tt(g["attn_dv"]), 2e-5)
