@@ -10,6 +10,7 @@ set ``operators.DROPOUT_RATE`` before calling.
 from __future__ import annotations
 
 import ctypes
+import weakref
 
 import torch
 
@@ -343,7 +344,7 @@ def _check_kstart(row_kstart, B, N, device):
 # Dense masks are checked against the interval form the kernels work with (one host synchronisation per new mask);
 # callers that build their masks the way the reference's collator does may switch the check off.
 VERIFY_MASKS = True
-_KSTART_CACHE = {}  # (data_ptr, version, shape) -> row_kstart of the most recent masks
+_KSTART_CACHE = []  # (weak reference to a mask tensor, its version counter, row_kstart): the most recent masks
 
 
 def row_kstart_from_lengths(doc_lengths, seq: int, device="cuda") -> torch.Tensor:
@@ -369,10 +370,10 @@ def row_kstart_from_mask(mask: torch.Tensor) -> torch.Tensor:
     of this form is refused (the check costs one host synchronisation; VERIFY_MASKS = False skips it)."""
     if mask.dim() != 3 or mask.shape[1] != mask.shape[2]:
         raise ValueError("mask must be [B, N, N]")
-    key = (mask.data_ptr(), mask._version, tuple(mask.shape))
-    hit = _KSTART_CACHE.get(key)
-    if hit is not None:
-        return hit
+    # the same tensor object, unmodified since (one batch's mask is used by every layer, forward and backward)
+    for ref, version, ks in _KSTART_CACHE:
+        if ref() is mask and version == mask._version:
+            return ks
     mb = _cuda(mask, "mask").bool()
     B, N, _ = mb.shape
     idx = torch.arange(N, device=mb.device, dtype=torch.int32)
@@ -384,9 +385,8 @@ def row_kstart_from_mask(mask: torch.Tensor) -> torch.Tensor:
         if not torch.equal(rebuilt, mb):
             raise ValueError("attention mask is not causal x block-diagonal x padding: every row must attend an "
                              "interval of keys that ends at its own position (or nothing)")
-    if len(_KSTART_CACHE) > 8:
-        _KSTART_CACHE.clear()
-    _KSTART_CACHE[key] = kstart
+    _KSTART_CACHE[:] = [e for e in _KSTART_CACHE if e[0]() is not None][-7:]
+    _KSTART_CACHE.append((weakref.ref(mask), mask._version, kstart))
     return kstart
 
 

@@ -70,8 +70,8 @@ def test_reference_packed_batch_fp32(packed_golden):
         for i, gr in enumerate(flat(grads)):
             assert rel_err(gr, tt(g[f"g{i}"])) < 1e-4, f"gradient {i}"
         # ignoring the mask must give a different answer (documents would attend across their boundaries)
-        _, (loss_c, _, _) = gpt2.t_loss_bkwd3_t(gp, y, None, None, True, [1] * (1 + 3 * L))
-        assert abs(float(loss_c) - float(loss)) > 1e-4
+        grads_c, _ = gpt2.t_loss_bkwd3_t(gp, y, None, None, True, [1] * (1 + 3 * L))
+        assert rel_err(grads_c[2][2], grads[2][2]) > 1e-2, "the first layer's QKV gradient must feel the mask"
         # the attention operator pair with the dense mask, non-padding rows (the reference attends all keys uniformly
         # on a row without keys; here such rows give zeros)
         qkv, d_o = tt(g["attn_qkv"]).cuda(), tt(g["attn_do"]).cuda()
