@@ -34,9 +34,14 @@ if str(ROOT) not in sys.path:
 METRIC = "GPT-2 113M train tokens/s"
 UNIT = "tokens/s"
 MICRO_BATCH = 8
-# DRAM bytes (read + write) per launch of the dominant kernel, averaged over the GEMM launches of the train step,
-# from the ncu capture summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 84.8e6  # DRAM read + write bytes of the average GEMM launch of a step, from an ncu capture
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the tcgen05 GEMM at the shapes of the
+# GPT-2 small step, from single-kernel ncu captures of pre-tjax_b200/kernel_bench.py cases (the summaries under
+# profiles/ named here). `roofline.traffic` is the launch-weighted mean over the GEMM launches of the timed steps:
+# a captured shape contributes its measured bytes, any other shape its algorithmic bytes (operands read once, output
+# written once), and the line says how many launches were covered by a capture.
+NCU_GEMM_TRAFFIC = {
+    # (M, N, K, a_kmajor, b_kmajor): (bytes per launch, profiles/ file)
+}
 
 
 def zipf_ids(vocab: int, shape, seed: int, a: float = 1.1) -> torch.Tensor:
@@ -99,8 +104,49 @@ def measured_peaks() -> tuple:
 
 
 # ---- CPU arm: the reference algorithm (oracle port) on the host cores -----------------------------------------------
+def reference_checkout_step_rate(ref_dir: str, cfg, steps: int, warmup: int, seqs: int) -> dict:
+    """The UNMODIFIED reference (a checkout of martin-kukla/pre-tjax at ref_dir) on the host cores: its torch.func
+    gradient (uncompiled_grad_loss, loss_and_optimizer_triton.py:234) + adam_w_in_place (:376-401), float32, dropout
+    rate 0 (a module constant of the reference), the reference's own parameter initialisation. The reference has no
+    gradient clipping, so none is timed."""
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    import model_torch_func as mtf
+    mtf.DEVICE = "cpu"
+    mtf.DROPOUT_RATE = 0.0
+    import model_triton as mt
+    mt.DROPOUT_RATE = 0.0
+    import loss_and_optimizer_triton as lot
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    torch.manual_seed(0)
+    prm = mtf.init_transformer_gpt2(cfg.vocab, cfg.dim, cfg.layers, cfg.heads, cfg.ffn, cfg.seq)
+    mom = [[[torch.zeros_like(t) for t in grp] for grp in prm] for _ in range(2)]
+    wd_mask = [[not (t.dim() == 1 and bool((t == 0).all())) for t in grp] for grp in prm]
+    mask = torch.tril(torch.ones((cfg.seq, cfg.seq), dtype=torch.bool)).unsqueeze(0).expand(seqs, -1, -1).contiguous()
+    idx = torch.arange(cfg.seq).unsqueeze(0).expand(seqs, -1).contiguous()
+    times = []
+    for i in range(warmup + steps):
+        y = zipf_ids(cfg.vocab, (seqs, cfg.seq + 1), seed=1000 + i)
+        t0 = time.perf_counter()
+        grads, _ = lot.uncompiled_grad_loss(prm, y, mask, idx)
+        prm, mom = lot.adam_w_in_place(prm, grads, 6e-4, (0.9, 0.95), 1e-8, mom, i, weight_decay=0.1,
+                                       weight_decay_mask=wd_mask)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return {"value": seqs * cfg.seq / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "reference",
+            "sample": f"{seqs} sequence(s) of {cfg.seq} tokens per step (micro-batch {MICRO_BATCH}), {steps} timed "
+                      f"step(s) after {warmup} warm-up, the unmodified reference's torch.func path, float32, dropout off",
+            "sec_per_step": sec}
+
+
 def cpu_reference_step_rate(cfg, steps: int, warmup: int, seqs: int = 1) -> dict:
-    """tokens/s of fwd + bwd + clip + AdamW in float32 on the CPU for `seqs` sequences per step."""
+    """tokens/s of fwd + bwd + clip + AdamW in float32 on the CPU for `seqs` sequences per step: the unmodified
+    reference when PTJ_REFERENCE_DIR names a checkout of it, else the oracle port of the same algorithm."""
+    ref_dir = os.environ.get("PTJ_REFERENCE_DIR")
+    if ref_dir and os.path.isfile(os.path.join(ref_dir, "model_torch_func.py")):
+        return reference_checkout_step_rate(ref_dir, cfg, steps, warmup, seqs)
     from oracle import gpt2_oracle as orc
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     prm = orc.init_params(cfg.vocab, cfg.dim, cfg.layers, cfg.heads, cfg.ffn, cfg.seq, seed=0)
@@ -118,17 +164,30 @@ def cpu_reference_step_rate(cfg, steps: int, warmup: int, seqs: int = 1) -> dict
             times.append(dt)
     sec = sum(times) / len(times)
     return {"value": seqs * cfg.seq / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{seqs} sequence(s) of {cfg.seq} tokens per step (of the {MICRO_BATCH}-sequence micro-batch), "
+            "sample": f"{seqs} sequence(s) of {cfg.seq} tokens per step (micro-batch {MICRO_BATCH}), "
                       f"{steps} timed step(s) after {warmup} warm-up, float32, dropout off", "sec_per_step": sec}
+
+
+def cpu_arm(cfg, steps: int, warmup: int) -> dict:
+    """The CPU arm on the FULL micro-batch (what one GPU step processes); if the host cannot hold the float32
+    activations of all sequences at once (about 30 GB for GPT-2 small x 8), on as many sequences as fit."""
+    seqs = MICRO_BATCH
+    while True:
+        try:
+            return cpu_reference_step_rate(cfg, steps, warmup, seqs=seqs)
+        except (MemoryError, RuntimeError) as e:
+            if seqs == 1 or "memory" not in str(e).lower() and not isinstance(e, MemoryError):
+                raise
+            seqs = max(1, seqs // 2)
 
 
 def run_reference_arm(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 2))
     warm = 1 if args.warmup > 0 else 0
-    r = cpu_reference_step_rate(cfg, steps, warm, seqs=1)
+    r = cpu_arm(cfg, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": r["sec_per_step"] * 1e3, "higher_is_better": True,
@@ -136,8 +195,9 @@ def run_reference_arm(args, cfg):
         "config": workload_config(cfg, args.gpus), "gpu_launches": 0,
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "reference torch.func algorithm restated on the CPU (the Python reference cannot travel to this box); "
-                "requested steps are capped so the CPU run stays within minutes",
+        "note": ("the unmodified reference's torch.func path" if r["kind"] == "reference" else
+                 "reference torch.func algorithm restated on the CPU (no checkout of the reference was named in "
+                 "PTJ_REFERENCE_DIR)") + "; requested steps are capped so the CPU run stays within minutes",
     }
     print(json.dumps(line), flush=True)
 
@@ -183,6 +243,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # The gradient all-reduces overlap backward, whose persistent GEMM / attention kernels want every SM: keep the
+        # communication kernels to a few thread blocks (NVLink/NVSwitch bandwidth needs no more for ~0.5 GB per step).
+        os.environ.setdefault("NCCL_MAX_CTAS", "8")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ops = ptj.operators
@@ -222,9 +285,16 @@ def main():
     if rank == 0:
         sampler.start()
     launches0 = ptj._lib.launch_count()
+    if trainer.reducer is not None:
+        trainer.reducer.measure_exposed = True
     ms = timed(lambda i: losses.append(trainer.step(dev[i % n_batches])), args.steps)
     host_enqueue_ms = host_ms[0]
     launches = ptj._lib.launch_count() - launches0
+    exposed = None
+    if trainer.reducer is not None:
+        trainer.reducer.measure_exposed = False
+        ex = trainer.reducer.exposed_ms()
+        exposed = sum(ex) / max(1, len(ex))
     # the same steps once more with every GEMM launch bracketed by CUDA events (the roofline line). The events sit
     # between kernels of the stream, where they keep the next kernel's set-up from overlapping the previous
     # kernel's tail, so this pass is a little slower than the one above and is not the one reported as `value`.
@@ -239,8 +309,13 @@ def main():
     tokens_per_step = MICRO_BATCH * cfg.seq * world
     if rank == 0:
         peak_tf, peak_gbs, label = measured_peaks()
-        gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
-        gemm_flop = sum(f for _, _, f in gemm_events)
+        gemm_ms = sum(e[0].elapsed_time(e[1]) for e in gemm_events)
+        gemm_flop = sum(e[2] for e in gemm_events)
+        traffic, covered = 0.0, 0
+        for e in gemm_events:
+            hit = NCU_GEMM_TRAFFIC.get(e[3])
+            covered += hit is not None
+            traffic += hit[0] if hit is not None else e[4]
         achieved = gemm_flop / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         line = {
             "metric": METRIC, "value": tokens_per_step * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
@@ -257,11 +332,15 @@ def main():
                          "launches": len(gemm_events), "avg_launch_ms": gemm_ms / max(1, len(gemm_events)),
                          "gemm_share_of_step": gemm_ms / ms_prof if ms_prof > 0 else None,
                          "ms_per_step_with_events": ms_prof / args.steps,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         "traffic": traffic / max(1, len(gemm_events)),
+                         "traffic_source": f"{covered} of {len(gemm_events)} launches at shapes with an ncu capture "
+                                           f"(profiles/), the rest at their algorithmic bytes"},
             "final_loss": float(losses[-1][0].item()),
         }
+        if exposed is not None:
+            line["allreduce_exposed_ms"] = exposed
         if world == 1 and not args.no_cpu_baseline:
-            r = cpu_reference_step_rate(cfg, steps=2, warmup=1, seqs=1)
+            r = cpu_arm(cfg, steps=1, warmup=1)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -2,7 +2,7 @@
 //
 // bf16 inputs: persistent, warp-specialised tcgen05 kernel. One warp issues TMA tensor copies into a ring of
 // 128-byte-swizzled shared-memory stages, one thread issues tcgen05.mma (128 x BN x 16 per instruction, fp32
-// accumulators in tensor memory, two accumulator buffers), four warps drain finished accumulators with tcgen05.ld
+// accumulators in tensor memory, two accumulator buffers), eight warps drain finished accumulators with tcgen05.ld
 // and run the elementwise epilogue while the next tile is already being multiplied. Either operand may be K-major
 // or MN-major, which covers forward (x W^T), input-gradient (dy W) and weight-gradient (dy^T x) products without
 // any transposed copy. Work items = output tiles x K splits, walked by a static persistent schedule.
@@ -24,7 +24,14 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 8;     // a multiple of 4: warp w may only read tensor-memory lanes 32*(w%4)..
 constexpr int kWarpsPerQuarter = kEpilogueWarps / 4;   // these warps share a lane quarter and take its 32-column chunks in turn
-constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, the rest: epilogue
+constexpr int kFirstEpilogueWarp = 4;  // warps 0-3 form one warp group: warp 0 TMA, warp 1 MMA + TMEM owner, 2-3 idle
+constexpr int kGemmThreads = 32 * (kFirstEpilogueWarp + kEpilogueWarps);
+// Registers are re-split between the warp groups (setmaxnreg works on whole groups of four warps): the copy / MMA group
+// keeps 40 per thread, the two epilogue groups get 232. A block of 10 warps is allocated like 12 and held to 168
+// registers per thread, where the epilogue spilled a few values; with all but a sliver of the SM's L1 configured as
+// shared memory a spill is a round trip to L2 under the load of the operand copies, in the one part of the kernel that
+// has to keep up with the tensor pipe.
+constexpr int kRegsIssue = 40, kRegsEpilogue = 232;  // warp 0: TMA, warp 1: MMA + TMEM owner, the rest: epilogue
 constexpr int kSmemLimit = 227 * 1024;
 static_assert(kStripBytes % 512 == 0, "tile stores with the 64-byte swizzle need 512-byte aligned strips");
 constexpr int chunks_per_warp(int bn) { return (bn / 32 + kWarpsPerQuarter - 1) / kWarpsPerQuarter; }
@@ -226,6 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int tiles = p.num_m * p.num_n;
   const int total = tiles * p.split_k;
+  if (warp < kFirstEpilogueWarp) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
 
   if (warp == 0) {
     if (lane == 0) {
@@ -301,19 +309,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (ok) mma_commit(&tmem_full[buf]);
       }
     }
-  } else {
+  } else if (warp >= kFirstEpilogueWarp) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int sub = (warp - 2) >> 2;   // position among the warps that share this lane quarter
+    const int sub = (warp - kFirstEpilogueWarp) >> 2;   // position among the warps that share this lane quarter
     constexpr int kChunks = chunks_per_warp(BN);  // this warp takes chunks sub, sub + kWarpsPerQuarter, ...
     int it = 0;
     bool ok = true;
-    SidePrefetch sp{SIDE ? strips + (warp - 2) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - 2], 0u};
+    SidePrefetch sp{SIDE ? strips + (warp - kFirstEpilogueWarp) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - kFirstEpilogueWarp], 0u};
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
-      float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
+      float* wbias = bias_smem + (warp - kFirstEpilogueWarp) * (kChunks * 32);
       const bool bias_staged = p.ep.bias != nullptr && p.split_k == 1;
       if (bias_staged) {
         // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
@@ -349,7 +358,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
-        uint8_t* strip = strips + (warp - 2) * kStrip;
+        uint8_t* strip = strips + (warp - kFirstEpilogueWarp) * kStrip;
         const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
@@ -475,6 +484,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
   const int total = tiles * p.split_k;
   const int pair = static_cast<int>(blockIdx.x) >> 1, npairs = static_cast<int>(gridDim.x) >> 1;
+  if (warp < kFirstEpilogueWarp) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
 
   if (warp == 0) {
     if (lane == 0) {
@@ -551,21 +561,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (ok) mma_commit_pair(&tmem_full[buf], 3);
       }
     }
-  } else {
+  } else if (warp >= kFirstEpilogueWarp) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     const int quarter = warp & 3;
-    const int sub = (warp - 2) >> 2;
+    const int sub = (warp - kFirstEpilogueWarp) >> 2;
     constexpr int kChunks = chunks_per_warp(BN);
     const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     int it = 0;
     bool ok = true;
-    SidePrefetch sp{SIDE ? strips + (warp - 2) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - 2], 0u};
+    SidePrefetch sp{SIDE ? strips + (warp - kFirstEpilogueWarp) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - kFirstEpilogueWarp], 0u};
     for (int item = pair; item < total && ok; item += npairs, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
       const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
-      float* wbias = bias_smem + (warp - 2) * (kChunks * 32);
+      float* wbias = bias_smem + (warp - kFirstEpilogueWarp) * (kChunks * 32);
       const bool bias_staged = p.ep.bias != nullptr && p.split_k == 1;
       if (bias_staged) {
         // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
@@ -601,7 +612,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
-        uint8_t* strip = strips + (warp - 2) * kStrip;
+        uint8_t* strip = strips + (warp - kFirstEpilogueWarp) * kStrip;
         const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
         if (p.split_k > 1) {
           float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;

@@ -18,8 +18,8 @@ from . import _lib
 from ._lib import AttnShape, DropoutArgs, PTJ_BF16, PTJ_F32
 
 DROPOUT_RATE = 0.1
-# When set to a list, every tensor-core GEMM appends (start event, stop event, 2*M*N*K) to it: lets a benchmark
-# attribute device time and FLOPs to the GEMM kernel without a profiler.
+# When set to a list, every tensor-core GEMM appends (start event, stop event, 2*M*N*K, (M, N, K, a_kmajor, b_kmajor),
+# algorithmic bytes) to it: lets a benchmark attribute device time, FLOPs and bytes to the GEMM kernel without a profiler.
 GEMM_PROFILE = None
 
 
@@ -226,7 +226,9 @@ def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None
         "ptj_gemm")
     if prof is not None:
         e1.record()
-        prof.append((e0, e1, 2.0 * M * N * K))
+        side = M * N * out.element_size() * ((aux is not None) + (aux_out is not None) + (epilogue == _lib.EPI_ACCUM))
+        prof.append((e0, e1, 2.0 * M * N * K, (M, N, K, bool(a_kmajor), bool(b_kmajor)),
+                     float(2 * (M * K + N * K) + M * N * out.element_size() + side)))
     return out
 
 

@@ -102,11 +102,52 @@ def make_buckets(layout: FlatLayout, bucket_elems: int) -> List[Bucket]:
     return buckets
 
 
+class PeerLost(RuntimeError):
+    """A rank of the data-parallel group stopped reporting, or a collective did not finish within its time limit."""
+
+
+class PeerWatch:
+    """Host-side failure detection for the data-parallel group, through the process group's key-value store.
+
+    Every rank publishes the index of the step it is about to run; before launching the step's first collective a
+    rank checks that every peer has published that index too, waiting at most ``timeout_s``. A rank that raised,
+    exited or never joined is therefore noticed on the host, between steps, with nothing in flight on the GPU: the
+    survivors get a PeerLost instead of a collective that never returns. (The reference is a single process and has
+    nothing of the kind; a crash there loses everything since the last pickle.)"""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, prefix: str = "ptj/step"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+
+    def announce(self, step: int):
+        self.store.set(f"{self.prefix}/{self.rank}/{step}", b"1")
+
+    def check(self, step: int):
+        import datetime
+        keys = [f"{self.prefix}/{r}/{step}" for r in range(self.world) if r != self.rank]
+        try:
+            self.store.wait(keys, datetime.timedelta(seconds=self.timeout_s))
+        except Exception as e:  # the store raises its own timeout type
+            missing = []
+            for r, k in zip([r for r in range(self.world) if r != self.rank], keys):
+                try:
+                    self.store.wait([k], datetime.timedelta(milliseconds=1))
+                except Exception:
+                    missing.append(r)
+            raise PeerLost(f"rank(s) {missing or '?'} did not reach step {step} within {self.timeout_s:.1f} s: "
+                           f"not launching this step's collectives") from e
+        if step >= 2:  # keep the store small
+            try:
+                self.store.delete_key(f"{self.prefix}/{self.rank}/{step - 2}")
+            except Exception:
+                pass
+
+
 class GradReducer:
     """Bucketed sum-allreduce of a flat gradient buffer, overlapped with backward. Works with NCCL on CUDA tensors
     (side stream + events) and with gloo on CPU tensors (synchronous), which is how the host logic is tested."""
 
-    def __init__(self, flat_grads: torch.Tensor, layout: FlatLayout, bucket_mb: float, group=None):
+    def __init__(self, flat_grads: torch.Tensor, layout: FlatLayout, bucket_mb: float, group=None,
+                 wait_timeout_s: Optional[float] = None):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -116,6 +157,11 @@ class GradReducer:
         self.cuda = flat_grads.is_cuda
         self.comm_stream = torch.cuda.Stream() if self.cuda else None
         self.launched: List[int] = []
+        # host-side bound on waiting for a collective (None: the process group's own timeout is the only limit)
+        self.wait_timeout_s = wait_timeout_s
+        # (event before the wait, event after it) of recent steps, when exposure is being measured
+        self.measure_exposed = False
+        self.exposed_events: List[Tuple[object, object]] = []
         self.reset()
 
     def reset(self):
@@ -151,12 +197,38 @@ class GradReducer:
         missing = [b.names for b in self.buckets if b.pending != 0]
         if missing:
             raise RuntimeError(f"backward never produced the gradients of {missing[0]}: bucket cannot be reduced")
+        ev0 = ev1 = None
+        if self.cuda and self.measure_exposed:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         for idx in self.launched:
             w = self.buckets[idx].work
-            if w is not None:
-                w.wait()  # NCCL: makes the current stream wait for the collective; gloo: blocks the host
+            if w is None:
+                continue
+            try:
+                if self.cuda or self.wait_timeout_s is None:
+                    w.wait()  # NCCL: makes the current stream wait for the collective; gloo: blocks the host
+                else:
+                    import datetime
+                    if w.wait(datetime.timedelta(seconds=self.wait_timeout_s)) is False:
+                        raise RuntimeError("timed out")
+            except Exception as e:
+                raise PeerLost(f"all-reduce of gradient bucket {idx} ({self.buckets[idx].names[0]} ...) failed: {e}") from e
+            # (an asynchronous NCCL error - a peer died, a link fault - is raised by the process group's watchdog from
+            # wait() or from the next call on the group, within the group's timeout; it lands in the except above)
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+            if ev1 is not None:
+                ev1.record()
+                self.exposed_events.append((ev0, ev1))
+
+    def exposed_ms(self) -> List[float]:
+        """Per measured step, the time the compute stream spent waiting for gradient all-reduces that backward did not
+        hide (synchronises the device; clears the record)."""
+        torch.cuda.synchronize()
+        out = [a.elapsed_time(b) for a, b in self.exposed_events]
+        self.exposed_events = []
+        return out
 
 
 @dataclass
@@ -201,7 +273,7 @@ class Trainer:
     """fwd + bwd + gradient allreduce + clip + AdamW for one micro-batch per rank."""
 
     def __init__(self, cfg: GPT2Config, tc: TrainConfig = None, params=None, device="cuda", world: int = 1,
-                 rank: int = 0, group=None):
+                 rank: int = 0, group=None, peer_watch: Optional[PeerWatch] = None):
         from .optimizer import init_from_config
         self.cfg, self.tc = cfg, tc or TrainConfig()
         self.world, self.rank = world, rank
@@ -227,6 +299,7 @@ class Trainer:
         ns = _lib.lib().ptj_sumsq_scratch_floats(n)
         self.sumsq_scratch = torch.empty(ns, device=self.device, dtype=torch.float32)
         self.reducer = GradReducer(self.g, self.layout, self.tc.bucket_mb, group) if world > 1 else None
+        self.peer_watch = peer_watch  # optional: checked on the host before each step's collectives
         self.t = 0
         self.ids_dev = None
 
@@ -260,6 +333,9 @@ class Trainer:
         sorted_pos = torch.sort(y[:, :-1].reshape(-1), stable=True).indices.to(torch.int32)
         n_valid = None
         if self.reducer is not None:
+            if self.peer_watch is not None:  # every peer is alive and about to run this step: safe to communicate
+                self.peer_watch.announce(self.t)
+                self.peer_watch.check(self.t)
             self.reducer.reset()
             if self.tc.global_token_norm:
                 lab = y[:, 1:]  # the kernel's predicate: not padding and inside the vocabulary

@@ -144,6 +144,60 @@ def _worker(rank, world, port, case, ret):
         dist.destroy_process_group()
 
 
+def _leaver(rank, world, port, ret):
+    """Both ranks run two steps; rank 1 then leaves between steps (nothing in flight). Rank 0 must learn of it on the
+    host, before it launches the third step's collective, and within the watch's time limit."""
+    import time
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tr, cfg = pkg("trainer"), cfg_small()
+    lay = tr.FlatLayout.build(cfg)
+    store = dist.distributed_c10d._get_default_store()
+    watch = tr.PeerWatch(store, rank, world, timeout_s=1.5)
+    flat = torch.ones(lay.total)
+    red = tr.GradReducer(flat, lay, bucket_mb=0.004, wait_timeout_s=5.0)
+    launched_after_loss = False
+    try:
+        for step in range(3):
+            if rank == 1 and step == 2:
+                ret[rank] = "left"
+                return  # leaves between steps, without announcing step 2
+            watch.announce(step)
+            t0 = time.time()
+            try:
+                watch.check(step)
+            except tr.PeerLost as e:
+                ret[rank] = ("lost", step, time.time() - t0 < 10.0, "rank(s) [1]" in str(e), launched_after_loss)
+                return
+            red.reset()
+            red.mark_ready(lay.names)
+            launched_after_loss = launched_after_loss or step == 2
+            red.finish()
+        ret[rank] = "finished"
+    finally:
+        if rank == 1:
+            time.sleep(3.0)  # keep the store's peer alive while rank 0 times out on the missing key
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_leaving_between_steps_is_noticed_on_the_host():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    assert ret.get(1) == "left"
+    assert ret.get(0) == ("lost", 2, True, True, False), ret.get(0)
+
+
 @pytest.mark.parametrize("case", ["sum", "missing", "twice"])
 def test_bucketed_allreduce_two_ranks(case):
     ctx = mp.get_context("spawn")
