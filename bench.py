@@ -243,9 +243,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        # The gradient all-reduces overlap backward, whose persistent GEMM / attention kernels want every SM: keep the
-        # communication kernels to a few thread blocks (NVLink/NVSwitch bandwidth needs no more for ~0.5 GB per step).
-        os.environ.setdefault("NCCL_MAX_CTAS", "8")
+        # (NCCL's own choice of thread blocks per collective is kept: capping it to 8 made the last, exposed all-reduce
+        # 1.2 ms long on two GPUs, more than the persistent kernels gained from the SMs it freed)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ops = ptj.operators

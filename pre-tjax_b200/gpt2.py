@@ -123,11 +123,21 @@ class Weights:
         return Weights(cfg, t)
 
 
-def split_k_for(m_tiles: int, n_tiles: int, k_blocks: int) -> int:
-    """K split of a weight-gradient GEMM: aim for about two waves of work items over 148 SMs."""
-    tiles = max(1, m_tiles * n_tiles)
-    s = max(1, round(2 * 148 / tiles))
-    return int(min(s, 8, max(1, k_blocks // 4)))
+def split_k_for(M: int, N: int, K: int) -> int:
+    """K split of a weight-gradient GEMM (long K, small output): the number of equal parts of K that, dealt to the 74
+    thread-block pairs of the 256 x 256-tile kernel, finishes first. Cost of S parts = rounds needed for tiles * S work
+    items, each 1/S long, plus a charge per part for writing and re-reading its float32 partial tile (measured on
+    the GPT-2 small shapes: 2 parts for the 3072 x 768 FFN matrices, 5 for the QKV matrix, 8 for 768 x 768)."""
+    tiles = max(1, -(-M // 256) * -(-N // 256))
+    k_blocks = max(1, K // 64)
+    best, best_cost = 1, float("inf")
+    for s in range(1, 9):
+        if s > max(1, k_blocks // 4):
+            break
+        cost = -(-tiles * s // 74) / s + 0.015 * s
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 class Gpt2Step:
@@ -152,7 +162,7 @@ class Gpt2Step:
         M, N = out.shape[0], x2d.shape[1]
         split = 1
         if dy2d.dtype == torch.bfloat16:
-            split = split_k_for((M + 127) // 128, (N + 255) // 256, (T + 63) // 64)
+            split = split_k_for(M, N, T)
             need = split * M * N
             if split > 1 and (self._ws is None or self._ws.numel() < need):
                 self._ws = torch.empty(need, device=out.device, dtype=torch.float32)
