@@ -16,6 +16,11 @@
  * Masks come from Philox4x32-10 keyed by `seed`, counter = (element index / 8, stream id): each call serves eight
  * consecutive elements with 16 bits each and an element is dropped when its 16 bits are below floor(p * 65536).
  * Forward and backward regenerate identical masks from (seed, stream id, element index) without storing them.
+ *
+ * Every `seed` argument (including ptj_dropout_args.seed) is either the seed itself, a value below 2^63, or, with
+ * bit 63 set, the device address (in the low 63 bits) of a uint64_t that holds the seed when the kernel runs: see
+ * PTJ_SEED_AT. The second form is for callers that record the launches of a training step once (a CUDA graph) and
+ * replay them: they rewrite the seed words in device memory between replays instead of re-issuing the launches.
  */
 #ifndef PTJ_B200_H_
 #define PTJ_B200_H_
@@ -41,6 +46,9 @@ typedef enum {
 } ptj_status;
 
 enum { PTJ_F32 = 0, PTJ_BF16 = 1 };
+
+/* seed argument that makes a kernel read its seed from the device word at `dev_ptr` (8-byte aligned) */
+#define PTJ_SEED_AT(dev_ptr) ((uint64_t)(uintptr_t)(dev_ptr) | ((uint64_t)1 << 63))
 
 /* ---- library ---------------------------------------------------------------------------------------- */
 int ptj_version(void);

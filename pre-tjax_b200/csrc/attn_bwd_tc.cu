@@ -244,7 +244,6 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(b, count);
     }
     *abort_flag = 0;
-    for (int i = 0; i < 20; ++i) rk_s[i] = p.rk[i];
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
@@ -260,6 +259,10 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after_sync();
   grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem = *tmem_slot;
+  if (MODE == 1) {  // the kernel draws its own keep flags: round keys of the (possibly device-resident) seed
+    if (tid == 0) philox_round_keys(p.dr.seed, rk_s);
+    __syncthreads();
+  }
   constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);  // Q K^T and dO V^T
   constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);   // Pd^T dO and dS^T Q
   constexpr uint32_t idesc_q = idesc_bf16_f32(T, DH, false, true);  // dS K

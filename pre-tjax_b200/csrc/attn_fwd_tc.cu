@@ -32,7 +32,7 @@ constexpr int kOffP = kOffV + kVStages * kTileBytes;     // P[2 groups][2 sub-ti
 constexpr int kOffDump = kOffP + 4 * kTileBytes;          // float[64 + 3][128]: hand-over of one group's state
 constexpr int kOffBars = kOffDump + (DH + 3) * T * 4;
 constexpr int kNumBars = 4 + 2 * kKStages + 2 * kVStages + 2 * kSBufs + 6 + 2;
-constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 1024;
+constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 1024;
 constexpr int kTmemCols = 512;
 
 struct Sched {
@@ -103,6 +103,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* dump_free = dump_full + 1;      // one arrival per warp of the group that merges
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dump_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* rk_s = tmem_slot + 2;  // Philox round keys (MODE 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const AbortCtx ctx{abort_flag, p.fault};
@@ -132,6 +133,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after_sync();
   grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem = *tmem_slot;
+  if (MODE == 1) {  // the kernel draws its own keep flags: round keys of the (possibly device-resident) seed
+    if (tid == 0) philox_round_keys(p.dr.seed, rk_s);
+    __syncthreads();
+  }
 
   // the copy / MMA warps hand most of their registers to the softmax warps (whole groups of four warps switch together)
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -297,7 +302,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint64_t call0 = ((static_cast<uint64_t>(c.bh) * p.S + q_row) * p.S + static_cast<uint64_t>(c.j) * T) >> 3;
         if (MODE == 1) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + q, p.dr.stream_id, rw[0][q]);
+          for (int q = 0; q < 4; ++q) philox_rk(rk_s, call0 + q, p.dr.stream_id, rw[0][q]);
         }
         uint4 kb = make_uint4(0u, 0u, 0u, 0u);
         if (MODE == 2)
@@ -367,7 +372,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int cc = 0; cc < 4; ++cc) {
           if (MODE == 1 && cc + 1 < 4) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) philox_rk(p.rk, call0 + (cc + 1) * 4 + q, p.dr.stream_id, rw[(cc + 1) & 1][q]);
+            for (int q = 0; q < 4; ++q) philox_rk(rk_s, call0 + (cc + 1) * 4 + q, p.dr.stream_id, rw[(cc + 1) & 1][q]);
           }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {  // exp2(-inf) = 0 takes care of the masked columns
@@ -500,12 +505,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // Keep flags of the attention-probability dropout for one call, computed once and shared by the forward and the
 // backward kernel: word c of the uint4 at ((bh * ntri + qt (qt + 1) / 2 + kt) * 128 + row) holds the flags of
 // columns 32 c .. 32 c + 31 of row `row` of tile (qt, kt); ntri = nq (nq + 1) / 2. One thread per word.
-struct RoundKeys {
-  uint32_t k[20];
-};
 __global__ void __launch_bounds__(512)
-attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, const RoundKeys rk, int S, int nq) {
+attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, int S, int nq) {
   grid_dep_sync();
+  __shared__ uint32_t rk_s[20];
+  if (threadIdx.x == 0) philox_round_keys(dr.seed, rk_s);
+  __syncthreads();
+  uint32_t rk[20];  // in registers: the kernel is bound by its integer instructions, keys as plain operands
+#pragma unroll
+  for (int i = 0; i < 20; ++i) rk[i] = rk_s[i];
   // one block per tile (its position is decoded once), one thread per word: 128 rows x 4 words
   const int ntri = nq * (nq + 1) / 2;
   const int64_t tile = blockIdx.x;  // bh * ntri + tri
@@ -525,7 +533,7 @@ attn_keep_bits_kernel(uint32_t* __restrict__ bits, const AttnDropout dr, const R
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     uint32_t w[4];
-    philox_rk(rk.k, (idx0 >> 3) + q, dr.stream_id, w);
+    philox_rk(rk, (idx0 >> 3) + q, dr.stream_id, w);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       word |= ((w[e] << 16) >= thr_hi ? 1u : 0u) << (8 * q + 2 * e);
@@ -544,12 +552,7 @@ size_t attn_keep_bits_bytes(const ptj_attn_shape& sh) {
 
 int attn_keep_bits_tc(uint32_t* bits, const ptj_attn_shape& sh, const AttnDropout& dr, cudaStream_t st) {
   const int64_t tiles = static_cast<int64_t>(attn_keep_bits_bytes(sh) / 2048);
-  RoundKeys rk;
-  for (int r = 0; r < 10; ++r) {
-    rk.k[2 * r] = static_cast<uint32_t>(dr.seed) + static_cast<uint32_t>(r) * 0x9E3779B9u;
-    rk.k[2 * r + 1] = static_cast<uint32_t>(dr.seed >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
-  }
-  launch_k(attn_keep_bits_kernel, static_cast<unsigned>(tiles), 512, 0, st, bits, dr, rk, static_cast<int>(sh.seq),
+  launch_k(attn_keep_bits_kernel, static_cast<unsigned>(tiles), 512, 0, st, bits, dr, static_cast<int>(sh.seq),
                                                                       static_cast<int>(sh.seq / T));
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;

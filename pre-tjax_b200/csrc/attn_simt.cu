@@ -17,6 +17,7 @@ attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
                      float* __restrict__ row_max, float* __restrict__ row_sum, const int32_t* __restrict__ kstart,
                      const ptj_attn_shape sh, float scale, AttnDropout dr) {
   grid_dep_sync();
+  dr.seed = resolve_seed(dr.seed);
   __shared__ float qs[kWarpsPerBlock][kMaxD];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int64_t S = sh.seq, D = sh.d_head;
@@ -86,6 +87,7 @@ attn_bwd_simt_kernel(const T* __restrict__ d_o, const T* __restrict__ q, const T
                      const int32_t* __restrict__ kstart, const ptj_attn_shape sh, const ptj_attn_shape dsh, float scale,
                      AttnDropout dr) {
   grid_dep_sync();
+  dr.seed = resolve_seed(dr.seed);
   __shared__ float xs[kWarpsPerBlock][kMaxD];  // MODE 0: q row;  MODE 1: k row
   __shared__ float ys[kWarpsPerBlock][kMaxD];  // MODE 0: dO row; MODE 1: v row
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;

@@ -28,14 +28,22 @@ struct AttnParams {
   float scale_log2;  // log2(e) / sqrt(d_head)
   float scale;       // 1 / sqrt(d_head)
   AttnDropout dr;
-  uint32_t rk[20];   // Philox round keys of dr.seed (round r uses rk[2r], rk[2r+1]): the same for every call
   const uint4* keep_bits;  // optional precomputed keep flags, one uint4 per (batch*head, tile, row): see attn_keep_bits_tc
   const int32_t* kstart;   // optional [batch, seq]: first key a query row may attend to (document start); NULL = 0
   unsigned int* fault;
 };
 
-// philox4x32_10 of common.cuh with the key schedule taken from a table (kernel parameters = constant operands)
-__device__ __forceinline__ void philox_rk(const uint32_t (&rk)[20], uint64_t ctr, uint32_t stream_id, uint32_t (&out)[4]) {
+// Philox round keys of a seed (round r uses rk[2r], rk[2r+1]): the same for every call of a kernel, so one thread
+// writes them to shared memory at start-up, after resolving the seed argument (it may be the address of the seed).
+__device__ __forceinline__ void philox_round_keys(uint64_t seed_arg, uint32_t* rk) {
+  const uint64_t seed = resolve_seed(seed_arg);
+  for (int r = 0; r < 10; ++r) {
+    rk[2 * r] = static_cast<uint32_t>(seed) + static_cast<uint32_t>(r) * 0x9E3779B9u;
+    rk[2 * r + 1] = static_cast<uint32_t>(seed >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
+  }
+}
+// philox4x32_10 of common.cuh with the key schedule taken from a table
+__device__ __forceinline__ void philox_rk(const uint32_t* rk, uint64_t ctr, uint32_t stream_id, uint32_t (&out)[4]) {
   uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32), c2 = stream_id, c3 = 0x5054'4a31u;
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
@@ -197,10 +205,6 @@ inline AttnParams make_params(const ptj_attn_shape& sh, const AttnDropout& dr) {
   p.scale = 1.f / sqrtf(static_cast<float>(DH));
   p.scale_log2 = p.scale * kLog2e;
   p.dr = dr;
-  for (int r = 0; r < 10; ++r) {
-    p.rk[2 * r] = static_cast<uint32_t>(dr.seed) + static_cast<uint32_t>(r) * 0x9E3779B9u;
-    p.rk[2 * r + 1] = static_cast<uint32_t>(dr.seed >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
-  }
   p.fault = tc::fault_word();
   return p;
 }

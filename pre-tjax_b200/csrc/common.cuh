@@ -157,6 +157,14 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint64_t seed, uint64_
 // keyed by the site's seed and stream id, yields four 32-bit words = eight 16-bit lanes; element e = idx % 8 uses the
 // low half of word e / 2 when e is even and the high half when odd. The element is DROPPED when its lane is below
 // floor(p * 65536). Forward and backward regenerate the same bits; nothing is stored.
+// A `seed` argument of any entry point is either the 63-bit seed itself or, with bit 63 set, the DEVICE ADDRESS (low 63
+// bits) of a uint64 that holds it. The second form lets a caller replay the same recorded launches (a CUDA graph of a
+// whole training step) with fresh masks: it rewrites the words in device memory between replays. Kernels resolve the
+// argument once, before their first use of it.
+constexpr uint64_t kSeedIsPointer = 1ull << 63;
+__device__ __forceinline__ uint64_t resolve_seed(uint64_t s) {
+  return (s & kSeedIsPointer) ? __ldg(reinterpret_cast<const uint64_t*>(s & ~kSeedIsPointer)) : s;
+}
 __host__ __device__ __forceinline__ uint32_t dropout_threshold16(float p) {
   double t = static_cast<double>(p) * 65536.0;
   if (t <= 0.0) return 0u;

@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kEwThreads)
 dropout_kernel(const T* __restrict__ x, const T* __restrict__ resid, T* __restrict__ y, int64_t n, bool vec,
                uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
+  seed = resolve_seed(seed);
   constexpr int V = Elem<T>::kVec;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;

@@ -13,6 +13,7 @@ embed_fwd_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ w_emb, 
                  T* __restrict__ y, int64_t tokens, int64_t seq, int dim, int64_t vocab, float scale, uint32_t thr,
                  float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
+  seed = resolve_seed(seed);
   const int64_t total = tokens * dim;
   for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x * 4) {
@@ -41,6 +42,7 @@ __global__ void __launch_bounds__(256)
 pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t batch, int64_t seq, int dim,
                uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
+  seed = resolve_seed(seed);
   const int64_t total = seq * dim;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -65,6 +67,7 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
                  float* __restrict__ d_w_emb, int accumulate, int64_t tokens, int dim, int64_t vocab, float scale,
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
+  seed = resolve_seed(seed);
   extern __shared__ float part[];  // [8][dim]
   __shared__ int32_t pos_s[256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

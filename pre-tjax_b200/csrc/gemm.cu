@@ -123,7 +123,7 @@ template <typename TOut, bool SIDE>
 __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t* strip, int64_t row0, int64_t row,
                                               int64_t n0, float (&acc)[32], int lane, const float* bias_s,
                                               const StoreMaps* maps, SidePrefetch& sp, const AbortCtx& ctx,
-                                              int64_t next_n0, bool& ok) {
+                                              int64_t next_n0, bool& ok, uint64_t seed) {
   // (warp-uniform) only full-width blocks: at a ragged right edge the tile store was seen to write the whole 16-byte
   // piece that holds the last valid column, i.e. up to seven padding columns
   const bool use_tma = maps != nullptr && sizeof(TOut) == 2 && row0 < ep.M && n0 + 32 <= ep.N;
@@ -167,7 +167,7 @@ __device__ __forceinline__ void tile_epilogue(const EpilogueParams& ep, uint8_t*
     if (staged) warp_load_block<TOut>(strip, static_cast<const TOut*>(sptr), ep.ldc, row0, n0, ep.M, side, lane);
     else if (inside) load_row<TOut, 32>(static_cast<const TOut*>(sptr) + row * ep.ldc, n0, ep.N, false, side);
   }
-  if (inside) epilogue_post<TOut, 32>(ep, row, n0, acc, side);
+  if (inside) epilogue_post<TOut, 32>(ep, row, n0, acc, side, seed);
   if (use_tma) {
     if (want_pre) {
       if (lane == 0) bulk_wait_read_all();
@@ -316,6 +316,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     constexpr int kChunks = chunks_per_warp(BN);  // this warp takes chunks sub, sub + kWarpsPerQuarter, ...
     int it = 0;
     bool ok = true;
+    const uint64_t seed = p.ep.mode == PTJ_EPI_DROPOUT_RESID ? resolve_seed(p.ep.seed) : 0ull;
     SidePrefetch sp{SIDE ? strips + (warp - kFirstEpilogueWarp) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - kFirstEpilogueWarp], 0u};
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
@@ -373,10 +374,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int ncol = (sub + (chunk + 1) * kWarpsPerQuarter) * 32;  // this warp's next block of the tile, if any
           const int64_t next_n0 = ncol < BN ? static_cast<int64_t>(n_blk) * BN + ncol : -1;
           tile_epilogue<__nv_bfloat16, SIDE>(p.ep, strip, row0, row, n0, acc, lane, bias_c,
-                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok);
+                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok, seed);
           if (!ok) break;
         } else {
-          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok);
+          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok, seed);
         }
       }
       tc_fence_before_sync();
@@ -570,6 +571,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t leader_empty1 = mapa_shared(smem_u32(&tmem_empty[1]), 0);
     int it = 0;
     bool ok = true;
+    const uint64_t seed = p.ep.mode == PTJ_EPI_DROPOUT_RESID ? resolve_seed(p.ep.seed) : 0ull;
     SidePrefetch sp{SIDE ? strips + (warp - kFirstEpilogueWarp) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - kFirstEpilogueWarp], 0u};
     for (int item = pair; item < total && ok; item += npairs, ++it) {
       const int split = item / tiles, tile = item - split * tiles;
@@ -627,10 +629,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const int ncol = (sub + (chunk + 1) * kWarpsPerQuarter) * 32;  // this warp's next block of the tile, if any
           const int64_t next_n0 = ncol < BN ? static_cast<int64_t>(n_blk) * BN + ncol : -1;
           tile_epilogue<__nv_bfloat16, SIDE>(p.ep, strip, row0, row, n0, acc, lane, bias_c,
-                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok);
+                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok, seed);
           if (!ok) break;
         } else {
-          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok);
+          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok, seed);
         }
       }
       tc_fence_before_sync();
@@ -731,7 +733,9 @@ gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, int64
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) epilogue_row_segment<TOut, 8>(ep, m0 + ty * 4 + i, n0 + tx * 8, acc[i]);
+  const uint64_t seed = ep.mode == PTJ_EPI_DROPOUT_RESID ? resolve_seed(ep.seed) : 0ull;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) epilogue_row_segment<TOut, 8>(ep, m0 + ty * 4 + i, n0 + tx * 8, acc[i], seed);
 }
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is needed once per kernel instantiation and device, not per launch.

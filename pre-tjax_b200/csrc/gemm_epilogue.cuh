@@ -108,9 +108,10 @@ __device__ __forceinline__ const void* epilogue_side_input(const EpilogueParams&
 }
 
 // a[] = the side input's values at (m, n0 .. n0+CNT-1) (ignored when the mode has no side input)
+// seed: ep.seed resolved by the caller (resolve_seed), once per thread
 template <typename TOut, int CNT>
 __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t m, int64_t n0, float (&acc)[CNT],
-                                              const float (&a)[CNT]) {
+                                              const float (&a)[CNT], uint64_t seed) {
   constexpr bool kFast = sizeof(TOut) == 2;  // bf16 output: hardware tanh is exact enough after rounding
   if (ep.mode == PTJ_EPI_GELU) {
     if (kFast) {
@@ -143,28 +144,29 @@ __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t 
     } else if ((base & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < CNT; j += 8) {
-        const uint32_t keep = dropout_keep_bits8(ep.seed, ep.stream_id, (base + j) >> 3, ep.drop_thr);
+        const uint32_t keep = dropout_keep_bits8(seed, ep.stream_id, (base + j) >> 3, ep.drop_thr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[j + e] = a[j + e] + (((keep >> e) & 1u) ? acc[j + e] : 0.f);
       }
     } else {
 #pragma unroll
       for (int j = 0; j < CNT; ++j)
-        acc[j] = a[j] + (dropout_keep(ep.seed, ep.stream_id, base + j, ep.drop_thr) ? acc[j] : 0.f);
+        acc[j] = a[j] + (dropout_keep(seed, ep.stream_id, base + j, ep.drop_thr) ? acc[j] : 0.f);
     }
   }
 }
 
 // both phases + per-thread stores (used where one thread owns a short row segment)
 template <typename TOut, int CNT>
-__device__ __forceinline__ void epilogue_row_segment(const EpilogueParams& ep, int64_t m, int64_t n0, float (&acc)[CNT]) {
+__device__ __forceinline__ void epilogue_row_segment(const EpilogueParams& ep, int64_t m, int64_t n0, float (&acc)[CNT],
+                                                     uint64_t seed) {
   if (!epilogue_pre<TOut, CNT>(ep, m, n0, acc)) return;
   const bool full = ep.vec_ok && n0 + CNT <= ep.N;
   if (ep.mode == PTJ_EPI_GELU && ep.aux_out != nullptr)
     store_row<TOut, CNT>(static_cast<TOut*>(ep.aux_out) + m * ep.ldc, n0, ep.N, full, acc);
   float a[CNT];
   if (const void* side = epilogue_side_input(ep)) load_row<TOut, CNT>(static_cast<const TOut*>(side) + m * ep.ldc, n0, ep.N, full, a);
-  epilogue_post<TOut, CNT>(ep, m, n0, acc, a);
+  epilogue_post<TOut, CNT>(ep, m, n0, acc, a, seed);
   store_row<TOut, CNT>(static_cast<TOut*>(ep.c) + m * ep.ldc, n0, ep.N, full, acc);
 }
 

@@ -140,6 +140,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = dim / V;
   const bool want_cs = partial != nullptr && mk.colsum != nullptr;
+  const uint64_t mask_seed = (mk.out != nullptr && mk.train && mk.thr != 0u) ? resolve_seed(mk.seed) : 0ull;
   const int nq = want_cs ? 3 : 2;
   float* acc_g = sm_acc + warp * nq * kSlots;
   float* acc_b = acc_g + kSlots;
@@ -250,7 +251,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
             const uint64_t idx = static_cast<uint64_t>(row) * dim + static_cast<uint64_t>(vi) * V;
             uint32_t keep = 0xffu;
             if (mk.train && mk.thr != 0u)
-              keep = dropout_keep_bits8(mk.seed, mk.stream_id, idx >> 3, mk.thr) >> (idx & 7);
+              keep = dropout_keep_bits8(mask_seed, mk.stream_id, idx >> 3, mk.thr) >> (idx & 7);
 #pragma unroll
             for (int j = 0; j < V; ++j) {
               const float r = Elem<T>::round(o[j]);

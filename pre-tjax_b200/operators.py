@@ -51,8 +51,28 @@ def _ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+SEED_IS_POINTER = 1 << 63
+
+
+class SeedRef(int):
+    """A seed argument that is the address of a device word (bit 63 set), not a seed value."""
+
+
+def seed_at(words: torch.Tensor, index: int = 0) -> SeedRef:
+    """A seed argument that makes the kernels read the seed from element `index` of a CUDA int64 tensor when they run
+    (PTJ_SEED_AT of the C header): lets a recorded step (CUDA graph) be replayed with fresh dropout masks. The tensor
+    must stay alive, and hold its final value, whenever a kernel that was given the reference runs."""
+    assert words.is_cuda and words.dtype == torch.int64 and 0 <= index < words.numel()
+    return SeedRef((words.data_ptr() + 8 * index) | SEED_IS_POINTER)
+
+
 def _seed(p_gen_aux) -> int:
-    return 0 if p_gen_aux is None else int(p_gen_aux) & 0xFFFFFFFFFFFFFFFF
+    """Immediate seeds are 63-bit values: bit 63 marks a device-resident seed (seed_at) and is cleared otherwise."""
+    if p_gen_aux is None:
+        return 0
+    if isinstance(p_gen_aux, SeedRef):
+        return int(p_gen_aux)
+    return int(p_gen_aux) & (SEED_IS_POINTER - 1)
 
 
 # ---- LayerNorm ------------------------------------------------------------------------------------------------------

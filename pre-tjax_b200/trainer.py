@@ -246,6 +246,10 @@ class TrainConfig:
     seed: int = 0
     global_token_norm: bool = False
     compute_dtype: torch.dtype = torch.bfloat16
+    # Record forward + backward of a step once as a CUDA graph and replay it (single GPU, plain causal batches): the
+    # host then issues one graph launch instead of some 360 kernel launches per step. Dropout seeds live in device
+    # memory and are rewritten before every replay, so the masks change from step to step exactly as without the graph.
+    cuda_graph: bool = False
 
     @staticmethod
     def benchmark_recipe(**overrides) -> "TrainConfig":
@@ -265,7 +269,7 @@ def step_seeds(base_seed: int, step: int, rank: int, n: int) -> List[int]:
         z = (base_seed * 0x9E3779B97F4A7C15 + step * 0xBF58476D1CE4E5B9 + rank * 0x94D049BB133111EB + site + 1) & (2**64 - 1)
         z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & (2**64 - 1)
         z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & (2**64 - 1)
-        out.append(z ^ (z >> 31))
+        out.append((z ^ (z >> 31)) & (2**63 - 1))  # 63 bits: bit 63 of a seed argument marks a device-resident seed
     return out
 
 
@@ -302,6 +306,12 @@ class Trainer:
         self.peer_watch = peer_watch  # optional: checked on the host before each step's collectives
         self.t = 0
         self.ids_dev = None
+        self.use_graph = bool(self.tc.cuda_graph) and world == 1 and self.device.type == "cuda"
+        self._graph = None           # (batch shape, torch.cuda.CUDAGraph, static ids, static stats)
+        self._seed_words = None      # int64[1 + 3 L] on the device: this step's dropout seeds, read by the kernels
+        self._seed_host = None
+        self.graph_launches = 0      # kernels recorded in the graph (one replay launches that many)
+        self.graph_replays = 0
 
     # weights the kernels read: bf16 shadow for matrices, fp32 master for vectors
     def _refresh_shadow(self):
@@ -324,6 +334,8 @@ class Trainer:
         mean loss, accuracy, fraction of non-padding labels (of this rank's micro-batch).
         row_kstart: optional int32 [B, S] on the device for packed / padded batches (operators.row_kstart_from_lengths
         or row_kstart_from_mask): position i attends keys [row_kstart[b, i], i]; None = plain causal."""
+        if self.use_graph and train and row_kstart is None:
+            return self._graph_step(y, lr)
         if not y.is_cuda:
             if self.ids_dev is None or self.ids_dev.shape != y.shape:
                 self.ids_dev = torch.empty(y.shape, device=self.device, dtype=torch.int32)
@@ -347,6 +359,46 @@ class Trainer:
                                            sorted_pos=sorted_pos, row_kstart=row_kstart)
         if self.reducer is not None:
             self.reducer.finish()
+        self.apply_update(lr if lr is not None else self.tc.lr)
+        return stats
+
+    def _graph_step(self, y: torch.Tensor, lr: Optional[float]) -> torch.Tensor:
+        """The same step with forward + backward replayed from a CUDA graph. Per step the host copies the token ids
+        and the step's dropout seeds into fixed device buffers, launches the graph, and runs clip + AdamW (whose
+        step count and learning rate change every step) as ordinary launches."""
+        from . import operators as ops
+        n_seeds = 1 + 3 * self.cfg.layers
+        if self._seed_words is None:
+            self._seed_words = torch.zeros(n_seeds, device=self.device, dtype=torch.int64)
+            self._seed_host = torch.zeros(n_seeds, dtype=torch.int64).pin_memory()
+        self._seed_host.copy_(torch.tensor(step_seeds(self.tc.seed, self.t, self.rank, n_seeds), dtype=torch.int64))
+        self._seed_words.copy_(self._seed_host, non_blocking=True)
+        if self._graph is None or self._graph[0] != tuple(y.shape):
+            ids = torch.empty(tuple(y.shape), device=self.device, dtype=torch.int32)
+            ids.copy_(y, non_blocking=True)
+            refs = [ops.seed_at(self._seed_words, i) for i in range(n_seeds)]
+
+            def fwd_bwd():
+                sorted_pos = torch.sort(ids[:, :-1].reshape(-1), stable=True).indices.to(torch.int32)
+                return self.engine.loss_and_grads(self.w, self.gv, ids, True, refs, sorted_pos=sorted_pos)
+
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):  # warm-up: sizes the allocator's pools and every lazily initialised cache
+                for _ in range(2):
+                    fwd_bwd()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = _lib.launch_count()
+            with torch.cuda.graph(graph):
+                stats = fwd_bwd()
+            self.graph_launches = _lib.launch_count() - before
+            self._graph = (tuple(y.shape), graph, ids, stats)
+        _, graph, ids, stats = self._graph
+        ids.copy_(y, non_blocking=True)
+        graph.replay()
+        self.graph_replays += 1
         self.apply_update(lr if lr is not None else self.tc.lr)
         return stats
 

@@ -87,14 +87,16 @@ def test_step_seeds_are_distinct():
     assert len(set(a)) == 37
     assert set(a).isdisjoint(tr.step_seeds(0, 1, 0, 37)) and set(a).isdisjoint(tr.step_seeds(0, 0, 1, 37))
     assert a == tr.step_seeds(0, 0, 0, 37)
-    assert all(0 <= s < 2 ** 64 for s in a)
+    assert all(0 <= s < 2 ** 63 for s in a)  # bit 63 of a seed argument marks a device-resident seed
 
 
 def test_split_k_heuristic():
-    f = pkg("gpt2").split_k_for
-    assert f(393, 3, 128) == 1      # LM-head weight gradient: plenty of tiles already
-    assert 2 <= f(6, 3, 128) <= 8   # 768 x 768 weight gradient: needs a K split to fill 148 SMs
-    assert f(1, 1, 2) == 1
+    f = pkg("gpt2").split_k_for     # (M, N, K) of the weight-gradient product, K = tokens
+    assert f(50257, 768, 8192) == 1      # LM-head weight gradient: plenty of tiles already
+    assert f(768, 768, 8192) == 8        # 9 tiles of 256 x 256: needs a K split to fill the 74 thread-block pairs
+    assert f(3072, 768, 8192) == 2       # 36 tiles: two parts make one round of 72 work items
+    assert f(2304, 768, 8192) == 5
+    assert f(128, 128, 128) == 1         # nothing to split
 
 
 # ---- two gloo ranks -------------------------------------------------------------------------------------------------------

@@ -202,3 +202,36 @@ def test_trainer_single_step_matches_oracle_update():
     mv = t.layout.views(t.m)
     for (name, _), b in zip(cfg.param_shapes(), flat(mom[0])):
         assert rel_err(mv[name], b) < 2e-4, name
+
+
+def test_device_resident_seeds_and_graph_replay_match_direct_launches():
+    """(1) A seed passed as the address of a device word gives the mask of the value stored there. (2) A trainer that
+    replays forward + backward from a CUDA graph, rewriting its dropout seeds in device memory before every replay,
+    stays bit-identical to a trainer that launches every kernel directly, dropout 0.1 on the tensor-core path."""
+    ops, gpt2, tr = pkg("operators"), pkg("gpt2"), pkg("trainer")
+    n, p, seed = 4096, 0.25, 0x1234_5678_9ABC
+    x = torch.randn(n, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    words = torch.tensor([7, seed], dtype=torch.int64, device="cuda")
+    a = ops.dropout(x, True, seed, p=p)
+    b = ops.dropout(x, True, ops.seed_at(words, 1), p=p)
+    assert torch.equal(a, b)
+    words[1] = 99
+    assert not torch.equal(a, ops.dropout(x, True, ops.seed_at(words, 1), p=p))
+
+    cfg = gpt2.GPT2Config(vocab=512, dim=128, layers=2, heads=2, ffn=256, seq=128, dropout=0.1)
+    prm = orc.init_params(512, 128, 2, 2, 256, 128, seed=3)
+    g = torch.Generator().manual_seed(4)
+    batches = [torch.randint(1, 512, (4, 129), generator=g, dtype=torch.int32) for _ in range(5)]
+    runs = []
+    for use_graph in (False, True):
+        tc = tr.TrainConfig.benchmark_recipe(lr=1e-3, seed=11, cuda_graph=use_graph)
+        t = tr.Trainer(cfg, tc, params=prm, device="cuda")
+        losses = [float(t.step(y)[0]) for y in batches]
+        torch.cuda.synchronize()
+        runs.append((losses, t.p.clone(), t.m.clone()))
+        if use_graph:
+            assert t.graph_replays == len(batches) and t.graph_launches > 50
+    assert runs[0][0] == runs[1][0], (runs[0][0], runs[1][0])
+    assert torch.equal(runs[0][1], runs[1][1]) and torch.equal(runs[0][2], runs[1][2])
+    assert len(set(runs[0][0])) == len(batches)
+    assert pkg("operators").last_kernel_fault() == 0
