@@ -246,10 +246,11 @@ class TrainConfig:
     seed: int = 0
     global_token_norm: bool = False
     compute_dtype: torch.dtype = torch.bfloat16
-    # Record forward + backward of a step (with the bucketed gradient all-reduces, when data-parallel) once as a CUDA
-    # graph and replay it (plain causal batches): the host then issues one graph launch instead of some 360 kernel
-    # launches per step. Dropout seeds live in device memory and are rewritten before every replay, so the masks
-    # change from step to step exactly as without the graph.
+    # Record forward + backward of a step once as a CUDA graph and replay it (single process, plain causal batches): the
+    # host then issues one graph launch instead of some 360 kernel launches per step. Dropout seeds live in device
+    # memory and are rewritten before every replay, so the masks change from step to step exactly as without the
+    # graph. Data-parallel steps keep ordinary launches: recording the bucketed NCCL all-reduces together with the
+    # kernels left both ranks of a two-GPU run waiting on each other, so that combination is not offered.
     cuda_graph: bool = False
 
     @staticmethod
@@ -307,7 +308,7 @@ class Trainer:
         self.peer_watch = peer_watch  # optional: checked on the host before each step's collectives
         self.t = 0
         self.ids_dev = None
-        self.use_graph = bool(self.tc.cuda_graph) and self.device.type == "cuda" and not self.tc.global_token_norm
+        self.use_graph = bool(self.tc.cuda_graph) and world == 1 and self.device.type == "cuda"
         self._graph = None           # (batch shape, torch.cuda.CUDAGraph, static ids, static stats)
         self._seed_words = None      # int64[1 + 3 L] on the device: this step's dropout seeds, read by the kernels
         self._seed_host = None
@@ -380,18 +381,8 @@ class Trainer:
             refs = [ops.seed_at(self._seed_words, i) for i in range(n_seeds)]
 
             def fwd_bwd():
-                # data-parallel: the host-side bucket bookkeeping runs while recording; the all-reduces it launches on
-                # the side stream, and the waits for them, become nodes of the graph
                 sorted_pos = torch.sort(ids[:, :-1].reshape(-1), stable=True).indices.to(torch.int32)
-                on_ready = None
-                if self.reducer is not None:
-                    self.reducer.reset()
-                    on_ready = self.reducer.mark_ready
-                out = self.engine.loss_and_grads(self.w, self.gv, ids, True, refs, sorted_pos=sorted_pos,
-                                                 on_ready=on_ready)
-                if self.reducer is not None:
-                    self.reducer.finish()
-                return out
+                return self.engine.loss_and_grads(self.w, self.gv, ids, True, refs, sorted_pos=sorted_pos)
 
             side = torch.cuda.Stream(self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
@@ -408,9 +399,6 @@ class Trainer:
             self._graph = (tuple(y.shape), graph, ids, stats)
         _, graph, ids, stats = self._graph
         ids.copy_(y, non_blocking=True)
-        if self.reducer is not None and self.peer_watch is not None:  # peers alive and at this step: safe to communicate
-            self.peer_watch.announce(self.t)
-            self.peer_watch.check(self.t)
         graph.replay()
         self.graph_replays += 1
         self.apply_update(lr if lr is not None else self.tc.lr)

@@ -30,7 +30,7 @@ def _cfg():
     return pkg("gpt2").GPT2Config(vocab=512, dim=128, layers=2, heads=2, ffn=256, seq=128, dropout=0.0)
 
 
-def _worker(rank, world, port, ret, use_graph):
+def _worker(rank, world, port, ret):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -38,8 +38,7 @@ def _worker(rank, world, port, ret, use_graph):
     try:
         ptj = pkg()
         cfg = _cfg()
-        t = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=5, cuda_graph=use_graph), device=f"cuda:{rank}", world=world,
-                        rank=rank)
+        t = ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=5), device=f"cuda:{rank}", world=world, rank=rank)
         losses = []
         for ys in _batches(cfg, 3, world):
             losses.append(float(t.step(ys[rank])[0]))
@@ -50,18 +49,20 @@ def _worker(rank, world, port, ret, use_graph):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_two_ranks_agree_and_match_the_averaged_single_gpu_step(use_graph):
-    """use_graph: forward + backward AND the bucketed all-reduces are replayed from one CUDA graph per rank."""
+def test_two_ranks_agree_and_match_the_averaged_single_gpu_step():
     world = 2
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, ret, use_graph)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(180)
+    for p in procs:  # a rank that is still running has lost its peer or hung: end it, do not wait for it
+        if p.is_alive():
+            p.kill()
+            p.join(10)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     (p0, l0, f0), (p1, l1, f1) = ret[0], ret[1]
     assert f0 == 0 and f1 == 0
