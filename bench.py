@@ -41,6 +41,10 @@ MICRO_BATCH = 8
 # written once), and the line says how many launches were covered by a capture.
 NCU_GEMM_TRAFFIC = {
     # (M, N, K, a_kmajor, b_kmajor): (bytes per launch, profiles/ file)
+    (8192, 3072, 768, True, True): (67.7e6, "gemm_tc_kernel_ffn1_fwd_ffn2_dgrad_counters.md"),    # FFN-1 forward + GELU
+    (8192, 3072, 768, True, False): (89.8e6, "gemm_tc_kernel_ffn1_fwd_ffn2_dgrad_counters.md"),   # dy W2 x gelu'
+    (3072, 768, 8192, False, False): (68.1e6, "gemm_tc_pair_kernel_wgrad_dgrad_ffn1_counters.md"),  # FFN-1 weight gradient
+    (8192, 768, 3072, True, False): (58.8e6, "gemm_tc_pair_kernel_wgrad_dgrad_ffn1_counters.md"),   # dh W1
 }
 
 

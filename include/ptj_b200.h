@@ -99,6 +99,9 @@ int ptj_layernorm_bwd_dropout(const void* dy, const void* x, const float* gamma,
  *   - dim <= ptj_layernorm_bwd_noalloc_max_dim() (2048); larger sizes return PTJ_ERR_TOO_LARGE.
  *   - The first call on a device looks up the array's device address (a driver query, done once per device with
  *     that device current); make that first call before any stream capture.
+ *   - The array belongs to the CURRENT device: the device that owns `stream` must be current at the call (as for
+ *     every entry point that launches on `stream`); with another device current the launch would be handed the
+ *     address of that other device's array.
  *   - It calls no cudaMalloc / cudaFree or other allocating routine.
  *   - All calls on a device share the one array, which keeps the last call's contents (nothing in it has to start
  *     at zero: every call overwrites what it reads). Two calls that overlap on the GPU (different streams) race;

@@ -6,8 +6,9 @@ This file restates, in plain PyTorch on the CPU, the arithmetic of the reference
 __graft_entry__.smoke() and bench.py's CPU-baseline / reference arm may import it.
 
 Pinning: tests/golden/make_golden.py runs the real reference (imported from its checkout, unmodified) on seeded
-inputs and stores its outputs; tests/test_oracle_golden.py checks every function here against those fixtures, and
-oracle/pin_against_reference.py repeats the comparison live wherever the reference checkout is present.
+inputs and stores its outputs (make_golden_eval.py and make_golden_packed.py do the same for the evaluation callers
+and for batches packed by the reference's collator); tests/test_oracle_golden.py checks every function here against
+those fixtures.
 Dropout randomness is the one thing that cannot be pinned to the reference (its masks come from triton.language.rand
 / torch.bernoulli, which never agreed with each other either): the oracle takes the 0/1 masks as INPUTS, so the
 semantics "multiply by the mask, do not rescale" are checked exactly while the bit stream is this project's Philox

@@ -66,3 +66,35 @@ def test_rejects_sizes_beyond_the_fixed_capacity():
     rc = lib.ptj_layernorm_bwd_noalloc(x.data_ptr(), x.data_ptr(), g.data_ptr(), None, x.data_ptr(), g.data_ptr(),
                                        g.data_ptr(), 4, cap + 8, 0, torch.cuda.current_stream().cuda_stream)
     assert rc == -9 and b"capacity" in lib.ptj_status_string(rc)
+
+
+def test_optional_outputs_empty_input_and_the_capacity_edge():
+    """dgamma / dbeta may be left out (no partial sums are needed then), zero rows are legal, and the widest row the
+    fixed array is sized for (dim 2048, every block of the grid in use) matches the regular entry point bit for bit."""
+    lib = pkg("_lib").lib()
+    fn = lib.ptj_layernorm_bwd_noalloc
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(1)
+    rows, dim = 600, 768
+    x = torch.randn(rows, dim, generator=g).bfloat16().cuda()
+    dy = torch.randn(rows, dim, generator=g).bfloat16().cuda()
+    gamma = (1 + 0.1 * torch.randn(dim, generator=g)).cuda()
+    full = _run(lib, fn, dy, x, gamma, torch.zeros_like(x))["noalloc"][0]
+    dx = torch.empty_like(x)
+    assert fn(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), None, dx.data_ptr(), None, None, rows, dim, 1, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dx, full), "leaving out the parameter gradients must not change dx"
+    # zero rows: nothing to read, parameter gradients are zero
+    dg, db = torch.full((dim,), 3.0, device="cuda"), torch.full((dim,), 3.0, device="cuda")
+    assert fn(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), None, dx.data_ptr(), dg.data_ptr(), db.data_ptr(), 0, dim, 1, st) == 0
+    torch.cuda.synchronize()
+    assert float(dg.abs().max()) == 0.0 and float(db.abs().max()) == 0.0
+    # dim at the capacity, enough rows to occupy every block of the grid
+    cap = int(lib.ptj_layernorm_bwd_noalloc_max_dim())
+    rows = 8 * 148 * 2 + 5
+    x = torch.randn(rows, cap, generator=g).bfloat16().cuda()
+    dy = torch.randn(rows, cap, generator=g).bfloat16().cuda()
+    gamma = (1 + 0.1 * torch.randn(cap, generator=g)).cuda()
+    out = _run(lib, fn, dy, x, gamma, torch.zeros_like(x))
+    for a, b in zip(out["regular"], out["noalloc"]):
+        assert torch.equal(a, b)
