@@ -227,7 +227,7 @@ def main():
     ap.add_argument("--model", default="gpt2-small", choices=["gpt2-small", "gpt2-medium"])
     ap.add_argument("--micro-batch", type=int, default=None, help="sequences per GPU (default 8; 16 for gpt2-medium)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="issue every kernel of a step from the host instead of replaying a CUDA graph of forward + backward (single GPU)")
+    ap.add_argument("--no-graph", action="store_true", help="issue every kernel of a step from the host instead of replaying CUDA graphs of forward + backward")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -253,7 +253,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ops = ptj.operators
-    tc = ptj.TrainConfig.benchmark_recipe(seed=0, cuda_graph=(world == 1 and not args.no_graph))
+    tc = ptj.TrainConfig.benchmark_recipe(seed=0, cuda_graph=not args.no_graph)
     trainer = ptj.Trainer(cfg, tc, device=f"cuda:{local}", world=world, rank=rank)
     n_batches = 4
     host = [zipf_ids(cfg.vocab, (MICRO_BATCH, cfg.seq + 1), seed=17 + 1000 * rank + i).pin_memory() for i in range(n_batches)]
@@ -335,7 +335,9 @@ def main():
                     "h2d_bytes_per_step": host[0].numel() * 4, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches), "host_enqueue_ms_per_step": host_enqueue_ms,
-            "launch_mode": "CUDA graph of forward + backward, clip + AdamW launched directly" if graph_mode else "every kernel launched from the host",
+            "launch_mode": ("CUDA graph of forward + backward, clip + AdamW launched directly" if world == 1 else
+                            "CUDA graphs of forward + backward, cut at every gradient bucket; all-reduces, clip + AdamW launched directly")
+            if graph_mode else "every kernel launched from the host",
             "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 GEMM, all launches of the timed steps)",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf) if achieved else None, "peak_source": f"of {label}",

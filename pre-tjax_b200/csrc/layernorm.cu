@@ -3,6 +3,7 @@
 // dbeta). HBM-bound: one warp owns one row, the row lives in registers between the statistics and the output pass,
 // all global accesses are 16-byte vectors.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -279,6 +280,247 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
   }
 }
 
+// ---- bf16 backward, rows of up to 2048 columns: several warps per row, rows staged through shared memory ---------
+// The warp-per-row kernel above spends 1 600 instructions per row and keeps one row per warp in flight; it runs at a
+// third of the memory roofline, issue- and latency-bound at once. Here a row is spread over W = ceil(dim / 256) warps
+// (one 16-byte vector per lane), so a thread's running column sums are 24 registers instead of shared-memory strips,
+// the arithmetic runs two floats wide (fma.rn.f32x2), and the loads are decoupled from the registers: every thread
+// copies its own vectors of the next kRing - 1 rows into a private shared-memory ring with cp.async (each thread reads
+// back only what it copied itself, so the ring needs no barrier), which keeps ~24 rows per SM in flight. Row sums
+// cross the W warps of a row group through shared memory and a named barrier. RG row groups per block take
+// alternate rows of the block's contiguous row range; their column sums are folded in group order at the end.
+constexpr int kRing = 4;
+__host__ __device__ constexpr int ln_rows_groups(int W) { return W >= 7 ? 1 : 12 / W; }
+
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t bf2_to_f2(uint32_t w) {  // two packed bf16 -> two floats
+  return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ float f2_hsum(uint64_t v) {
+  float a, b;
+  f2_unpack(v, a, b);
+  return a + b;
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Sum of one value per warp over the W warps of a row group (every thread gets the total; fixed order). `slot` is this
+// exchange's own W floats; a slot is reused one row later, with two other exchanges' barriers in between.
+template <int W>
+__device__ __forceinline__ float group_sum(float v, float* slot, int wr, int lane, int bar_id) {
+  v = warp_sum(v);
+  if constexpr (W == 1) return v;
+  if (lane == 0) slot[wr] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(32 * W) : "memory");
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) t += slot[w];
+  return t;
+}
+
+// two values at once, one barrier
+template <int W>
+__device__ __forceinline__ void group_sum2(float& a, float& b, float* slot, int wr, int lane, int bar_id) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if constexpr (W == 1) return;
+  if (lane == 0) {
+    slot[wr] = a;
+    slot[W + wr] = b;
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(32 * W) : "memory");
+  a = 0.f;
+  b = 0.f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) {
+    a += slot[w];
+    b += slot[W + w];
+  }
+}
+
+template <int W>
+__global__ void __launch_bounds__(32 * W * ln_rows_groups(W), 2)
+ln_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const float* __restrict__ gamma, const __nv_bfloat16* dx_add, __nv_bfloat16* dx,
+                   float* __restrict__ partial, int64_t rows, int dim, const LnMask mk) {
+  grid_dep_sync();
+  constexpr int RG = ln_rows_groups(W);
+  constexpr int kThreads = 32 * W * RG;
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  uint4* ring = reinterpret_cast<uint4*>(sm_raw);                                   // [kRing][3][kThreads]
+  float* red = reinterpret_cast<float*>(sm_raw + sizeof(uint4) * kRing * 3 * kThreads);  // [RG][4][W]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int grp = warp / W, wr = warp - grp * W;
+  const int nvec = dim >> 3;
+  const int vi = wr * 32 + lane;
+  const bool live = vi < nvec;
+  const bool want_sums = partial != nullptr;
+  const bool want_cs = want_sums && mk.colsum != nullptr;
+  const bool masked = mk.out != nullptr;
+  const bool draw = masked && mk.train && mk.thr != 0u;
+  const uint64_t mask_seed = draw ? resolve_seed(mk.seed) : 0ull;
+  float* my_red = red + grp * 4 * W;
+  const int bar_id = 1 + grp;
+  const float inv_n = 1.f / static_cast<float>(dim), inv_nm1 = 1.f / static_cast<float>(dim - 1);
+  const float n_adj = static_cast<float>(dim) * inv_nm1;
+
+  uint64_t gm[4];
+  {
+    float g8[8];
+    if (live) {
+      load_params<8>(gamma + vi * 8, g8);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g8[j] = 0.f;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) gm[q] = f2_pack(g8[2 * q], g8[2 * q + 1]);
+  }
+  uint64_t acc_g[4], acc_b[4], acc_d[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) acc_g[q] = acc_b[q] = acc_d[q] = 0ull;  // two packed +0.0f
+
+  // this block's rows [r0, r1); group g takes r0 + g, r0 + g + RG, ...
+  const int64_t r0 = rows * blockIdx.x / gridDim.x, r1 = rows * (blockIdx.x + 1) / gridDim.x;
+  const int n_my = r0 + grp < r1 ? static_cast<int>((r1 - r0 - grp + RG - 1) / RG) : 0;
+  auto row_of = [&](int it) { return r0 + grp + static_cast<int64_t>(it) * RG; };
+  auto fetch = [&](int it) {
+    if (it < n_my && live) {
+      const int64_t off = row_of(it) * dim + vi * 8;
+      uint4* dst = ring + (it % kRing) * 3 * kThreads + tid;
+      cp_async16(dst, x + off);
+      cp_async16(dst + kThreads, dy + off);
+      if (dx_add != nullptr) cp_async16(dst + 2 * kThreads, dx_add + off);
+    }
+    cp_async_commit();  // (an empty group when there is nothing to fetch keeps the wait count uniform)
+  };
+#pragma unroll
+  for (int it = 0; it < kRing - 1; ++it) fetch(it);
+
+  for (int it = 0; it < n_my; ++it) {
+    fetch(it + kRing - 1);
+    cp_async_wait<kRing - 1>();
+    const int64_t row = row_of(it);
+    uint64_t xv[4], dv[4];
+    uint4 rres = make_uint4(0u, 0u, 0u, 0u);
+    {
+      const uint4* src = ring + (it % kRing) * 3 * kThreads + tid;
+      uint4 tx = make_uint4(0u, 0u, 0u, 0u), td = tx;
+      if (live) {
+        tx = src[0];
+        td = src[kThreads];
+        if (dx_add != nullptr) rres = src[2 * kThreads];
+      }
+      xv[0] = bf2_to_f2(tx.x); xv[1] = bf2_to_f2(tx.y); xv[2] = bf2_to_f2(tx.z); xv[3] = bf2_to_f2(tx.w);
+      dv[0] = bf2_to_f2(td.x); dv[1] = bf2_to_f2(td.y); dv[2] = bf2_to_f2(td.z); dv[3] = bf2_to_f2(td.w);
+    }
+    // mean, then the centred sum of squares (two passes over registers, as in the forward kernel)
+    const float mean = group_sum<W>(f2_hsum(f2_add(f2_add(xv[0], xv[1]), f2_add(xv[2], xv[3]))), my_red, wr, lane, bar_id) * inv_n;
+    const uint64_t nmean = f2_pack(-mean, -mean);
+    uint64_t ssq = 0ull;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      xv[q] = f2_add(xv[q], nmean);
+      ssq = f2_fma(xv[q], xv[q], ssq);
+    }
+    // (lanes beyond the row hold x = 0 and would add mean^2: they contribute nothing instead)
+    const float rstd = 1.f / sqrtf(group_sum<W>(live ? f2_hsum(ssq) : 0.f, my_red + W, wr, lane, bar_id) * inv_nm1);
+    const uint64_t rstd2 = f2_pack(rstd, rstd);
+    uint64_t s1 = 0ull, s2 = 0ull;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      xv[q] = f2_mul(xv[q], rstd2);                 // xhat
+      acc_g[q] = f2_fma(dv[q], xv[q], acc_g[q]);    // dgamma += dy * xhat
+      acc_b[q] = f2_add(acc_b[q], dv[q]);           // dbeta  += dy
+      dv[q] = f2_mul(dv[q], gm[q]);                 // dy * gamma
+      s1 = f2_add(s1, dv[q]);
+      s2 = f2_fma(dv[q], xv[q], s2);
+    }
+    if (dx == nullptr) continue;  // parameter gradients only (uniform over the block)
+    float m1 = f2_hsum(s1), m2 = f2_hsum(s2);
+    group_sum2<W>(m1, m2, my_red + 2 * W, wr, lane, bar_id);
+    m1 *= inv_n;
+    m2 *= inv_n * n_adj;
+    // dx = (dy*gamma - m1 - xhat * m2) * rstd (+ the gradient arriving over the residual connection)
+    const uint64_t c1 = f2_pack(-m1 * rstd, -m1 * rstd), c2 = f2_pack(-m2 * rstd, -m2 * rstd);
+    const uint32_t rw[4] = {rres.x, rres.y, rres.z, rres.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint64_t o = f2_fma(xv[q], c2, f2_fma(dv[q], rstd2, c1));
+      if (dx_add != nullptr) o = f2_add(o, bf2_to_f2(rw[q]));
+      float a, b;
+      f2_unpack(o, a, b);
+      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      ow[q] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    if (live) *reinterpret_cast<uint4*>(dx + row * dim + vi * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    if (masked) {  // second output: dropout applied to dx as stored (rounded to bf16), see LnMask
+      if (mk.train) {
+        if (draw) {
+          const Philox4 r = philox4x32_10(mask_seed, static_cast<uint64_t>(row) * nvec + vi, mk.stream_id);
+          const uint32_t rnd[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t keep = ((rnd[q] & 0xffffu) >= mk.thr ? 0x0000ffffu : 0u) |
+                                  ((rnd[q] >> 16) >= mk.thr ? 0xffff0000u : 0u);
+            ow[q] &= keep;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float a, b;
+          f2_unpack(bf2_to_f2(ow[q]), a, b);
+          __nv_bfloat162 h = __floats2bfloat162_rn(a * mk.eval_scale, b * mk.eval_scale);
+          ow[q] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      if (live)
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(mk.out) + row * dim + vi * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      if (want_cs) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc_d[q] = f2_add(acc_d[q], bf2_to_f2(ow[q]));  // the values as stored
+      }
+    }
+  }
+  if (!want_sums) return;
+  // fold the row groups' column sums in group order (fixed order => reproducible); the ring is free by now
+  cp_async_wait<0>();
+  __syncthreads();
+  const int nq = want_cs ? 3 : 2;
+  float* fold = reinterpret_cast<float*>(sm_raw);  // [RG][nq][W * 256]
+  constexpr int kCols = W * 256;
+  {
+    float* mine = fold + static_cast<size_t>(grp) * nq * kCols + vi * 8;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      f2_unpack(acc_g[q], mine[2 * q], mine[2 * q + 1]);
+      f2_unpack(acc_b[q], mine[kCols + 2 * q], mine[kCols + 2 * q + 1]);
+      if (want_cs) f2_unpack(acc_d[q], mine[2 * kCols + 2 * q], mine[2 * kCols + 2 * q + 1]);
+    }
+  }
+  __syncthreads();
+  float* out = partial + static_cast<size_t>(blockIdx.x) * nq * dim;
+  for (int t = tid; t < nq * dim; t += kThreads) {
+    const int which = t / dim, c = t - which * dim;
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < RG; ++g) sum += fold[(static_cast<size_t>(g) * nq + which) * kCols + c];
+    out[t] = sum;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kLnThreads)
 ln_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
@@ -379,6 +621,32 @@ int launch_bwd(const T* dy, const T* x, const float* gamma, const T* dx_add, T* 
   const int grid = ln_bwd_grid(rows);
   float* partial = dgamma != nullptr ? scratch : nullptr;
   const int nq = (partial != nullptr && mk.colsum != nullptr) ? 3 : 2;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    if (vec_ok && dim >= 8 && dim <= 2048) {  // several warps per row, rows staged through shared memory
+      const int w = static_cast<int>(ceil_div(dim, 256));
+#define PTJ_LN_ROWS(W)                                                                                              \
+  case W: {                                                                                                         \
+    constexpr int kT = 32 * W * ln_rows_groups(W);                                                                  \
+    constexpr size_t kRingBytes = sizeof(uint4) * kRing * 3 * kT;                                                   \
+    constexpr size_t kFoldBytes = sizeof(float) * ln_rows_groups(W) * 3 * W * 256;                                  \
+    constexpr size_t kSm = (kRingBytes > kFoldBytes ? kRingBytes : kFoldBytes) + sizeof(float) * ln_rows_groups(W) * 4 * W; \
+    static_assert(kSm <= 227 * 1024, "shared memory of the LayerNorm backward");                                    \
+    cudaFuncSetAttribute(ln_bwd_rows_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSm);             \
+    launch_k(ln_bwd_rows_kernel<W>, grid, kT, kSm, st, dy, x, gamma, dx_add, dx, partial, rows, dim, mk);            \
+  } break;
+      switch (w) {
+        PTJ_LN_ROWS(1) PTJ_LN_ROWS(2) PTJ_LN_ROWS(3) PTJ_LN_ROWS(4) PTJ_LN_ROWS(5) PTJ_LN_ROWS(6) PTJ_LN_ROWS(7) PTJ_LN_ROWS(8)
+      }
+#undef PTJ_LN_ROWS
+      PTJ_CHECK_LAUNCH();
+      if (partial != nullptr) {
+        launch_k(ln_bwd_finalize_kernel, static_cast<int>(ceil_div(nq * dim, 8)), 256, 0, st, partial, dgamma, dbeta,
+                 mk.colsum, nq, grid, dim);
+        PTJ_CHECK_LAUNCH();
+      }
+      return PTJ_OK;
+    }
+  }
   const size_t smem = static_cast<size_t>(kLnWarps) * nq * (nv <= 8 ? nv : 0) * V * 32 * sizeof(float);
 #define PTJ_LN_BWD(NV)                                                                                   \
   case NV:                                                                                               \

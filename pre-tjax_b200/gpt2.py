@@ -176,8 +176,19 @@ class Gpt2Step:
         """dx[T, N_in] = dy[T, N_out] w[N_out, N_in]: w is the 'MN-major' B operand."""
         T = dy2d.shape[0]
         K = w2d.shape[0] if cols is None else cols
-        return ops.gemm(dy2d, w2d, a_kmajor=True, b_kmajor=False, M=T, N=w2d.shape[1], K=K, lda=dy2d.stride(0),
-                        ldb=w2d.stride(0), out_dtype=self.dtype, **kw)
+        N = w2d.shape[1]
+        # A very long K with a narrow output (the LM head: K = vocabulary, N = model width) leaves the 74 thread-block
+        # pairs a bad last round (96 tiles of 256 x 256 at GPT-2 small); parts of K even it out. Measured at
+        # [8192, 768, 50257]: 543 us unsplit, 478 / 467 / 496 us in 2 / 3 / 4 parts; the K = 2304 and 3072 products of a
+        # layer only lose (32 -> 40 us, 48 -> 56 us), hence the lower bound on K.
+        split = 1
+        if dy2d.dtype == torch.bfloat16 and K >= 16384 and not kw:
+            split = split_k_for(T, N, K)
+            need = split * T * N
+            if split > 1 and (self._ws is None or self._ws.numel() < need):
+                self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
+        return ops.gemm(dy2d, w2d, a_kmajor=True, b_kmajor=False, M=T, N=N, K=K, lda=dy2d.stride(0),
+                        ldb=w2d.stride(0), out_dtype=self.dtype, split_k=split, workspace=self._ws, **kw)
 
     # -- forward --
     def forward(self, w: Weights, ids_in: torch.Tensor, train: bool, seeds: Sequence[int], row_kstart=None):

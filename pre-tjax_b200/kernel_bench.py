@@ -108,6 +108,10 @@ def main():
         rows.append(r)
         print(json.dumps(r), flush=True)
 
+    def run(name, fn, flops=None, nbytes=None, reps=None):
+        """Times one case unless --case names another one."""
+        add(name, time_us(fn, reps=reps, name=name), flops, nbytes)
+
     # ---- GEMMs (bf16 in, fp32 accumulate) ----
     if want("gemm"):
         x_d, x_f = bf(T, D), bf(T, F)
@@ -126,7 +130,7 @@ def main():
             ("gemm dgrad ffn1     dh W1", lambda: ops.gemm(y_f, w1, a_kmajor=True, b_kmajor=False, M=T, N=D, K=F), 2 * T * F * D),
             ("gemm dgrad out-proj dy Wo", lambda: ops.gemm(y_d, w_o, a_kmajor=True, b_kmajor=False, M=T, N=D, K=D), 2 * T * D * D),
             ("gemm dgrad qkv      dqkv Wqkv", lambda: ops.gemm(y_qkv, w_qkv, a_kmajor=True, b_kmajor=False, M=T, N=D, K=3 * D), 2 * T * 3 * D * D),
-            ("gemm dgrad lm-head  dlogits Wemb", lambda: ops.gemm(logits, w_emb, a_kmajor=True, b_kmajor=False, M=T, N=D, K=V, lda=Vp), 2 * T * V * D),
+            ("gemm dgrad lm-head  dlogits Wemb (K split as in the step)", lambda: step._dgrad(logits, w_emb, cols=V), 2 * T * V * D),
         ]
         step = ptj.gpt2.Gpt2Step(ptj.PRESETS["gpt2-small"])
         g_w2, g_w1, g_wo, g_wqkv, g_emb = (torch.empty(*s, device=dev) for s in ((D, F), (F, D), (D, D), (3 * D, D), (V, D)))
@@ -153,14 +157,14 @@ def main():
         dq, dk, dv = (d5[:, :, :, c, :].permute(0, 2, 1, 3) for c in range(3))
         fl_attn = 4 * B * H * S * S * 64 / 2
         m, l = ops.attn_fwd(q, k, v, o4, True, 5, p=0.1)
-        add("attention fwd  B*H=%d S=1024 d=64 dropout 0.1" % (B * H), time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1)), flops=fl_attn)
-        add("attention bwd  (dQ, dK, dV; recompute) dropout 0.1", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1)), flops=2.5 * fl_attn)
+        run("attention fwd  B*H=%d S=1024 d=64 dropout 0.1" % (B * H), lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1), flops=fl_attn)
+        run("attention bwd  (dQ, dK, dV; recompute) dropout 0.1", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1), flops=2.5 * fl_attn)
         bits = ops.attn_keep_bits(q, k, v, o4, 5, p=0.1)
-        add("attention keep flags of one call (Philox, 16-bit lanes)", time_us(lambda: ops.attn_keep_bits(q, k, v, o4, 5, p=0.1, bits=bits)))
-        add("attention fwd  dropout 0.1, keep flags given", time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits)), flops=fl_attn)
-        add("attention bwd  dropout 0.1, keep flags given", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1, keep_bits=bits)), flops=2.5 * fl_attn)
-        add("attention fwd  no dropout", time_us(lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.0)), flops=fl_attn)
-        add("attention bwd  no dropout", time_us(lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.0)), flops=2.5 * fl_attn)
+        run("attention keep flags of one call (Philox, 16-bit lanes)", lambda: ops.attn_keep_bits(q, k, v, o4, 5, p=0.1, bits=bits))
+        run("attention fwd  dropout 0.1, keep flags given", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits), flops=fl_attn)
+        run("attention bwd  dropout 0.1, keep flags given", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1, keep_bits=bits), flops=2.5 * fl_attn)
+        run("attention fwd  no dropout", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.0), flops=fl_attn)
+        run("attention bwd  no dropout", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.0), flops=2.5 * fl_attn)
 
     # ---- memory-bound operators (operands rotate through copies so that nothing is served from L2) ----
     if want("memory"):
@@ -169,34 +173,34 @@ def main():
         dg, db = torch.empty(D, device=dev), torch.empty(D, device=dev)
         xs = copies(lambda: (bf(T, D), bf(T, D), bf(T, D)), 3 * T * D * 2)
         n = len(xs)
-        add("layernorm fwd [T,768] bf16", time_us(lambda i: ops.t_layernorm_fwd_t((g, bta), xs[i % n][0])), nbytes=2 * T * D * 2)
-        add("layernorm bwd dx+dgamma+dbeta (+residual grad)", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db)), nbytes=4 * T * D * 2)
+        run("layernorm fwd [T,768] bf16", lambda i: ops.t_layernorm_fwd_t((g, bta), xs[i % n][0]), nbytes=2 * T * D * 2)
+        run("layernorm bwd dx+dgamma+dbeta (+residual grad)", lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db), nbytes=4 * T * D * 2)
         cs = torch.empty(D, device=dev)
-        add("layernorm bwd ... + dropout(dx) as a second output", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1))), nbytes=5 * T * D * 2)
-        add("layernorm bwd ... + dropout(dx) + its column sums", time_us(lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1), dropped_colsum_out=cs)), nbytes=5 * T * D * 2)
-        add("colsum (bias grad) [T,768]", time_us(lambda i: ops.colsum(xs[i % n][0], out=cs)), nbytes=T * D * 2)
-        add("dropout [T,768] (mask regenerated)", time_us(lambda i: ops.dropout(xs[i % n][0], True, 7, p=0.1)), nbytes=2 * T * D * 2)
-        add("dropout + residual add [T,768]", time_us(lambda i: ops.dropout(xs[i % n][0], True, 7, residual=xs[i % n][1], p=0.1)), nbytes=3 * T * D * 2)
+        run("layernorm bwd ... + dropout(dx) as a second output", lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1)), nbytes=5 * T * D * 2)
+        run("layernorm bwd ... + dropout(dx) + its column sums", lambda i: ops.layernorm_bwd(xs[i % n][1], (g, None), xs[i % n][0], dx_add=xs[i % n][2], dgamma_out=dg, dbeta_out=db, dropped=(True, 7, 0.1), dropped_colsum_out=cs), nbytes=5 * T * D * 2)
+        run("colsum (bias grad) [T,768]", lambda i: ops.colsum(xs[i % n][0], out=cs), nbytes=T * D * 2)
+        run("dropout [T,768] (mask regenerated)", lambda i: ops.dropout(xs[i % n][0], True, 7, p=0.1), nbytes=2 * T * D * 2)
+        run("dropout + residual add [T,768]", lambda i: ops.dropout(xs[i % n][0], True, 7, residual=xs[i % n][1], p=0.1), nbytes=3 * T * D * 2)
         del xs
         fs = copies(lambda: (bf(T, F), bf(T, F)), 2 * T * F * 2)
         n = len(fs)
-        add("gelu fwd [T,3072]", time_us(lambda i: ops.t_gelu_fwd_t(fs[i % n][0])), nbytes=2 * T * F * 2)
-        add("gelu bwd [T,3072]", time_us(lambda i: ops.t_gelu_bkwd2_t(fs[i % n][1], fs[i % n][0])), nbytes=3 * T * F * 2)
-        add("colsum (bias grad) [T,3072]", time_us(lambda i: ops.colsum(fs[i % n][0])), nbytes=T * F * 2)
+        run("gelu fwd [T,3072]", lambda i: ops.t_gelu_fwd_t(fs[i % n][0]), nbytes=2 * T * F * 2)
+        run("gelu bwd [T,3072]", lambda i: ops.t_gelu_bkwd2_t(fs[i % n][1], fs[i % n][0]), nbytes=3 * T * F * 2)
+        run("colsum (bias grad) [T,3072]", lambda i: ops.colsum(fs[i % n][0]), nbytes=T * F * 2)
         del fs
         lg, lg2 = bf(T, Vp), torch.empty(T, Vp, device=dev, dtype=torch.bfloat16)  # 824 MB each: far beyond L2
         labels = torch.randint(1, V, (T,), device=dev, dtype=torch.int32)
         r5 = max(3, REPS // 4)
-        add("log-softmax fwd [T,50257] (ld 50304)", time_us(lambda: lib.check(lib.lib().ptj_log_softmax_fwd(lg.data_ptr(), lg2.data_ptr(), T, V, Vp, Vp, 1, st()), "lsm"), reps=r5), nbytes=2 * T * V * 2)
-        add("log-softmax bwd [T,50257]", time_us(lambda: lib.check(lib.lib().ptj_log_softmax_bwd(lg.data_ptr(), lg.data_ptr(), lg2.data_ptr(), T, V, Vp, 1, st()), "lsm"), reps=r5), nbytes=3 * T * V * 2)
-        add("colsum (lm-head bias grad) [T,50257]", time_us(lambda: ops.colsum(lg, cols=V), reps=r5), nbytes=T * V * 2)
-        add("cross-entropy fwd+bwd in place [T,50257]", time_us(lambda: ops.cross_entropy(labels, lg2, cols=V, want_grad=True, in_place=True), reps=r5), nbytes=2 * T * V * 2)
+        run("log-softmax fwd [T,50257] (ld 50304)", lambda: lib.check(lib.lib().ptj_log_softmax_fwd(lg.data_ptr(), lg2.data_ptr(), T, V, Vp, Vp, 1, st()), "lsm"), reps=r5, nbytes=2 * T * V * 2)
+        run("log-softmax bwd [T,50257]", lambda: lib.check(lib.lib().ptj_log_softmax_bwd(lg.data_ptr(), lg.data_ptr(), lg2.data_ptr(), T, V, Vp, 1, st()), "lsm"), reps=r5, nbytes=3 * T * V * 2)
+        run("colsum (lm-head bias grad) [T,50257]", lambda: ops.colsum(lg, cols=V), reps=r5, nbytes=T * V * 2)
+        run("cross-entropy fwd+bwd in place [T,50257]", lambda: ops.cross_entropy(labels, lg2, cols=V, want_grad=True, in_place=True), reps=r5, nbytes=2 * T * V * 2)
         del lg, lg2
         n = 124_453_248
         p_, g_, m_, v_ = (torch.zeros(n, device=dev) for _ in range(4))
         sh = torch.zeros(n, device=dev, dtype=torch.bfloat16)
-        add("adamw fused (+bf16 shadow) 124M params", time_us(lambda: lib.check(lib.lib().ptj_adamw(p_.data_ptr(), g_.data_ptr(), m_.data_ptr(), v_.data_ptr(), sh.data_ptr(), n, 0, 0, 0, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, 0, 0.0, st()), "adamw"), reps=r5), nbytes=n * 30)
-        add("grad sum of squares 124M", time_us(lambda: ptj.optimizer.sumsq(g_), reps=r5), nbytes=n * 4)
+        run("adamw fused (+bf16 shadow) 124M params", lambda: lib.check(lib.lib().ptj_adamw(p_.data_ptr(), g_.data_ptr(), m_.data_ptr(), v_.data_ptr(), sh.data_ptr(), n, 0, 0, 0, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, 0, 0.0, st()), "adamw"), reps=r5, nbytes=n * 30)
+        run("grad sum of squares 124M", lambda: ptj.optimizer.sumsq(g_), reps=r5, nbytes=n * 4)
         del p_, g_, m_, v_, sh
         # embedding backward on Zipf(1.1) token ids (the most frequent token makes a run of several hundred rows)
         gz = torch.Generator().manual_seed(0)

@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -162,6 +162,8 @@ class GradReducer:
         # (event before the wait, event after it) of recent steps, when exposure is being measured
         self.measure_exposed = False
         self.exposed_events: List[Tuple[object, object]] = []
+        # when set, called with the bucket index instead of launching the all-reduce (graph recording, see Trainer)
+        self.on_complete: Optional[Callable[[int], None]] = None
         self.reset()
 
     def reset(self):
@@ -177,7 +179,13 @@ class GradReducer:
             if b.pending < 0:
                 raise RuntimeError(f"gradient {n} reported ready twice in one step")
             if b.pending == 0:
-                self._launch(self.owner[n])
+                (self.on_complete or self._launch)(self.owner[n])
+
+    def launch_bucket(self, idx: int):
+        """All-reduce bucket idx now: its gradients are final as far as the current stream is concerned (used when the
+        kernels come from recorded graph segments and nothing reports tensor by tensor)."""
+        self.buckets[idx].pending = 0
+        self._launch(idx)
 
     def _launch(self, idx: int):
         b = self.buckets[idx]
@@ -246,11 +254,12 @@ class TrainConfig:
     seed: int = 0
     global_token_norm: bool = False
     compute_dtype: torch.dtype = torch.bfloat16
-    # Record forward + backward of a step once as a CUDA graph and replay it (single process, plain causal batches): the
-    # host then issues one graph launch instead of some 360 kernel launches per step. Dropout seeds live in device
-    # memory and are rewritten before every replay, so the masks change from step to step exactly as without the
-    # graph. Data-parallel steps keep ordinary launches: recording the bucketed NCCL all-reduces together with the
-    # kernels left both ranks of a two-GPU run waiting on each other, so that combination is not offered.
+    # Record forward + backward of a step once as a CUDA graph and replay it (plain causal batches): the host then
+    # issues one graph launch instead of some 360 kernel launches per step. Dropout seeds live in device memory and are
+    # rewritten before every replay, so the masks change from step to step exactly as without the graph.
+    # With data parallelism the recording is cut into one graph per gradient bucket: the NCCL all-reduces are NOT
+    # recorded (a recording that contained them left both ranks of a two-GPU run waiting on each other); they are
+    # issued from the host between the graph launches, on their own stream, as in the unrecorded step.
     cuda_graph: bool = False
 
     @staticmethod
@@ -308,8 +317,9 @@ class Trainer:
         self.peer_watch = peer_watch  # optional: checked on the host before each step's collectives
         self.t = 0
         self.ids_dev = None
-        self.use_graph = bool(self.tc.cuda_graph) and world == 1 and self.device.type == "cuda"
-        self._graph = None           # (batch shape, torch.cuda.CUDAGraph, static ids, static stats)
+        self.use_graph = (bool(self.tc.cuda_graph) and self.device.type == "cuda"
+                          and not (world > 1 and self.tc.global_token_norm))
+        self._graph = None           # (batch shape, [graph | bucket index, ...], static ids, static stats)
         self._seed_words = None      # int64[1 + 3 L] on the device: this step's dropout seeds, read by the kernels
         self._seed_host = None
         self.graph_launches = 0      # kernels recorded in the graph (one replay launches that many)
@@ -336,8 +346,8 @@ class Trainer:
         mean loss, accuracy, fraction of non-padding labels (of this rank's micro-batch).
         row_kstart: optional int32 [B, S] on the device for packed / padded batches (operators.row_kstart_from_lengths
         or row_kstart_from_mask): position i attends keys [row_kstart[b, i], i]; None = plain causal."""
-        if self.use_graph and train and row_kstart is None:
-            return self._graph_step(y, lr)
+        if self.use_graph and train and row_kstart is None and (self.world == 1 or self.t >= 2):
+            return self._graph_step(y, lr)  # (data parallel: the first two steps run unrecorded and warm everything up)
         if not y.is_cuda:
             if self.ids_dev is None or self.ids_dev.shape != y.shape:
                 self.ids_dev = torch.empty(y.shape, device=self.device, dtype=torch.int32)
@@ -380,29 +390,83 @@ class Trainer:
             ids.copy_(y, non_blocking=True)
             refs = [ops.seed_at(self._seed_words, i) for i in range(n_seeds)]
 
-            def fwd_bwd():
+            def fwd_bwd(on_ready=None):
                 sorted_pos = torch.sort(ids[:, :-1].reshape(-1), stable=True).indices.to(torch.int32)
-                return self.engine.loss_and_grads(self.w, self.gv, ids, True, refs, sorted_pos=sorted_pos)
+                return self.engine.loss_and_grads(self.w, self.gv, ids, True, refs, sorted_pos=sorted_pos,
+                                                  on_ready=on_ready)
 
-            side = torch.cuda.Stream(self.device)
-            side.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(side):  # warm-up: sizes the allocator's pools and every lazily initialised cache
-                for _ in range(2):
-                    fwd_bwd()
-            torch.cuda.current_stream(self.device).wait_stream(side)
-            torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
             before = _lib.launch_count()
-            with torch.cuda.graph(graph):
-                stats = fwd_bwd()
+            if self.reducer is None:
+                side = torch.cuda.Stream(self.device)
+                side.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(side):  # warm-up: sizes the allocator's pools and every lazily initialised cache
+                    for _ in range(2):
+                        fwd_bwd()
+                torch.cuda.current_stream(self.device).wait_stream(side)
+                torch.cuda.synchronize(self.device)
+                graph = torch.cuda.CUDAGraph()
+                before = _lib.launch_count()
+                with torch.cuda.graph(graph):
+                    stats = fwd_bwd()
+                parts = [graph]
+            else:
+                parts, stats = self._record_segments(fwd_bwd)
             self.graph_launches = _lib.launch_count() - before
-            self._graph = (tuple(y.shape), graph, ids, stats)
-        _, graph, ids, stats = self._graph
+            self._graph = (tuple(y.shape), parts, ids, stats)
+        _, parts, ids, stats = self._graph
         ids.copy_(y, non_blocking=True)
-        graph.replay()
+        if self.reducer is not None:
+            if self.peer_watch is not None:
+                self.peer_watch.announce(self.t)
+                self.peer_watch.check(self.t)
+            self.reducer.reset()
+        for part in parts:
+            if isinstance(part, int):
+                self.reducer.launch_bucket(part)  # event on this stream -> NCCL stream -> all-reduce in place
+            else:
+                part.replay()
+        if self.reducer is not None:
+            self.reducer.finish()
         self.graph_replays += 1
         self.apply_update(lr if lr is not None else self.tc.lr)
         return stats
+
+    def _record_segments(self, fwd_bwd):
+        """Records forward + backward as a chain of CUDA graphs that ends one graph at every point where a gradient
+        bucket becomes final, and returns [graph, bucket, graph, bucket, ...] in launch order. Nothing runs while
+        recording and no collective is recorded; all graphs draw from one memory pool, so tensors made in one segment
+        stay valid in the later ones, and they are always replayed in this order."""
+        dev = self.device
+        torch.cuda.synchronize(dev)
+        pool = torch.cuda.graph_pool_handle()
+        stream = torch.cuda.Stream(dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        parts: List[object] = []
+        cur = [None]
+
+        def begin():
+            cur[0] = torch.cuda.CUDAGraph()
+            cur[0].capture_begin(pool=pool, capture_error_mode="thread_local")
+
+        def cut(bucket: int):
+            cur[0].capture_end()
+            parts.extend([cur[0], bucket])
+            begin()
+
+        self.reducer.reset()
+        self.reducer.on_complete = cut
+        try:
+            with torch.cuda.stream(stream):
+                begin()
+                try:
+                    stats = fwd_bwd(self.reducer.mark_ready)
+                finally:
+                    cur[0].capture_end()
+                parts.append(cur[0])
+        finally:
+            self.reducer.on_complete = None
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        return parts, stats
 
     def apply_update(self, lr: float):
         """Clip by the global norm of the (reduced) gradient buffer and run the fused AdamW; t counts from 1."""

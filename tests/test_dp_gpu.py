@@ -48,6 +48,56 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
+def _worker_recorded(rank, world, port, ret):
+    """An unrecorded and a recorded data-parallel trainer side by side in one process group (both ranks issue their
+    collectives in the same order): dropout 0.1, buckets small enough to cut the recording into several graphs."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        ptj = pkg()
+        cfg = pkg("gpt2").GPT2Config(vocab=512, dim=128, layers=2, heads=2, ffn=256, seq=128, dropout=0.1)
+        mk = lambda graph: ptj.Trainer(cfg, ptj.TrainConfig.benchmark_recipe(seed=5, bucket_mb=0.25, cuda_graph=graph),
+                                       device=f"cuda:{rank}", world=world, rank=rank)
+        plain, recorded = mk(False), mk(True)
+        same = True
+        for ys in _batches(cfg, 6, world):
+            a = plain.step(ys[rank]).clone()
+            b = recorded.step(ys[rank]).clone()
+            same = same and torch.equal(a, b)
+        torch.cuda.synchronize()
+        parts = recorded._graph[1]
+        ret[rank] = (bool(same and torch.equal(plain.p, recorded.p)), len(parts), recorded.graph_replays,
+                     len(recorded.reducer.buckets), int(ptj.operators.last_kernel_fault()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_recorded_graph_segments_match_unrecorded_data_parallel_steps():
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_recorded, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            p.join(10)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for rank in range(world):
+        same, n_parts, replays, n_buckets, fault = ret[rank]
+        assert fault == 0
+        assert n_buckets >= 3 and n_parts == 2 * n_buckets + 1, (n_buckets, n_parts)
+        assert replays == 4, "the first two steps run unrecorded, the other four are replays"
+        assert same, "recorded and unrecorded steps must agree bit for bit (losses and parameters)"
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_ranks_agree_and_match_the_averaged_single_gpu_step():
     world = 2

@@ -316,6 +316,31 @@ def test_colsum_and_sumsq(ops, rows, cols):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dim", [200, 512, 768, 1016, 1280, 1536, 1792, 2048])
+@pytest.mark.parametrize("rows", [5, 1237])
+def test_layernorm_backward_bf16_rows_over_several_warps(dim, rows):
+    """The bf16 backward spreads a row over ceil(dim / 256) warps: every warp count, rows that do not divide over
+    the blocks and row groups, all outputs against the oracle, and the two reduced forms (parameter gradients only;
+    dx without parameter gradients) bit for bit against the full call."""
+    ops = pkg("operators")
+    x, dy, res = (rnd(rows, dim, seed=s).bfloat16() for s in (1, 2, 5))
+    x = (x.float() * 0.5 + 3.0).bfloat16()  # a mean well away from zero
+    gamma = 1 + 0.2 * rnd(dim, seed=3)
+    dx, dg, db = ops.layernorm_bwd(gpu(dy), (gpu(gamma), None), gpu(x), dx_add=gpu(res))
+    odx, odg, odb = orc.layernorm_bwd(dy.float(), gamma, x.float())
+    check(dx, odx + res.float(), BF16_TOL)
+    check(dg, odg, 1e-3)  # float32 sums of exact products of the bf16 inputs
+    check(db, odb, 1e-4)
+    dg2, db2 = ops.t_layernorm_bkwd2_p_t(gpu(dy), (gpu(gamma), gpu(gamma)), gpu(x))
+    assert torch.equal(dg, dg2) and torch.equal(db, db2)
+    dx3 = ops.t_layernorm_bkwd2_x_t(gpu(dy), (gpu(gamma), gpu(gamma)), gpu(x))
+    check(dx3, odx, BF16_TOL)
+    dx4, dg4, db4, dropped = ops.layernorm_bwd(gpu(dy), (gpu(gamma), None), gpu(x), dx_add=gpu(res), dropped=(True, 77, 0.25, 3))
+    assert torch.equal(dx4, dx) and torch.equal(dg4, dg) and torch.equal(db4, db)
+    assert torch.equal(dropped, ops.dropout(dx, True, 77, stream_id=3, p=0.25))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_layernorm_backward_with_fused_dropout_output(dtype):
     """ptj_layernorm_bwd_dropout: dx, dgamma, dbeta equal the plain call bit for bit, and the extra output equals
