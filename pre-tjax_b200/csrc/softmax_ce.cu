@@ -235,6 +235,131 @@ cross_entropy_kernel(const int32_t* __restrict__ labels, const T* logits, T* dlo
   }
 }
 
+// ---- bf16 cross entropy, rows that start on a 16-byte boundary ---------------------------------------------------
+// The kernel above spends about 25 instructions per logit (64-bit column arithmetic, arg-max bookkeeping and the
+// online rescale inside the inner loop, a compare per element for the label) and is issue-bound at half of the memory
+// roofline. This one walks the row three times with 16-byte vectors and does the least possible per element:
+//   1. maximum only, on packed bf16 pairs (half an instruction per element);
+//   2. sum of 2^((x - max) log2 e), two floats wide;
+//   3. dlogits = 2^(x log2 e + c), with c = -max log2 e + log2(1 / (n_valid * sum)) folding both scale factors into
+//      the exponent; the label's element is patched by one thread afterwards.
+// Passes 2 and 3 read the row from L2 (512-thread blocks, three per SM: the 444 rows in flight, 100 KB each at
+// GPT-2's vocabulary, stay well inside the L2). Accuracy: the label is the arg-max iff x[label] equals the maximum and no earlier column does (ties go to
+// the first index, as in torch.argmax); the second condition is only walked for rows where the first holds.
+constexpr int kCeThreads = 512;
+
+__device__ __forceinline__ uint32_t bf2_max(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ uint64_t bf2_as_f2(uint32_t w) {
+  return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+__global__ void __launch_bounds__(kCeThreads, 3)
+cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat16* logits, __nv_bfloat16* dlogits,
+                          float* __restrict__ row_stats, const float* __restrict__ n_valid, int64_t rows, int cols,
+                          int64_t ld) {
+  grid_dep_sync();
+  __shared__ float red[33];
+  const float inv_n = 1.f / *n_valid;
+  const int nvec = cols >> 3;        // whole 16-byte vectors; the last cols & 7 elements are walked one by one
+  const int tail0 = nvec << 3;
+  constexpr float kLog2e = 1.4426950408889634f;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = logits + row * ld;
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    __nv_bfloat16* dr = dlogits != nullptr ? dlogits + row * ld : nullptr;
+    const int label = labels[row];
+    if (label <= 0 || label >= cols) {  // padding (or an id outside the vocabulary): no contribution
+      if (threadIdx.x == 0) {
+        row_stats[row] = 0.f;
+        row_stats[rows + row] = 0.f;
+      }
+      if (dr != nullptr) {
+        for (int i = threadIdx.x; i < nvec; i += kCeThreads) reinterpret_cast<uint4*>(dr)[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) dr[c] = __float2bfloat16_rn(0.f);
+      }
+      continue;
+    }
+    const float x_label = __bfloat162float(xr[label]);  // read before the row is overwritten in place
+    // pass 1: maximum
+    uint32_t pm = 0xff80ff80u;  // two packed -inf
+    {
+      int i = threadIdx.x;
+      for (; i + 3 * kCeThreads < nvec; i += 4 * kCeThreads) {
+        const uint4 a = xv[i], b = xv[i + kCeThreads], c = xv[i + 2 * kCeThreads], d = xv[i + 3 * kCeThreads];
+        pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)), bf2_max(bf2_max(b.x, b.y), bf2_max(b.z, b.w))));
+        pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(c.x, c.y), bf2_max(c.z, c.w)), bf2_max(bf2_max(d.x, d.y), bf2_max(d.z, d.w))));
+      }
+      for (; i < nvec; i += kCeThreads) {
+        const uint4 a = xv[i];
+        pm = bf2_max(pm, bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)));
+      }
+    }
+    float m = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xffff0000u));
+    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) m = fmaxf(m, __bfloat162float(xr[c]));
+    m = block_max(m, red);
+    // is the label the first column that attains the maximum?
+    float hit = 0.f;
+    if (x_label == m) {  // (uniform over the block)
+      int earlier = 0;
+      for (int c = threadIdx.x; c < label; c += kCeThreads) earlier |= (__bfloat162float(xr[c]) == m) ? 1 : 0;
+      hit = __syncthreads_or(earlier) ? 0.f : 1.f;
+    }
+    // pass 2: sum of exponentials
+    const float nml = -m * kLog2e;
+    const uint64_t l2e2 = f2_pack(kLog2e, kLog2e), nml2 = f2_pack(nml, nml);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+      const uint4 a = xv[i];
+      float e0, e1, e2, e3, e4, e5, e6, e7;
+      f2_unpack(f2_fma(bf2_as_f2(a.x), l2e2, nml2), e0, e1);
+      f2_unpack(f2_fma(bf2_as_f2(a.y), l2e2, nml2), e2, e3);
+      f2_unpack(f2_fma(bf2_as_f2(a.z), l2e2, nml2), e4, e5);
+      f2_unpack(f2_fma(bf2_as_f2(a.w), l2e2, nml2), e6, e7);
+      s0 += ex2_approx(e0) + ex2_approx(e1);
+      s1 += ex2_approx(e2) + ex2_approx(e3);
+      s2 += ex2_approx(e4) + ex2_approx(e5);
+      s3 += ex2_approx(e6) + ex2_approx(e7);
+    }
+    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) s0 += ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, nml));
+    const float s = block_sum((s0 + s1) + (s2 + s3), red);
+    if (threadIdx.x == 0) {
+      row_stats[row] = -(x_label - m - logf(s));
+      row_stats[rows + row] = hit;
+    }
+    if (dr == nullptr) continue;
+    // pass 3: dlogits = softmax / n_valid, the label's column minus 1 / n_valid
+    const float c3 = nml + log2f(inv_n / s);
+    const uint64_t c32 = f2_pack(c3, c3);
+    uint4* dv = reinterpret_cast<uint4*>(dr);
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+      const uint4 a = xv[i];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float y0, y1;
+        f2_unpack(f2_fma(bf2_as_f2(w[q]), l2e2, c32), y0, y1);
+        __nv_bfloat162 h = __floats2bfloat162_rn(ex2_approx(y0), ex2_approx(y1));
+        o[q] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      dv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads)
+      dr[c] = __float2bfloat16_rn(ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, c3)));
+    __syncthreads();  // the label's column has been written (by whichever thread owns it) before it is patched
+    if (threadIdx.x == 0) dr[label] = __float2bfloat16_rn(ex2_approx(fmaf(x_label, kLog2e, c3)) - inv_n);
+  }
+}
+
 __global__ void ce_finalize_kernel(const float* __restrict__ row_stats, const float* __restrict__ n_valid,
                                    int64_t rows, float* __restrict__ out3) {
   grid_dep_sync();
@@ -341,6 +466,11 @@ extern "C" int ptj_cross_entropy(const int32_t* labels, const void* logits, void
     launch_k(cross_entropy_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         labels, static_cast<const float*>(logits), static_cast<float*>(dlogits), row_stats, n_valid, rows, cols, ld,
         same_phase<float>(logits, ld, dlogits, ld));
+  } else if (aligned16(logits) && (dlogits == nullptr || aligned16(dlogits)) && ld % 8 == 0 && cols <= 0x7fffffffLL) {
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 3;  // three resident 512-thread blocks per SM
+    launch_k(cross_entropy_bf16_kernel, static_cast<int>(rows < cap ? rows : cap), kCeThreads, 0, st, labels,
+             static_cast<const __nv_bfloat16*>(logits), static_cast<__nv_bfloat16*>(dlogits), row_stats, n_valid, rows,
+             static_cast<int>(cols), ld);
   } else {
     launch_k(cross_entropy_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
         labels, static_cast<const __nv_bfloat16*>(logits), static_cast<__nv_bfloat16*>(dlogits), row_stats, n_valid,

@@ -461,7 +461,10 @@ class Trainer:
                 try:
                     stats = fwd_bwd(self.reducer.mark_ready)
                 finally:
-                    cur[0].capture_end()
+                    import warnings
+                    with warnings.catch_warnings():  # nothing follows the last bucket: the final graph may be empty
+                        warnings.filterwarnings("ignore", message="The CUDA Graph is empty")
+                        cur[0].capture_end()
                 parts.append(cur[0])
         finally:
             self.reducer.on_complete = None

@@ -188,6 +188,35 @@ def test_cross_entropy_label_outside_vocabulary_is_not_counted(ops):
     check(dl, odl, F32_TOL)
 
 
+def test_cross_entropy_bf16_ties_tail_and_label_positions(ops):
+    """The bf16 kernel for 16-byte aligned rows: a vocabulary that is not a multiple of the vector width (scalar tail),
+    labels in the first vector, in the tail and in between, and rows whose maximum occurs twice (the first index
+    wins, as in torch.argmax), against the oracle on the same bf16 values."""
+    rows, cols, ld = 24, 1003, 1008
+    x = rnd(rows, cols, seed=4, scale=2.0).bfloat16()
+    labels = torch.randint(1, cols, (rows,), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+    labels[0], labels[1], labels[2], labels[3] = 1, 7, cols - 1, cols - 3      # first vector / tail
+    x[4, 100] = x[4, 900] = 9.0; labels[4] = 100                               # tie, label is the first maximum
+    x[5, 100] = x[5, 900] = 9.0; labels[5] = 900                               # tie, label is the second one
+    x[6, 1001] = 9.0; labels[6] = 1001                                         # the maximum sits in the scalar tail
+    x[7, 3] = x[7, 1002] = 9.0; labels[7] = 1002
+    labels[8] = 0
+    buf = torch.zeros(rows, ld, dtype=torch.bfloat16)
+    buf[:, :cols] = x
+    buf = gpu(buf)
+    stats, nv, d = ops.cross_entropy(gpu(labels), buf, cols=cols, want_grad=True, in_place=False)
+    ol, on, odl = orc.cross_entropy_fwd_bwd(labels, x.float())
+    check(stats[0].reshape(()), ol.reshape(()), 1e-4)
+    check(d[:, :cols], odl, BF16_TOL)
+    assert float(d[8, :cols].abs().max()) == 0.0 and float(d[:, cols:].abs().max()) == 0.0
+    want_hits = (torch.argmax(x.float(), dim=1).to(torch.int32) == labels) & (labels != 0)
+    assert abs(float(stats[1]) - float(want_hits.sum()) / int(on)) < 1e-6
+    assert bool(want_hits[4]) and not bool(want_hits[5]) and bool(want_hits[6]) and not bool(want_hits[7])
+    # forward only (no gradient buffer): same statistics
+    stats2, _, none = ops.cross_entropy(gpu(labels), buf, cols=cols, want_grad=False)
+    assert none is None and torch.equal(stats, stats2)
+
+
 def test_cross_entropy_all_padding(ops):
     logits = gpu(rnd(4, 16, seed=1))
     labels = gpu(torch.zeros(4, dtype=torch.int32))
