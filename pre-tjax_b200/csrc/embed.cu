@@ -2,6 +2,7 @@
 // (deterministic segmented scatter into the embedding table, batch-sum into the position table), and the
 // deterministic column sum used for bias gradients.
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace ptj {
 namespace {
@@ -36,6 +37,13 @@ embed_fwd_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ w_emb, 
   }
 }
 
+// eight consecutive elements starting at a 16-byte (bf16) / 32-byte (float) aligned address
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) { Elem<__nv_bfloat16>::load_vec(p, v); }
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
 // Gradient w.r.t. the position table: d_w_pos[s, c] = sum_b mask * dy[b, s, c]   (model_triton.py:2518)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -43,18 +51,91 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
                uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
   seed = resolve_seed(seed);
-  const int64_t total = seq * dim;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float s = 0.f;
+  const int64_t total = seq * dim;  // a multiple of 8 (the host checks dim % 8 == 0)
+  const bool masked = train && thr != 0u;
+  const float k_all = train ? 1.f : eval_scale;
+  // eight consecutive features per thread: one 16-byte (bf16) load and one Philox call per batch row
+  for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x * 8) {
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = 0.f;
     for (int64_t b = 0; b < batch; ++b) {
       const int64_t idx = b * total + i;
-      const float k = train ? (dropout_keep(seed, stream_id, static_cast<uint64_t>(idx), thr) ? 1.f : 0.f) : eval_scale;
-      s += Elem<T>::load(dy + idx) * k;
+      float x[8];
+      load8(dy + idx, x);
+      uint32_t keep = 0xffu;
+      if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(idx) >> 3, thr);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
     }
-    d_w_pos[i] = s;
+    *reinterpret_cast<float4*>(d_w_pos + i) = make_float4(s[0], s[1], s[2], s[3]);
+    *reinterpret_cast<float4*>(d_w_pos + i + 4) = make_float4(s[4], s[5], s[6], s[7]);
   }
 }
+
+// Adds rows pos_s[0 .. n) of dy (masked, scaled) into acc: warp w takes rows w, w + 8, ...; lanes run across the
+// features, 8 per vector = one Philox call. Several rows per step: their loads are independent (kept as raw 16-byte
+// pieces until they are added, in row order, so the sums do not depend on the grouping).
+template <typename T, int NV>
+__device__ __forceinline__ void add_rows(const T* __restrict__ dy, const int32_t* pos_s, int n, int dim, int nvec,
+                                     bool masked, float k_all, uint64_t seed, uint32_t stream_id, uint32_t thr,
+                                     float (&acc)[NV][8], int lane, int warp) {
+  constexpr int U = sizeof(T) == 2 ? 4 : 2;    // rows per step
+  constexpr int PV = sizeof(T) == 2 ? 1 : 2;   // 16-byte pieces per 8-element vector
+  for (int r0 = warp; r0 < n; r0 += 8 * U) {
+    uint4 raw[U][NV][PV];
+    int64_t rows_u[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + 8 * u;
+      rows_u[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        if (rows_u[u] >= 0 && v < nvec) {
+          const uint4* src = reinterpret_cast<const uint4*>(dy + rows_u[u] + v * 8);
+#pragma unroll
+          for (int q = 0; q < PV; ++q) raw[u][i][q] = src[q];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (rows_u[u] < 0) continue;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float x[8];
+          if (sizeof(T) == 2) {
+            const uint32_t w[4] = {raw[u][i][0].x, raw[u][i][0].y, raw[u][i][0].z, raw[u][i][0].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              x[2 * e] = __uint_as_float(w[e] << 16);
+              x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < PV; ++q) {
+              x[4 * q] = __uint_as_float(raw[u][i][q].x);
+              x[4 * q + 1] = __uint_as_float(raw[u][i][q].y);
+              x[4 * q + 2] = __uint_as_float(raw[u][i][q].z);
+              x[4 * q + 3] = __uint_as_float(raw[u][i][q].w);
+            }
+          }
+          uint32_t keep = 0xffu;
+          if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(rows_u[u] + v * 8) >> 3, thr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
+        }
+      }
+    }
+  }
+}
+
+constexpr int kHeavyRun = 128;
+constexpr int kHeavyCluster = 8;
 
 // Gradient w.r.t. the embedding table (model_triton.py:183-185, 205-213). Token positions arrive stably sorted by
 // token id; the thread block that lands on the first position of a run of equal ids sums the whole run: the run is
@@ -78,6 +159,8 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
     const int32_t id = ids[sorted_pos[j]];
     if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run (uniform over the block)
     if (id < 0 || id >= vocab) continue;
+    // runs longer than kHeavyRun rows are summed by a cluster of thread blocks (embed_bwd_heavy_kernel)
+    if (j + kHeavyRun < tokens && ids[sorted_pos[j + kHeavyRun]] == id) continue;
     float acc[NV][8];
 #pragma unroll
     for (int i = 0; i < NV; ++i)
@@ -93,59 +176,7 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
       __syncthreads();  // previous batch fully consumed
       pos_s[threadIdx.x] = pos;
       const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
-      // several rows per step: their loads are independent (kept as raw 16-byte pieces until they are added, in row
-      // order, so the sums do not depend on the grouping)
-      constexpr int U = sizeof(T) == 2 ? 4 : 2;    // rows per step
-      constexpr int PV = sizeof(T) == 2 ? 1 : 2;   // 16-byte pieces per 8-element vector
-      for (int r0 = warp; r0 < n; r0 += 8 * U) {
-        uint4 raw[U][NV][PV];
-        int64_t rows_u[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int r = r0 + 8 * u;
-          rows_u[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
-#pragma unroll
-          for (int i = 0; i < NV; ++i) {
-            const int v = lane + 32 * i;
-            if (rows_u[u] >= 0 && v < nvec) {
-              const uint4* src = reinterpret_cast<const uint4*>(dy + rows_u[u] + v * 8);
-#pragma unroll
-              for (int q = 0; q < PV; ++q) raw[u][i][q] = src[q];
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (rows_u[u] < 0) continue;
-#pragma unroll
-          for (int i = 0; i < NV; ++i) {
-            const int v = lane + 32 * i;
-            if (v < nvec) {
-              float x[8];
-              if (sizeof(T) == 2) {
-                const uint32_t w[4] = {raw[u][i][0].x, raw[u][i][0].y, raw[u][i][0].z, raw[u][i][0].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  x[2 * e] = __uint_as_float(w[e] << 16);
-                  x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-                }
-              } else {
-#pragma unroll
-                for (int q = 0; q < PV; ++q) {
-                  x[4 * q] = __uint_as_float(raw[u][i][q].x);
-                  x[4 * q + 1] = __uint_as_float(raw[u][i][q].y);
-                  x[4 * q + 2] = __uint_as_float(raw[u][i][q].z);
-                  x[4 * q + 3] = __uint_as_float(raw[u][i][q].w);
-                }
-              }
-              uint32_t keep = 0xffu;
-              if (masked) keep = dropout_keep_bits8(seed, stream_id, static_cast<uint64_t>(rows_u[u] + v * 8) >> 3, thr);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[i][e] += ((keep >> e) & 1u) ? x[e] * k_all : 0.f;
-            }
-          }
-        }
-      }
+      add_rows<T, NV>(dy, pos_s, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, warp);
       if (n < 256) break;
     }
     __syncthreads();
@@ -167,6 +198,96 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
     }
     __syncthreads();
   }
+}
+
+// The long runs (a Zipf head: the most frequent token of a GPT-2 batch of 8192 tokens occurs about 1 100 times) would
+// each keep one block busy for 100 us while the rest of the GPU idles. Here a cluster of kHeavyCluster blocks shares
+// one run: block r of the cluster sums the r-th slice of the run's rows, the slices' sums meet in block 0 through
+// distributed shared memory and are added in slice order (fixed order, no atomics => reproducible).
+// Work assignment without any helper tensor: cluster k looks at sorted position a = k * kHeavyRun. A run longer than
+// kHeavyRun contains at least one multiple of kHeavyRun; the cluster at the FIRST such multiple owns the run. Every
+// block of a cluster evaluates the same conditions, so a cluster leaves or stays as a whole.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
+embed_bwd_heavy_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids,
+                       const int32_t* __restrict__ sorted_pos, float* __restrict__ d_w_emb, int accumulate,
+                       int64_t tokens, int dim, int64_t vocab, float scale, uint32_t thr, float eval_scale, int train,
+                       uint64_t seed, uint32_t stream_id) {
+  grid_dep_sync();
+  seed = resolve_seed(seed);
+  extern __shared__ float part[];  // [8][dim] per-warp sums, then [dim] this block's sum
+  __shared__ int32_t pos_s[256];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned rank = tc::cluster_ctarank();
+  const int64_t a = static_cast<int64_t>(blockIdx.x) * kHeavyRun;
+  if (a >= tokens) return;
+  const int32_t id = ids[sorted_pos[a]];
+  if (id < 0 || id >= vocab) return;
+  if (a >= kHeavyRun && ids[sorted_pos[a - kHeavyRun]] == id) return;  // an earlier multiple lies in the same run
+  // head of the run: the matches among positions a, a - 1, ..., a - kHeavyRun + 1 are a prefix (ids are sorted)
+  const bool back = tid < kHeavyRun && a - tid >= 0 && ids[sorted_pos[a - tid]] == id;
+  const int64_t head = a - (__syncthreads_count(back) - 1);
+  if (head + kHeavyRun >= tokens || ids[sorted_pos[head + kHeavyRun]] != id) return;  // a short run: the other kernel's
+  // end of the run: probes every 32 positions, then the 32 positions after the last probe that matched
+  int64_t inside = head + kHeavyRun;
+  for (;;) {
+    const int64_t q = inside + (tid + 1) * 32;
+    const int c = __syncthreads_count(q < tokens && ids[sorted_pos[q]] == id);
+    inside += static_cast<int64_t>(c) * 32;
+    if (c < 256) break;
+  }
+  const int64_t qf = inside + 1 + tid;
+  const int64_t end = inside + 1 + __syncthreads_count(tid < 32 && qf < tokens && ids[sorted_pos[qf]] == id);
+  const int64_t len = end - head;
+  const int64_t s0 = head + len * rank / kHeavyCluster, s1 = head + len * (rank + 1) / kHeavyCluster;
+
+  const bool masked = train && thr != 0u;
+  const float k_all = train ? 1.f : eval_scale;
+  const int nvec = dim / 8;
+  float acc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  for (int64_t base = s0; base < s1; base += 256) {
+    const int64_t q = base + tid;
+    __syncthreads();  // previous batch fully consumed
+    pos_s[tid] = q < s1 ? sorted_pos[q] : -1;
+    __syncthreads();
+    const int n = static_cast<int>(s1 - base < 256 ? s1 - base : 256);
+    add_rows<T, NV>(dy, pos_s, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, warp);
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[warp * dim + v * 8 + e] = acc[i][e];
+    }
+  }
+  __syncthreads();
+  float* mine = part + 8 * dim;  // this block's slice sum, warps added in order
+  for (int c = tid; c < dim; c += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += part[w * dim + c];
+    mine[c] = t;
+  }
+  tc::cluster_sync_all();  // every block's slice sum is in its shared memory
+  if (rank == 0) {
+    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
+    for (int c = tid; c < dim; c += blockDim.x) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < kHeavyCluster; ++r) {
+        float v;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(tc::mapa_shared(tc::smem_u32(mine + c), r)));
+        t += v;
+      }
+      out[c] = (accumulate ? out[c] : 0.f) + t * scale;
+    }
+  }
+  tc::cluster_sync_all();  // nobody leaves (and frees its shared memory) before block 0 has read it
 }
 
 // rows of the table that no token hit are zeroed when not accumulating
@@ -352,6 +473,33 @@ int launch_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_p
   if (nv <= 1) PTJ_EMB(1) else if (nv <= 2) PTJ_EMB(2) else if (nv <= 4) PTJ_EMB(4) else if (nv <= 8) PTJ_EMB(8) else PTJ_EMB(16)
 #undef PTJ_EMB
   PTJ_CHECK_LAUNCH();
+  if (tokens <= kHeavyRun) return PTJ_OK;  // no run can be longer than kHeavyRun
+  // the long runs: one cluster of kHeavyCluster blocks per multiple of kHeavyRun among the sorted positions
+  const size_t smem_h = static_cast<size_t>(9) * dim * sizeof(float);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(tokens, kHeavyRun)), kHeavyCluster);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem_h;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = kHeavyCluster;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+#define PTJ_EMB_H(NV)                                                                                                \
+  {                                                                                                                  \
+    if (smem_h > 48 * 1024)                                                                                          \
+      cudaFuncSetAttribute(embed_bwd_heavy_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h); \
+    (void)cudaLaunchKernelEx(&cfg, embed_bwd_heavy_kernel<T, NV>, static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, \
+                             tokens, dim, vocab, scale, thr, eval_scale, train, seed, stream_id);                   \
+  }
+  if (nv <= 1) PTJ_EMB_H(1) else if (nv <= 2) PTJ_EMB_H(2) else if (nv <= 4) PTJ_EMB_H(4) else if (nv <= 8) PTJ_EMB_H(8) else PTJ_EMB_H(16)
+#undef PTJ_EMB_H
+  PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }
 
@@ -402,7 +550,8 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
     PTJ_CHECK_LAUNCH();
   }
   const int grid_e = flat_grid(tokens, 1);  // one block per sorted position (only run heads do work)
-  const int grid_p = flat_grid(seq * dim, 256);
+  if (!aligned16(d_w_pos)) return PTJ_ERR_MISALIGNED;
+  const int grid_p = flat_grid(seq * dim / 8, 256);
   if (dtype == PTJ_F32) {
     if (launch_embed_bwd<float>(dy, ids, sorted_pos, d_w_emb, tokens, (int)dim, vocab, scale, thr, 1.f - p, train, seed,
                                 stream_id, grid_e, st) != PTJ_OK)

@@ -334,6 +334,39 @@ def test_embedding_forward_backward(ops, dtype, tol):
     check(d_emb2, ref_emb - 0.5, tol)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)])
+def test_embedding_backward_long_runs(ops, dtype, tol):
+    """Tokens that occur more than 128 times in a batch are summed by a cluster of thread blocks (slices of the run
+    meet through distributed shared memory): run lengths on both sides of that limit and of the 256-position batch,
+    one run that starts at sorted position 0 and one that ends at the last position, dropout on, against a float64
+    scatter; two calls agree bit for bit."""
+    B, S, D, V, p, seed = 4, 1024, 64, 300, 0.1, 5
+    g = torch.Generator().manual_seed(1)
+    counts = {1: 1500, 9: 128, 11: 129, 17: 257, 21: 600, 299: 200}
+    flat = [t for t, n in counts.items() for _ in range(n)]
+    rest = B * S - len(flat)
+    flat += torch.randint(30, 290, (rest,), generator=g).tolist()
+    ids = torch.tensor(flat, dtype=torch.int32)[torch.randperm(B * S, generator=g)].view(B, S)
+    dy = rnd(B, S, D, seed=3).to(dtype)
+    mask = torch.from_numpy(philox.keep_mask(seed, 0, B * S * D, p)).view(B, S, D)
+    gm = (dy.double() * mask).reshape(-1, D) * math.sqrt(D)
+    ref = torch.zeros(V, D, dtype=torch.float64).index_add_(0, ids.reshape(-1).long(), gm)
+    outs = []
+    for _ in range(2):
+        d_emb = torch.full((V, D), 7.0, device="cuda")
+        d_pos = torch.empty((S, D), device="cuda")
+        ops.embed_bwd(gpu(dy), gpu(ids), d_emb, d_pos, accumulate=False, train=True, seed=seed, p=p)
+        outs.append((d_emb, d_pos))
+    check(outs[0][0], ref.float(), tol)
+    check(outs[0][1], (dy.double() * mask).sum(dim=0).float(), tol)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    # evaluation mode scales instead of masking
+    d_emb = torch.zeros((V, D), device="cuda")
+    ops.embed_bwd(gpu(dy), gpu(ids), d_emb, torch.empty((S, D), device="cuda"), accumulate=True, train=False, seed=seed, p=p)
+    ref_e = torch.zeros(V, D, dtype=torch.float64).index_add_(0, ids.reshape(-1).long(), dy.double().reshape(-1, D) * math.sqrt(D) * (1 - p))
+    check(d_emb, ref_e.float(), tol)
+
+
 @pytest.mark.parametrize("rows,cols", [(1, 1), (100, 7), (513, 300), (2048, 50257)])
 def test_colsum_and_sumsq(ops, rows, cols):
     x = rnd(rows, cols, seed=1)
