@@ -261,6 +261,56 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ uint64_t bf2_as_f2(uint32_t w) {
   return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
+__device__ __forceinline__ uint64_t f2_add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// maximum of a row (every thread gets it): packed bf16 pairs over the 16-byte vectors, the last cols & 7 elements one by one
+__device__ __forceinline__ float row_max_bf16(const __nv_bfloat16* xr, int cols, float* red) {
+  const uint4* xv = reinterpret_cast<const uint4*>(xr);
+  const int nvec = cols >> 3;
+  uint32_t pm = 0xff80ff80u;  // two packed -inf
+  int i = threadIdx.x;
+  for (; i + 3 * kCeThreads < nvec; i += 4 * kCeThreads) {
+    const uint4 a = xv[i], b = xv[i + kCeThreads], c = xv[i + 2 * kCeThreads], d = xv[i + 3 * kCeThreads];
+    pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)), bf2_max(bf2_max(b.x, b.y), bf2_max(b.z, b.w))));
+    pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(c.x, c.y), bf2_max(c.z, c.w)), bf2_max(bf2_max(d.x, d.y), bf2_max(d.z, d.w))));
+  }
+  for (; i < nvec; i += kCeThreads) {
+    const uint4 a = xv[i];
+    pm = bf2_max(pm, bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)));
+  }
+  float m = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xffff0000u));
+  for (int c = (nvec << 3) + threadIdx.x; c < cols; c += kCeThreads) m = fmaxf(m, __bfloat162float(xr[c]));
+  return block_max(m, red);
+}
+
+// sum over the row of 2^(x log2 e + nml), nml = -max log2 e (every thread gets it)
+__device__ __forceinline__ float row_expsum_bf16(const __nv_bfloat16* xr, int cols, float nml, float* red) {
+  const uint4* xv = reinterpret_cast<const uint4*>(xr);
+  const int nvec = cols >> 3;
+  const uint64_t l2e2 = f2_pack(kLog2e, kLog2e), nml2 = f2_pack(nml, nml);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  auto add8 = [&](const uint4& a) {
+    float e0, e1, e2, e3, e4, e5, e6, e7;
+    f2_unpack(f2_fma(bf2_as_f2(a.x), l2e2, nml2), e0, e1);
+    f2_unpack(f2_fma(bf2_as_f2(a.y), l2e2, nml2), e2, e3);
+    f2_unpack(f2_fma(bf2_as_f2(a.z), l2e2, nml2), e4, e5);
+    f2_unpack(f2_fma(bf2_as_f2(a.w), l2e2, nml2), e6, e7);
+    s0 += ex2_approx(e0) + ex2_approx(e1);
+    s1 += ex2_approx(e2) + ex2_approx(e3);
+    s2 += ex2_approx(e4) + ex2_approx(e5);
+    s3 += ex2_approx(e6) + ex2_approx(e7);
+  };
+  // (four loads in flight per thread, as in the maximum pass, measured no faster here: 344 against 340 us)
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) add8(xv[i]);
+  for (int c = (nvec << 3) + threadIdx.x; c < cols; c += kCeThreads) s0 += ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, nml));
+  return block_sum((s0 + s1) + (s2 + s3), red);
+}
 
 __global__ void __launch_bounds__(kCeThreads, 3)
 cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat16* logits, __nv_bfloat16* dlogits,
@@ -271,7 +321,6 @@ cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat1
   const float inv_n = 1.f / *n_valid;
   const int nvec = cols >> 3;        // whole 16-byte vectors; the last cols & 7 elements are walked one by one
   const int tail0 = nvec << 3;
-  constexpr float kLog2e = 1.4426950408889634f;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16* xr = logits + row * ld;
     const uint4* xv = reinterpret_cast<const uint4*>(xr);
@@ -290,22 +339,7 @@ cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat1
     }
     const float x_label = __bfloat162float(xr[label]);  // read before the row is overwritten in place
     // pass 1: maximum
-    uint32_t pm = 0xff80ff80u;  // two packed -inf
-    {
-      int i = threadIdx.x;
-      for (; i + 3 * kCeThreads < nvec; i += 4 * kCeThreads) {
-        const uint4 a = xv[i], b = xv[i + kCeThreads], c = xv[i + 2 * kCeThreads], d = xv[i + 3 * kCeThreads];
-        pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)), bf2_max(bf2_max(b.x, b.y), bf2_max(b.z, b.w))));
-        pm = bf2_max(pm, bf2_max(bf2_max(bf2_max(c.x, c.y), bf2_max(c.z, c.w)), bf2_max(bf2_max(d.x, d.y), bf2_max(d.z, d.w))));
-      }
-      for (; i < nvec; i += kCeThreads) {
-        const uint4 a = xv[i];
-        pm = bf2_max(pm, bf2_max(bf2_max(a.x, a.y), bf2_max(a.z, a.w)));
-      }
-    }
-    float m = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xffff0000u));
-    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) m = fmaxf(m, __bfloat162float(xr[c]));
-    m = block_max(m, red);
+    const float m = row_max_bf16(xr, cols, red);
     // is the label the first column that attains the maximum?
     float hit = 0.f;
     if (x_label == m) {  // (uniform over the block)
@@ -315,22 +349,8 @@ cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat1
     }
     // pass 2: sum of exponentials
     const float nml = -m * kLog2e;
-    const uint64_t l2e2 = f2_pack(kLog2e, kLog2e), nml2 = f2_pack(nml, nml);
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
-      const uint4 a = xv[i];
-      float e0, e1, e2, e3, e4, e5, e6, e7;
-      f2_unpack(f2_fma(bf2_as_f2(a.x), l2e2, nml2), e0, e1);
-      f2_unpack(f2_fma(bf2_as_f2(a.y), l2e2, nml2), e2, e3);
-      f2_unpack(f2_fma(bf2_as_f2(a.z), l2e2, nml2), e4, e5);
-      f2_unpack(f2_fma(bf2_as_f2(a.w), l2e2, nml2), e6, e7);
-      s0 += ex2_approx(e0) + ex2_approx(e1);
-      s1 += ex2_approx(e2) + ex2_approx(e3);
-      s2 += ex2_approx(e4) + ex2_approx(e5);
-      s3 += ex2_approx(e6) + ex2_approx(e7);
-    }
-    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) s0 += ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, nml));
-    const float s = block_sum((s0 + s1) + (s2 + s3), red);
+    const uint64_t l2e2 = f2_pack(kLog2e, kLog2e);
+    const float s = row_expsum_bf16(xr, cols, nml, red);
     if (threadIdx.x == 0) {
       row_stats[row] = -(x_label - m - logf(s));
       row_stats[rows + row] = hit;
@@ -340,8 +360,7 @@ cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat1
     const float c3 = nml + log2f(inv_n / s);
     const uint64_t c32 = f2_pack(c3, c3);
     uint4* dv = reinterpret_cast<uint4*>(dr);
-    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
-      const uint4 a = xv[i];
+    auto grad8 = [&](const uint4& a) {
       const uint32_t w[4] = {a.x, a.y, a.z, a.w};
       uint32_t o[4];
 #pragma unroll
@@ -351,12 +370,95 @@ cross_entropy_bf16_kernel(const int32_t* __restrict__ labels, const __nv_bfloat1
         __nv_bfloat162 h = __floats2bfloat162_rn(ex2_approx(y0), ex2_approx(y1));
         o[q] = *reinterpret_cast<uint32_t*>(&h);
       }
-      dv[i] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+      return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) dv[i] = grad8(xv[i]);
     for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads)
       dr[c] = __float2bfloat16_rn(ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, c3)));
     __syncthreads();  // the label's column has been written (by whichever thread owns it) before it is patched
     if (threadIdx.x == 0) dr[label] = __float2bfloat16_rn(ex2_approx(fmaf(x_label, kLog2e, c3)) - inv_n);
+  }
+}
+
+// log-softmax forward / backward on the same three-pass scheme (bf16, every row on a 16-byte boundary)
+__global__ void __launch_bounds__(kCeThreads, 3)
+log_softmax_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t rows, int cols,
+                            int64_t ld_x, int64_t ld_y) {
+  grid_dep_sync();
+  __shared__ float red[33];
+  const int nvec = cols >> 3;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * ld_x;
+    __nv_bfloat16* yr = y + row * ld_y;
+    const float m = row_max_bf16(xr, cols, red);
+    const float s = row_expsum_bf16(xr, cols, -m * kLog2e, red);
+    const float nshift = -(m + logf(s));
+    const uint64_t ns2 = f2_pack(nshift, nshift);
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    uint4* yv = reinterpret_cast<uint4*>(yr);
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+      const uint4 a = xv[i];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float y0, y1;
+        f2_unpack(f2_add2(bf2_as_f2(w[q]), ns2), y0, y1);
+        __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+        o[q] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      yv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (int c = (nvec << 3) + threadIdx.x; c < cols; c += kCeThreads) yr[c] = __float2bfloat16_rn(__bfloat162float(xr[c]) + nshift);
+  }
+}
+
+// dx = dy - softmax(x) * sum(dy)    (model_triton.py:91-102)
+__global__ void __launch_bounds__(kCeThreads, 3)
+log_softmax_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                            __nv_bfloat16* __restrict__ dx, int64_t rows, int cols, int64_t ld) {
+  grid_dep_sync();
+  __shared__ float red[33];
+  const int nvec = cols >> 3;
+  const int tail0 = nvec << 3;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * ld;
+    const __nv_bfloat16* gr = dy + row * ld;
+    __nv_bfloat16* dr = dx + row * ld;
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    const uint4* gv = reinterpret_cast<const uint4*>(gr);
+    const float m = row_max_bf16(xr, cols, red);
+    const float nml = -m * kLog2e;
+    const float s = row_expsum_bf16(xr, cols, nml, red);
+    uint64_t g0 = 0ull, g1 = 0ull;  // two packed +0.0f each
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+      const uint4 a = gv[i];
+      g0 = f2_add2(g0, f2_add2(bf2_as_f2(a.x), bf2_as_f2(a.y)));
+      g1 = f2_add2(g1, f2_add2(bf2_as_f2(a.z), bf2_as_f2(a.w)));
+    }
+    float ga, gb;
+    f2_unpack(f2_add2(g0, g1), ga, gb);
+    float gs = ga + gb;
+    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads) gs += __bfloat162float(gr[c]);
+    const float nk = -block_sum(gs, red) / s;
+    const uint64_t l2e2 = f2_pack(kLog2e, kLog2e), nml2 = f2_pack(nml, nml), nk2 = f2_pack(nk, nk);
+    uint4* dv = reinterpret_cast<uint4*>(dr);
+    for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+      const uint4 a = xv[i], g = gv[i];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w}, u[4] = {g.x, g.y, g.z, g.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float y0, y1;
+        f2_unpack(f2_fma(bf2_as_f2(w[q]), l2e2, nml2), y0, y1);
+        f2_unpack(f2_fma(f2_pack(ex2_approx(y0), ex2_approx(y1)), nk2, bf2_as_f2(u[q])), y0, y1);
+        __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+        o[q] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      dv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (int c = tail0 + threadIdx.x; c < cols; c += kCeThreads)
+      dr[c] = __float2bfloat16_rn(fmaf(ex2_approx(fmaf(__bfloat162float(xr[c]), kLog2e, nml)), nk, __bfloat162float(gr[c])));
   }
 }
 
@@ -418,6 +520,10 @@ extern "C" int ptj_log_softmax_fwd(const void* x, void* y, int64_t rows, int64_t
   if (dtype == PTJ_F32) {
     launch_k(log_softmax_fwd_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const float*>(x), static_cast<float*>(y), rows, cols, ld_x, ld_y, same_phase<float>(x, ld_x, y, ld_y));
+  } else if (dtype == PTJ_BF16 && aligned16(x) && aligned16(y) && ld_x % 8 == 0 && ld_y % 8 == 0 && cols <= 0x7fffffffLL) {
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 3;
+    launch_k(log_softmax_fwd_bf16_kernel, static_cast<int>(rows < cap ? rows : cap), kCeThreads, 0, st,
+             static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, static_cast<int>(cols), ld_x, ld_y);
   } else if (dtype == PTJ_BF16) {
     launch_k(log_softmax_fwd_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, cols, ld_x, ld_y,
@@ -439,6 +545,11 @@ extern "C" int ptj_log_softmax_bwd(const void* dy, const void* x, void* dx, int6
     const bool vec = same_phase<float>(x, ld, dy, ld) && same_phase<float>(x, ld, dx, ld);
     launch_k(log_softmax_bwd_kernel<float>, row_grid(rows), kRowThreads, 0, st, 
         static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<float*>(dx), rows, cols, ld, vec);
+  } else if (dtype == PTJ_BF16 && aligned16(x) && aligned16(dy) && aligned16(dx) && ld % 8 == 0 && cols <= 0x7fffffffLL) {
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 3;
+    launch_k(log_softmax_bwd_bf16_kernel, static_cast<int>(rows < cap ? rows : cap), kCeThreads, 0, st,
+             static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(dx),
+             rows, static_cast<int>(cols), ld);
   } else if (dtype == PTJ_BF16) {
     const bool vec = same_phase<__nv_bfloat16>(x, ld, dy, ld) && same_phase<__nv_bfloat16>(x, ld, dx, ld);
     launch_k(log_softmax_bwd_kernel<__nv_bfloat16>, row_grid(rows), kRowThreads, 0, st, 
