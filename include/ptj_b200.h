@@ -214,6 +214,28 @@ int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const voi
              int b_kmajor, int in_dtype, int out_dtype, int epilogue, const ptj_dropout_args* dropout,
              int split_k, float* workspace, size_t workspace_floats, void* stream);
 
+/* Two products C_i[M_i, N_i] = op(A_i) op(B_i) (i = 0, 1) in ONE launch: bf16 operands, float32 outputs, the same K and
+ * the same operand layouts for both, epilogue PTJ_EPI_NONE or PTJ_EPI_ACCUM each, optional K split each (own workspace
+ * of split_k * M * N floats). The tiles of both products are dealt to the GPU's thread-block pairs as one list, so two
+ * products that would each occupy half of the GPU (the weight gradients of a transformer layer: 36 tiles of 256 x 256
+ * each for the two FFN matrices at GPT-2 small) share one round instead of each being split over K and reduced by a
+ * second launch. Results are bit-identical to two ptj_gemm calls with the same split_k. Both products must qualify
+ * for the thread-block-pair kernel (M, N >= 256 and K >= 2048 or N >= 8192); otherwise PTJ_ERR_UNSUPPORTED is returned
+ * and nothing is launched: issue two ptj_gemm calls instead. No counterpart in the reference, whose matmuls are
+ * separate launches (model_triton.py:373-398). */
+typedef struct ptj_gemm_problem {
+  const void* a;
+  const void* b;
+  void* c;             /* float32 [M, ldc] */
+  int64_t M, N, lda, ldb, ldc;
+  int epilogue;        /* PTJ_EPI_NONE or PTJ_EPI_ACCUM */
+  int split_k;
+  float* workspace;    /* split_k * M * N floats when split_k > 1, 16-byte aligned */
+  size_t workspace_floats;
+} ptj_gemm_problem;
+int ptj_gemm_grouped2(const ptj_gemm_problem* p0, const ptj_gemm_problem* p1, int64_t K, int a_kmajor, int b_kmajor,
+                      void* stream);
+
 /* ---- causal scaled-dot-product attention ----------------------------------------------------------- */
 /* Replaces t_scaled_dot_prod_attn_fwd3_t (model_triton.py:706-754) and t_scaled_dot_prod_attn_bkwd3_t
  * (:951-1003): O = dropout(softmax(causal(Q K^T / sqrt(d)))) V with the dropout applied to the probabilities.

@@ -19,6 +19,12 @@ class DropoutArgs(ctypes.Structure):
     _fields_ = [("p", c_float), ("train", c_int), ("seed", c_uint64), ("stream_id", c_uint32)]
 
 
+class GemmProblem(ctypes.Structure):
+    _fields_ = [("a", c_void_p), ("b", c_void_p), ("c", c_void_p), ("M", c_int64), ("N", c_int64), ("lda", c_int64),
+                ("ldb", c_int64), ("ldc", c_int64), ("epilogue", c_int), ("split_k", c_int), ("workspace", c_void_p),
+                ("workspace_floats", c_size_t)]
+
+
 class AttnShape(ctypes.Structure):
     _fields_ = [
         ("batch", c_int64), ("heads", c_int64), ("seq", c_int64), ("d_head", c_int64),
@@ -56,6 +62,7 @@ _SIGNATURES = {
     "ptj_colsum": (c_int, [_P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_gemm": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
                          c_int, c_int, c_int, POINTER(DropoutArgs), c_int, _P, c_size_t, _P]),
+    "ptj_gemm_grouped2": (c_int, [POINTER(GemmProblem), POINTER(GemmProblem), c_int64, c_int, c_int, _P]),
     "ptj_attn_keep_bits_bytes": (c_size_t, [POINTER(AttnShape), c_int]),
     "ptj_attn_keep_bits": (c_int, [_P, POINTER(AttnShape), c_float, c_uint64, c_uint32, c_int, _P]),
     "ptj_attn_fwd": (c_int, [_P, _P, _P, _P, _P, _P, POINTER(AttnShape), c_float, c_int, c_uint64, c_uint32, _P, _P, c_int,

@@ -427,10 +427,15 @@ struct PairCfg {
   static constexpr int kAccStride = 256;
 };
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool SIDE>
+// GROUPED: the launch carries a second product (its own operand maps and parameters; same K-block size, operand layouts
+// and template arguments): work items [0, items1) belong to the first product, the rest to the second, dealt to the
+// pairs as one list. Two products that would each occupy half of the pairs then run side by side in one round.
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool SIDE, bool GROUPED = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ StoreMaps smaps, const GemmParams p) {
+                    const __grid_constant__ StoreMaps smaps, const __grid_constant__ GemmParams p,
+                    const __grid_constant__ CUtensorMap tmap_a2, const __grid_constant__ CUtensorMap tmap_b2,
+                    const __grid_constant__ GemmParams p2, const int items1) {
   using Cfg = PairCfg<BN>;
   constexpr int HB = BN / 2;  // B rows held by one CTA
   extern __shared__ uint8_t smem_raw[];
@@ -468,6 +473,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (GROUPED) {
+      prefetch_tensormap(&tmap_a2);
+      prefetch_tensormap(&tmap_b2);
+    }
     if (SIDE) prefetch_tensormap(&smaps.s);
   }
   __syncthreads();
@@ -482,8 +491,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   grid_dep_sync();  // set-up above touches no global memory; everything below may
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles = p.num_m * p.num_n;  // num_m counts 256-row tiles here
-  const int total = tiles * p.split_k;
+  // (num_m counts 256-row tiles here)
+  const int total = GROUPED ? items1 + p2.num_m * p2.num_n * p2.split_k : items1;
   const int pair = static_cast<int>(blockIdx.x) >> 1, npairs = static_cast<int>(gridDim.x) >> 1;
   if (warp < kFirstEpilogueWarp) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
 
@@ -493,12 +502,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int item = pair; item < total && ok; item += npairs) {
-        const int split = item / tiles, tile = item - split * tiles;
-        const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
-        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
-        if (p.split_k > 1) {
-          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        const bool second = GROUPED && item >= items1;
+        const GemmParams& q = second ? p2 : p;
+        const CUtensorMap* map_a = second ? &tmap_a2 : &tmap_a;
+        const CUtensorMap* map_b = second ? &tmap_b2 : &tmap_b;
+        const int li = second ? item - items1 : item;
+        const int tiles = q.num_m * q.num_n;
+        const int split = li / tiles, tile = li - split * tiles;
+        const int m_blk = tile % q.num_m, n_blk = tile / q.num_m;
+        int kb0 = 0, kb1 = q.num_kb;  // (64-bit divisions only when K is split)
+        if (q.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * q.num_kb / q.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * q.num_kb / q.split_k);
         }
         const int m0 = m_blk * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = n_blk * BN + static_cast<int>(rank) * HB;
@@ -509,16 +524,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           if (A_KMAJOR) {
-            tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0);
+            tma_load_2d_pair(sa, map_a, leader_full, kb * BK, m0);
           } else {
 #pragma unroll
-            for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(sa + h * 8192, &tmap_a, leader_full, m0 + h * 64, kb * BK);
+            for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(sa + h * 8192, map_a, leader_full, m0 + h * 64, kb * BK);
           }
           if (B_KMAJOR) {
-            tma_load_2d_pair(sb, &tmap_b, leader_full, kb * BK, n0);
+            tma_load_2d_pair(sb, map_b, leader_full, kb * BK, n0);
           } else {
 #pragma unroll
-            for (int h = 0; h < HB / 64; ++h) tma_load_2d_pair(sb + h * 8192, &tmap_b, leader_full, n0 + h * 64, kb * BK);
+            for (int h = 0; h < HB / 64; ++h) tma_load_2d_pair(sb + h * 8192, map_b, leader_full, n0 + h * 64, kb * BK);
           }
           if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
@@ -532,11 +547,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int it = 0;
       bool ok = true;
       for (int item = pair; item < total && ok; item += npairs, ++it) {
-        const int split = item / tiles;
-        int kb0 = 0, kb1 = p.num_kb;  // (64-bit divisions only when K is split)
-        if (p.split_k > 1) {
-          kb0 = static_cast<int>(static_cast<int64_t>(split) * p.num_kb / p.split_k);
-          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.num_kb / p.split_k);
+        const bool second = GROUPED && item >= items1;
+        const GemmParams& q = second ? p2 : p;
+        const int split = (second ? item - items1 : item) / (q.num_m * q.num_n);
+        int kb0 = 0, kb1 = q.num_kb;  // (64-bit divisions only when K is split)
+        if (q.split_k > 1) {
+          kb0 = static_cast<int>(static_cast<int64_t>(split) * q.num_kb / q.split_k);
+          kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * q.num_kb / q.split_k);
         }
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
@@ -574,19 +591,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint64_t seed = p.ep.mode == PTJ_EPI_DROPOUT_RESID ? resolve_seed(p.ep.seed) : 0ull;
     SidePrefetch sp{SIDE ? strips + (warp - kFirstEpilogueWarp) * kStrip + kEpiBlockBytes : nullptr, &side_bars[warp - kFirstEpilogueWarp], 0u};
     for (int item = pair; item < total && ok; item += npairs, ++it) {
-      const int split = item / tiles, tile = item - split * tiles;
-      const int m_blk = tile % p.num_m, n_blk = tile / p.num_m;
+      const bool second = GROUPED && item >= items1;
+      const GemmParams& q = second ? p2 : p;
+      const int li = second ? item - items1 : item;
+      const int tiles = q.num_m * q.num_n;
+      const int split = li / tiles, tile = li - split * tiles;
+      const int m_blk = tile % q.num_m, n_blk = tile / q.num_m;
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       float* wbias = bias_smem + (warp - kFirstEpilogueWarp) * (kChunks * 32);
-      const bool bias_staged = p.ep.bias != nullptr && p.split_k == 1;
+      const bool bias_staged = q.ep.bias != nullptr && q.split_k == 1;
       if (bias_staged) {
         // this warp's slice of the tile's bias, fetched while the tile is still being multiplied
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < kChunks; ++j) {
           const int64_t n = static_cast<int64_t>(n_blk) * BN + (sub + j * kWarpsPerQuarter) * 32 + lane;
-          wbias[j * 32 + lane] = n < p.N ? __ldg(p.ep.bias + n) : 0.f;
+          wbias[j * 32 + lane] = n < q.N ? __ldg(q.ep.bias + n) : 0.f;
         }
         __syncwarp();
       }
@@ -595,7 +616,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (SIDE) {
         // the side input of this warp's first block of the tile, requested before the accumulator is even complete
         const int64_t nf = static_cast<int64_t>(n_blk) * BN + sub * 32;
-        if (row0 < p.M && nf < p.N) side_prefetch_issue(sp, &smaps.s, row0, nf, lane);
+        if (row0 < q.M && nf < q.N) side_prefetch_issue(sp, &smaps.s, row0, nf, lane);
       }
       ok = mbar_wait(&tmem_full[buf], aphase, ctx, 0x0601u);
       ok = __all_sync(0xffffffffu, ok);
@@ -616,23 +637,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int64_t n0 = static_cast<int64_t>(n_blk) * BN + col;
         uint8_t* strip = strips + (warp - kFirstEpilogueWarp) * kStrip;
         const float* bias_c = bias_staged ? wbias + chunk * 32 : nullptr;
-        if (p.split_k > 1) {
-          float* w = p.workspace + static_cast<int64_t>(split) * p.M * p.N;
-          if ((p.N & 3) == 0 && n0 + 32 <= p.N) {
-            warp_store_block<float>(strip, w, p.N, row0, n0, p.M, acc, lane);
-          } else if (row < p.M) {
+        if (q.split_k > 1) {
+          float* w = q.workspace + static_cast<int64_t>(split) * q.M * q.N;
+          if ((q.N & 3) == 0 && n0 + 32 <= q.N) {
+            warp_store_block<float>(strip, w, q.N, row0, n0, q.M, acc, lane);
+          } else if (row < q.M) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) w[row * p.N + n0 + j] = acc[j];
+              if (n0 + j < q.N) w[row * q.N + n0 + j] = acc[j];
           }
-        } else if (p.out_bf16) {
+        } else if (q.out_bf16) {
           const int ncol = (sub + (chunk + 1) * kWarpsPerQuarter) * 32;  // this warp's next block of the tile, if any
           const int64_t next_n0 = ncol < BN ? static_cast<int64_t>(n_blk) * BN + ncol : -1;
-          tile_epilogue<__nv_bfloat16, SIDE>(p.ep, strip, row0, row, n0, acc, lane, bias_c,
-                                             p.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok, seed);
+          tile_epilogue<__nv_bfloat16, SIDE>(q.ep, strip, row0, row, n0, acc, lane, bias_c,
+                                             q.tma_store ? &smaps : nullptr, sp, ctx, next_n0, ok, seed);
           if (!ok) break;
         } else {
-          tile_epilogue<float, false>(p.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok, seed);
+          tile_epilogue<float, false>(q.ep, strip, row0, row, n0, acc, lane, bias_c, nullptr, sp, ctx, -1, ok, seed);
         }
       }
       tc_fence_before_sync();
@@ -792,15 +813,18 @@ int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int6
   return PTJ_OK;
 }
 
-template <int BN, bool AK, bool BK_, bool SIDE>
+// p2 != nullptr: a second product in the same launch (see GROUPED above)
+template <int BN, bool AK, bool BK_, bool SIDE, bool GROUPED = false>
 int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm, const GemmParams& p,
-                   cudaStream_t st) {
+                   cudaStream_t st, const CUtensorMap* ta2 = nullptr, const CUtensorMap* tb2 = nullptr,
+                   const GemmParams* p2 = nullptr) {
   using Cfg = PairCfg<BN>;
   const int smem_bytes = Cfg::smem_bytes(SIDE ? 2 * kEpiBlockBytes : kStripBytes);
-  auto kern = gemm_tc_pair_kernel<BN, AK, BK_, SIDE>;
+  auto kern = gemm_tc_pair_kernel<BN, AK, BK_, SIDE, GROUPED>;
   static std::atomic<uint64_t> attr_done{0};
   if (!ensure_max_smem(kern, attr_done)) return PTJ_ERR_LAUNCH;
-  const int total = p.num_m * p.num_n * p.split_k;
+  const int items1 = p.num_m * p.num_n * p.split_k;
+  const int total = items1 + (GROUPED ? p2->num_m * p2->num_n * p2->split_k : 0);
   const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
@@ -816,12 +840,34 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, sm, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, sm, p, GROUPED ? *ta2 : ta, GROUPED ? *tb2 : tb, GROUPED ? *p2 : p, items1) !=
+      cudaSuccess) {
     (void)cudaGetLastError();
     return PTJ_ERR_LAUNCH;
   }
   count_launch(1);
   return PTJ_OK;
+}
+
+// Operand tensor maps of the thread-block-pair kernel (256 x 256 tiles: each CTA loads 128 rows of A and 128 of B).
+bool make_pair_operand_maps(CUtensorMap* ta, CUtensorMap* tb, const void* a, const void* b, int64_t M, int64_t N,
+                            int64_t K, int64_t lda, int64_t ldb, bool a_kmajor, bool b_kmajor) {
+  const int pbn = 256;
+  {
+    const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t dims_mn[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
+    const uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    const uint32_t box_k[2] = {64, 128}, box_mn[2] = {64, 64};
+    if (!make_tmap_bf16(ta, a, 2, a_kmajor ? dims_k : dims_mn, str, a_kmajor ? box_k : box_mn)) return false;
+  }
+  {
+    const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t dims_mn[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    const uint32_t box_k[2] = {64, static_cast<uint32_t>(pbn / 2)}, box_mn[2] = {64, 64};
+    if (!make_tmap_bf16(tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return false;
+  }
+  return true;
 }
 
 // Which kernel: the CTA-pair kernel halves the shared-memory traffic per FLOP and wins wherever the main loop is
@@ -929,24 +975,10 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   }
 
   if (use_pair_kernel(M, N, K)) {
-    const int pbn = 256;
     p.num_m = static_cast<int>(ceil_div(M, 2 * BM));
-    p.num_n = static_cast<int>(ceil_div(N, pbn));
+    p.num_n = static_cast<int>(ceil_div(N, 256));
     CUtensorMap ta, tb;
-    {
-      const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
-      const uint64_t dims_mn[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
-      const uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
-      const uint32_t box_k[2] = {64, 128}, box_mn[2] = {64, 64};
-      if (!make_tmap_bf16(&ta, a, 2, a_kmajor ? dims_k : dims_mn, str, a_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
-    }
-    {
-      const uint64_t dims_k[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
-      const uint64_t dims_mn[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
-      const uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
-      const uint32_t box_k[2] = {64, static_cast<uint32_t>(pbn / 2)}, box_mn[2] = {64, 64};
-      if (!make_tmap_bf16(&tb, b, 2, b_kmajor ? dims_k : dims_mn, str, b_kmajor ? box_k : box_mn)) return PTJ_ERR_LAUNCH;
-    }
+    if (!make_pair_operand_maps(&ta, &tb, a, b, M, N, K, lda, ldb, a_kmajor != 0, b_kmajor != 0)) return PTJ_ERR_LAUNCH;
     int prc;
     if (p.tma_side)  // (A is K-major whenever tma_side is set)
       prc = b_kmajor ? launch_tc_pair<256, true, true, true>(ta, tb, smaps, p, st)
@@ -1002,4 +1034,68 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   if (rc != PTJ_OK) return rc;
 
   return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
+}
+
+// ---- two products in one launch -----------------------------------------------------------------------------------
+namespace {
+// parameters of one product of ptj_gemm_grouped2 for the thread-block-pair kernel (float32 output, no bias, no side input)
+int make_grouped_problem(const ptj_gemm_problem& g, int64_t K, int a_kmajor, int b_kmajor, CUtensorMap* ta,
+                         CUtensorMap* tb, GemmParams* out) {
+  if (!g.a || !g.b || !g.c || g.M < 1 || g.N < 1) return PTJ_ERR_BAD_SHAPE;
+  if (g.M > (1LL << 30) || g.N > (1LL << 30)) return PTJ_ERR_BAD_SHAPE;
+  if (g.lda < (a_kmajor ? K : g.M) || g.ldb < (b_kmajor ? K : g.N) || g.ldc < g.N) return PTJ_ERR_BAD_SHAPE;
+  if (g.epilogue != PTJ_EPI_NONE && g.epilogue != PTJ_EPI_ACCUM) return PTJ_ERR_UNSUPPORTED;
+  if (!aligned16(g.a) || !aligned16(g.b) || g.lda % 8 != 0 || g.ldb % 8 != 0) return PTJ_ERR_MISALIGNED;
+  if (!use_pair_kernel(g.M, g.N, K)) return PTJ_ERR_UNSUPPORTED;
+  const int num_kb = static_cast<int>(ceil_div(K, BK));
+  int split_k = g.split_k < 1 ? 1 : g.split_k;
+  if (split_k > num_kb) split_k = num_kb;
+  if (split_k > 1 && (!g.workspace || g.workspace_floats < static_cast<size_t>(split_k) * g.M * g.N ||
+                      !aligned16(g.workspace)))
+    return PTJ_ERR_WORKSPACE;
+  GemmParams p{};
+  p.ep.c = g.c;
+  p.ep.M = g.M;
+  p.ep.N = g.N;
+  p.ep.ldc = g.ldc;
+  p.ep.mode = g.epilogue;
+  p.ep.vec_ok = aligned16(g.c) && (g.ldc * 4) % 16 == 0;
+  p.M = g.M;
+  p.N = g.N;
+  p.K = K;
+  p.num_m = static_cast<int>(ceil_div(g.M, 2 * BM));
+  p.num_n = static_cast<int>(ceil_div(g.N, 256));
+  p.num_kb = num_kb;
+  p.split_k = split_k;
+  p.workspace = g.workspace;
+  p.fault = tc::fault_word();
+  if (p.fault == nullptr) return PTJ_ERR_DEVICE;
+  if (static_cast<int64_t>(p.num_m) * p.num_n * split_k > 0x3fffffffLL) return PTJ_ERR_BAD_SHAPE;
+  if (!make_pair_operand_maps(ta, tb, g.a, g.b, g.M, g.N, K, g.lda, g.ldb, a_kmajor != 0, b_kmajor != 0))
+    return PTJ_ERR_LAUNCH;
+  *out = p;
+  return PTJ_OK;
+}
+}  // namespace
+
+extern "C" int ptj_gemm_grouped2(const ptj_gemm_problem* g0, const ptj_gemm_problem* g1, int64_t K, int a_kmajor,
+                                 int b_kmajor, void* stream) {
+  if (!g0 || !g1 || K < 1 || K > (1LL << 30)) return PTJ_ERR_BAD_SHAPE;
+  if (ptj_device_check() != PTJ_OK) return PTJ_ERR_DEVICE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap ta0, tb0, ta1, tb1;
+  GemmParams p0, p1;
+  int rc = make_grouped_problem(*g0, K, a_kmajor, b_kmajor, &ta0, &tb0, &p0);
+  if (rc != PTJ_OK) return rc;
+  rc = make_grouped_problem(*g1, K, a_kmajor, b_kmajor, &ta1, &tb1, &p1);
+  if (rc != PTJ_OK) return rc;
+  const StoreMaps none{};
+  rc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1)
+                            : launch_tc_pair<256, true, false, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1))
+                : (b_kmajor ? launch_tc_pair<256, false, true, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1)
+                            : launch_tc_pair<256, false, false, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1));
+  if (rc != PTJ_OK) return rc;
+  rc = finish_split_k(p0.workspace, g0->c, nullptr, g0->M, g0->N, g0->ldc, p0.split_k, g0->epilogue, PTJ_F32, st);
+  if (rc != PTJ_OK) return rc;
+  return finish_split_k(p1.workspace, g1->c, nullptr, g1->M, g1->N, g1->ldc, p1.split_k, g1->epilogue, PTJ_F32, st);
 }

@@ -156,6 +156,9 @@ class Gpt2Step:
         # (measured 0.1 ms per GPT-2 small step faster), or, when set, a plain GEMM followed by ONE elementwise pass
         # that applies gelu' and sums the columns. Same results.
         self.split_gelu_bwd = False
+        # the two FFN weight gradients of a layer in one launch, and the QKV + out-projection pair in another
+        self.pair_wgrads = True
+        self._ws2 = [None, None]
 
     # -- helpers --
     def _wgrad(self, dy2d, x2d, out, accumulate=False):
@@ -171,6 +174,40 @@ class Gpt2Step:
         ops.gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, M=M, N=N, K=T, lda=dy2d.stride(0), ldb=x2d.stride(0),
                  out=out.view(M, N), epilogue=_lib.EPI_ACCUM if accumulate else _lib.EPI_NONE, split_k=split,
                  workspace=self._ws)
+
+    def _wgrad2(self, first, second):
+        """Two weight gradients (dy, x, out) in ONE launch of the thread-block-pair kernel when both qualify: their
+        tiles share the 74 pairs, so the two FFN matrices (36 tiles each at GPT-2 small) need no K split and no reduce
+        launch, and the QKV + out-projection pair (27 + 9 tiles) is split in two parts instead of five and eight.
+        Falls back to two launches."""
+        (dy0, x0, out0), (dy1, x1, out1) = first, second
+        T = dy0.shape[0]
+        ok = dy0.dtype == torch.bfloat16 and dy1.shape[0] == T and self.pair_wgrads
+        if ok:
+            tiles = sum(-(-o.shape[0] // 256) * -(-x.shape[1] // 256) for o, x in ((out0, x0), (out1, x1)))
+            out_mb = max(out0.shape[0] * x0.shape[1], out1.shape[0] * x1.shape[1]) * 4e-6
+            k_blocks = max(1, T // 64)
+            best, best_cost = 1, float("inf")
+            for s_ in range(1, 9):  # the cost model of split_k_for, on the tiles of both products
+                if s_ > max(1, k_blocks // 4):
+                    break
+                cost = -(-tiles * s_ // 74) / s_ + 0.0032 * out_mb * (8192.0 / max(T, 1)) * s_ * (s_ > 1)
+                if cost < best_cost - 1e-9:
+                    best, best_cost = s_, cost
+            probs = []
+            for i, (dy, x, out) in enumerate(((dy0, x0, out0), (dy1, x1, out1))):
+                M, N = out.shape[0], x.shape[1]
+                ws = None
+                if best > 1:
+                    ws = self._ws2[i]
+                    if ws is None or ws.numel() < best * M * N:
+                        ws = self._ws2[i] = torch.empty(best * M * N, device=out.device, dtype=torch.float32)
+                probs.append(dict(a=dy, b=x, out=out.view(M, N), lda=dy.stride(0), ldb=x.stride(0), split_k=best,
+                                  workspace=ws))
+            ok = ops.gemm_grouped2(probs, T, a_kmajor=False, b_kmajor=False)
+        if not ok:
+            self._wgrad(dy0, x0, out0)
+            self._wgrad(dy1, x1, out1)
 
     def _dgrad(self, dy2d, w2d, cols=None, **kw):
         """dx[T, N_in] = dy[T, N_out] w[N_out, N_in]: w is the 'MN-major' B operand."""
@@ -265,14 +302,14 @@ class Gpt2Step:
             if dy is None:
                 dy = ops.dropout(dx, train, s_res2, p=p)
                 ops.colsum(dy, out=G("b2f"))
-            self._wgrad(dy, a["h_act"], G("w2"))
+            dy_ffn = dy
             if self.split_gelu_bwd and F % 8 == 0 and F <= 8192:
                 # plain product, then one elementwise pass that applies gelu' in place and sums the columns (b1f)
                 dh_pre, _ = ops.gelu_bwd_colsum(self._dgrad(dy, g("w2")), a["h_pre"], colsum_out=G("b1f"), in_place=True)
             else:
                 dh_pre = self._dgrad(dy, g("w2"), epilogue=_lib.EPI_GELU_BWD, aux=a["h_pre"])
                 ops.colsum(dh_pre, out=G("b1f"))
-            self._wgrad(dh_pre, a["ln2"], G("w1"))
+            self._wgrad2((dy_ffn, a["h_act"], G("w2")), (dh_pre, a["ln2"], G("w1")))
             d_ln2 = self._dgrad(dh_pre, g("w1"))
             dx, dy = self._ln_bwd(d_ln2, g("g2"), a["x_mid"], G("g2"), G("b2"), dx_add=dx,
                                   dropped=(train, s_res1, p) if fuse else None)
@@ -280,7 +317,7 @@ class Gpt2Step:
             # x_mid = x + dropout(attn(ln1(x)) W_o^T)
             if dy is None:
                 dy = ops.dropout(dx, train, s_res1, p=p)
-            self._wgrad(dy, a["attn"], G("w_o"))
+            dy_attn = dy
             d_attn = self._dgrad(dy, g("w_o"))
             dqkv = torch.empty((T, 3 * D), device=dy.device, dtype=self.dtype)
             qkv5, dqkv5 = a["qkv"].view(B, S, H, 3, dh), dqkv.view(B, S, H, 3, dh)
@@ -290,7 +327,7 @@ class Gpt2Step:
             do4 = d_attn.view(B, S, H, dh).permute(0, 2, 1, 3)
             ops.attn_bwd(do4, q, k, v, o4, a["m"], a["l"], dq, dk, dv, train, s_attn, p=p, keep_bits=a.get("keep"),
                          row_kstart=acts.get("row_kstart"))
-            self._wgrad(dqkv, a["ln1"], G("w_qkv").view(3 * D, D))
+            self._wgrad2((dqkv, a["ln1"], G("w_qkv").view(3 * D, D)), (dy_attn, a["attn"], G("w_o")))
             d_ln1 = self._dgrad(dqkv, g("w_qkv").view(3 * D, D))
             s_prev = seeds[3 * l] if l > 0 else 0  # the layer below's second residual dropout consumes this dx
             dx, dy = self._ln_bwd(d_ln1, g("g1"), a["x"], G("g1"), G("b1"), dx_add=dx,

@@ -139,6 +139,8 @@ def main():
             ("gemm wgrad ffn1     dh^T x   [3072,768] (+split-K reduce)", lambda: step._wgrad(y_f, x_d, g_w1), 2 * T * F * D),
             ("gemm wgrad out-proj dy^T a   [768,768] (+split-K reduce)", lambda: step._wgrad(y_d, x_d, g_wo), 2 * T * D * D),
             ("gemm wgrad qkv      dqkv^T x [2304,768] (+split-K reduce)", lambda: step._wgrad(y_qkv, x_d, g_wqkv), 2 * T * 3 * D * D),
+            ("gemm wgrad ffn2 + ffn1 in one launch (no K split, no reduce)", lambda: step._wgrad2((y_d, x_f, g_w2), (y_f, x_d, g_w1)), 4 * T * F * D),
+            ("gemm wgrad qkv + out-proj in one launch (K in two parts each)", lambda: step._wgrad2((y_qkv, x_d, g_wqkv), (y_d, x_d, g_wo)), 2 * T * 4 * D * D),
             ("gemm wgrad lm-head  dlogits^T x [50257,768]", lambda: step._head_wgrad(logits, x_d, g_emb), 2 * T * V * D),
         ]
         for name, fn, fl in cases:

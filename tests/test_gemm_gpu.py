@@ -196,3 +196,43 @@ def test_pair_kernel_weight_gradient_split_k_accumulate(ops, split, N_out, N_in)
     ops.gemm(dY.cuda(), X.cuda(), out=base, epilogue=lib.EPI_ACCUM, **kw)
     assert rel_err(base, ref - 0.5) < 1e-3
     no_fault(ops)
+
+
+@pytest.mark.parametrize("layout", [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("shapes,K,splits", [
+    (((3072, 768), (768, 3072)), 4096, (1, 1)),      # the two FFN weight gradients: 36 + 36 tiles, one round
+    (((2304, 768), (768, 768)), 4096, (2, 2)),       # QKV + out-projection, K in two parts each
+    (((520, 296), (264, 1032)), 2048, (1, 3)),       # ragged edges, different splits, second product accumulates
+])
+def test_two_products_in_one_launch_match_two_launches(ops, layout, shapes, K, splits):
+    """ptj_gemm_grouped2 deals the tiles of two products to the thread-block pairs as one list: results must equal two
+    separate launches with the same K split bit for bit, and the float64 product within tolerance."""
+    lib = pkg("_lib")
+    a_k, b_k = layout
+    probs, refs, singles = [], [], []
+    for i, ((M, N), s) in enumerate(zip(shapes, splits)):
+        A, B = rnd(M, K, seed=41 + i, scale=0.1), rnd(N, K, seed=51 + i)
+        a_dev = (A if a_k else A.t().contiguous()).cuda()
+        b_dev = (B if b_k else B.t().contiguous()).cuda()
+        acc = i == 1 and len(set(splits)) > 1
+        out = torch.full((M, N), 0.25 if acc else float("nan"), device="cuda")
+        one = out.clone()
+        ops.gemm(a_dev, b_dev, a_kmajor=a_k, b_kmajor=b_k, M=M, N=N, K=K, out=one, split_k=s,
+                 epilogue=lib.EPI_ACCUM if acc else lib.EPI_NONE)
+        singles.append(one)
+        refs.append(A.double() @ B.double().t() + (0.25 if acc else 0.0))
+        probs.append(dict(a=a_dev, b=b_dev, out=out, lda=a_dev.stride(0), ldb=b_dev.stride(0), split_k=s, accumulate=acc))
+    assert ops.gemm_grouped2(probs, K, a_kmajor=a_k, b_kmajor=b_k)
+    no_fault(ops)
+    for pr, one, ref in zip(probs, singles, refs):
+        assert rel_err(pr["out"], ref) < 1e-3
+        assert torch.equal(pr["out"], one), "grouped and separate launches walk K in the same order"
+
+
+def test_grouped_launch_refuses_small_products(ops):
+    """Products the thread-block-pair kernel does not take are refused as a pair (nothing is launched)."""
+    a, b = rnd(128, 256, seed=1).cuda(), rnd(128, 256, seed=2).cuda()
+    out = torch.zeros(128, 128, device="cuda")
+    pr = dict(a=a, b=b, out=out, lda=256, ldb=256)
+    assert ops.gemm_grouped2([dict(pr), dict(pr)], 256) is False
+    assert float(out.abs().max()) == 0.0
