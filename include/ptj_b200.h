@@ -214,9 +214,10 @@ int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const voi
              int b_kmajor, int in_dtype, int out_dtype, int epilogue, const ptj_dropout_args* dropout,
              int split_k, float* workspace, size_t workspace_floats, void* stream);
 
-/* Two products C_i[M_i, N_i] = op(A_i) op(B_i) (i = 0, 1) in ONE launch: bf16 operands, float32 outputs, the same K and
- * the same operand layouts for both, epilogue PTJ_EPI_NONE or PTJ_EPI_ACCUM each, optional K split each (own workspace
- * of split_k * M * N floats). The tiles of both products are dealt to the GPU's thread-block pairs as one list, so two
+/* Two products C_i[M_i, N_i] = op(A_i) op(B_i) (i = 0, 1) in ONE launch: bf16 operands, float32 or bf16 outputs, the
+ * same K and the same operand layouts for both, epilogue PTJ_EPI_NONE or (float32 output) PTJ_EPI_ACCUM each, optional
+ * K split each (own workspace of split_k * M * N floats). The two may also be row ranges of ONE product, the second
+ * split over K, which evens out a last round of tiles that would leave most of the GPU idle. The tiles of both products are dealt to the GPU's thread-block pairs as one list, so two
  * products that would each occupy half of the GPU (the weight gradients of a transformer layer: 36 tiles of 256 x 256
  * each for the two FFN matrices at GPT-2 small) share one round instead of each being split over K and reduced by a
  * second launch. Results are bit-identical to two ptj_gemm calls with the same split_k. Both products must qualify
@@ -226,9 +227,10 @@ int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const voi
 typedef struct ptj_gemm_problem {
   const void* a;
   const void* b;
-  void* c;             /* float32 [M, ldc] */
+  void* c;             /* [M, ldc] of out_dtype */
   int64_t M, N, lda, ldb, ldc;
-  int epilogue;        /* PTJ_EPI_NONE or PTJ_EPI_ACCUM */
+  int out_dtype;       /* PTJ_F32 or PTJ_BF16 */
+  int epilogue;        /* PTJ_EPI_NONE or PTJ_EPI_ACCUM (float32 output only) */
   int split_k;
   float* workspace;    /* split_k * M * N floats when split_k > 1, 16-byte aligned */
   size_t workspace_floats;

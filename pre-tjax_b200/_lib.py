@@ -21,7 +21,8 @@ class DropoutArgs(ctypes.Structure):
 
 class GemmProblem(ctypes.Structure):
     _fields_ = [("a", c_void_p), ("b", c_void_p), ("c", c_void_p), ("M", c_int64), ("N", c_int64), ("lda", c_int64),
-                ("ldb", c_int64), ("ldc", c_int64), ("epilogue", c_int), ("split_k", c_int), ("workspace", c_void_p),
+                ("ldb", c_int64), ("ldc", c_int64), ("out_dtype", c_int), ("epilogue", c_int), ("split_k", c_int),
+                ("workspace", c_void_p),
                 ("workspace_floats", c_size_t)]
 
 

@@ -1038,13 +1038,17 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
 
 // ---- two products in one launch -----------------------------------------------------------------------------------
 namespace {
-// parameters of one product of ptj_gemm_grouped2 for the thread-block-pair kernel (float32 output, no bias, no side input)
+// parameters of one product of ptj_gemm_grouped2 for the thread-block-pair kernel (no bias, no side input).
+// store_maps: where the product may leave through tensor-map tile stores (bf16 output, K not split): the first
+// product only, the kernel has one set of output maps.
 int make_grouped_problem(const ptj_gemm_problem& g, int64_t K, int a_kmajor, int b_kmajor, CUtensorMap* ta,
-                         CUtensorMap* tb, GemmParams* out) {
+                         CUtensorMap* tb, GemmParams* out, StoreMaps* store_maps) {
   if (!g.a || !g.b || !g.c || g.M < 1 || g.N < 1) return PTJ_ERR_BAD_SHAPE;
   if (g.M > (1LL << 30) || g.N > (1LL << 30)) return PTJ_ERR_BAD_SHAPE;
   if (g.lda < (a_kmajor ? K : g.M) || g.ldb < (b_kmajor ? K : g.N) || g.ldc < g.N) return PTJ_ERR_BAD_SHAPE;
   if (g.epilogue != PTJ_EPI_NONE && g.epilogue != PTJ_EPI_ACCUM) return PTJ_ERR_UNSUPPORTED;
+  if (g.out_dtype != PTJ_F32 && g.out_dtype != PTJ_BF16) return PTJ_ERR_DTYPE;
+  if (g.epilogue == PTJ_EPI_ACCUM && g.out_dtype != PTJ_F32) return PTJ_ERR_UNSUPPORTED;
   if (!aligned16(g.a) || !aligned16(g.b) || g.lda % 8 != 0 || g.ldb % 8 != 0) return PTJ_ERR_MISALIGNED;
   if (!use_pair_kernel(g.M, g.N, K)) return PTJ_ERR_UNSUPPORTED;
   const int num_kb = static_cast<int>(ceil_div(K, BK));
@@ -1059,7 +1063,9 @@ int make_grouped_problem(const ptj_gemm_problem& g, int64_t K, int a_kmajor, int
   p.ep.N = g.N;
   p.ep.ldc = g.ldc;
   p.ep.mode = g.epilogue;
-  p.ep.vec_ok = aligned16(g.c) && (g.ldc * 4) % 16 == 0;
+  const size_t osz = dtype_size(g.out_dtype);
+  p.ep.vec_ok = aligned16(g.c) && (g.ldc * osz) % 16 == 0;
+  p.out_bf16 = g.out_dtype == PTJ_BF16;
   p.M = g.M;
   p.N = g.N;
   p.K = K;
@@ -1073,6 +1079,13 @@ int make_grouped_problem(const ptj_gemm_problem& g, int64_t K, int a_kmajor, int
   if (static_cast<int64_t>(p.num_m) * p.num_n * split_k > 0x3fffffffLL) return PTJ_ERR_BAD_SHAPE;
   if (!make_pair_operand_maps(ta, tb, g.a, g.b, g.M, g.N, K, g.lda, g.ldb, a_kmajor != 0, b_kmajor != 0))
     return PTJ_ERR_LAUNCH;
+  if (store_maps != nullptr && p.out_bf16 && p.ep.vec_ok && split_k == 1) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(g.N), static_cast<uint64_t>(g.M)};
+    const uint64_t str[1] = {static_cast<uint64_t>(g.ldc) * 2};
+    const uint32_t box[2] = {32, 32};
+    if (!make_tmap_bf16_sw64(&store_maps->c, g.c, 2, dims, str, box)) return PTJ_ERR_LAUNCH;
+    p.tma_store = 1;
+  }
   *out = p;
   return PTJ_OK;
 }
@@ -1085,17 +1098,17 @@ extern "C" int ptj_gemm_grouped2(const ptj_gemm_problem* g0, const ptj_gemm_prob
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap ta0, tb0, ta1, tb1;
   GemmParams p0, p1;
-  int rc = make_grouped_problem(*g0, K, a_kmajor, b_kmajor, &ta0, &tb0, &p0);
+  StoreMaps none{};  // (holds the first product's output map when that product stores through it)
+  int rc = make_grouped_problem(*g0, K, a_kmajor, b_kmajor, &ta0, &tb0, &p0, &none);
   if (rc != PTJ_OK) return rc;
-  rc = make_grouped_problem(*g1, K, a_kmajor, b_kmajor, &ta1, &tb1, &p1);
+  rc = make_grouped_problem(*g1, K, a_kmajor, b_kmajor, &ta1, &tb1, &p1, nullptr);
   if (rc != PTJ_OK) return rc;
-  const StoreMaps none{};
   rc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1)
                             : launch_tc_pair<256, true, false, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1))
                 : (b_kmajor ? launch_tc_pair<256, false, true, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1)
                             : launch_tc_pair<256, false, false, false, true>(ta0, tb0, none, p0, st, &ta1, &tb1, &p1));
   if (rc != PTJ_OK) return rc;
-  rc = finish_split_k(p0.workspace, g0->c, nullptr, g0->M, g0->N, g0->ldc, p0.split_k, g0->epilogue, PTJ_F32, st);
+  rc = finish_split_k(p0.workspace, g0->c, nullptr, g0->M, g0->N, g0->ldc, p0.split_k, g0->epilogue, g0->out_dtype, st);
   if (rc != PTJ_OK) return rc;
-  return finish_split_k(p1.workspace, g1->c, nullptr, g1->M, g1->N, g1->ldc, p1.split_k, g1->epilogue, PTJ_F32, st);
+  return finish_split_k(p1.workspace, g1->c, nullptr, g1->M, g1->N, g1->ldc, p1.split_k, g1->epilogue, g1->out_dtype, st);
 }

@@ -142,6 +142,28 @@ def split_k_for(M: int, N: int, K: int) -> int:
     return best
 
 
+def tail_split_for(M: int, N: int, K: int):
+    """For a product on the 256 x 256-tile thread-block-pair kernel whose last round of tiles would leave most of the 74
+    pairs idle (96 tiles: 74 + 22): (rows of the head part, K parts of the rest), so that head tiles fill whole rounds
+    and the remaining rows, split over K, fill one more round of short work items. None when the product does not go
+    to that kernel or its last round is at least 60 % full."""
+    if M < 256 or N < 256 or K < 2048:
+        return None
+    num_m, num_n = -(-M // 256), -(-N // 256)
+    tiles = num_m * num_n
+    full, rest = divmod(tiles, 74)
+    if full < 1 or rest == 0 or rest > 44:
+        return None
+    head_mb = (full * 74) // num_n
+    tail_tiles = (num_m - head_mb) * num_n
+    if head_mb < 1 or tail_tiles < 1:
+        return None
+    parts = min(8, int(74 / tail_tiles + 0.5), (K // 64) // 4)
+    if parts < 2:
+        return None
+    return head_mb * 256, parts
+
+
 class Gpt2Step:
     """One forward + backward pass. Gradients are written into caller-provided float32 tensors (``grads[name]``),
     so a trainer can hand in views of one flat buffer and overlap their reduction with the rest of backward."""
@@ -158,6 +180,8 @@ class Gpt2Step:
         self.split_gelu_bwd = False
         # the two FFN weight gradients of a layer in one launch, and the QKV + out-projection pair in another
         self.pair_wgrads = True
+        # input gradients whose last round of tiles is mostly empty: that round's rows split over K, same launch
+        self.tail_split = True
         self._ws2 = [None, None]
 
     # -- helpers --
@@ -219,11 +243,26 @@ class Gpt2Step:
         # [8192, 768, 50257]: 543 us unsplit, 478 / 467 / 496 us in 2 / 3 / 4 parts; the K = 2304 and 3072 products of a
         # layer only lose (32 -> 40 us, 48 -> 56 us), hence the lower bound on K.
         split = 1
-        if dy2d.dtype == torch.bfloat16 and K >= 16384 and not kw:
-            split = split_k_for(T, N, K)
-            need = split * T * N
-            if split > 1 and (self._ws is None or self._ws.numel() < need):
-                self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
+        if dy2d.dtype == torch.bfloat16 and not kw:
+            tail = tail_split_for(T, N, K) if self.tail_split else None
+            if tail is not None:
+                # the rows of the last, mostly empty round of tiles as a second product, split over K, in the same launch
+                head_rows, parts = tail
+                out = torch.empty((T, N), device=dy2d.device, dtype=self.dtype)
+                need = parts * (T - head_rows) * N
+                if self._ws is None or self._ws.numel() < need:
+                    self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
+                ld = dy2d.stride(0)
+                probs = [dict(a=dy2d[:head_rows], b=w2d, out=out[:head_rows], lda=ld, ldb=w2d.stride(0)),
+                         dict(a=dy2d[head_rows:], b=w2d, out=out[head_rows:], lda=ld, ldb=w2d.stride(0), split_k=parts,
+                              workspace=self._ws)]
+                if ops.gemm_grouped2(probs, K, a_kmajor=True, b_kmajor=False):
+                    return out
+            if K >= 16384:
+                split = split_k_for(T, N, K)
+                need = split * T * N
+                if split > 1 and (self._ws is None or self._ws.numel() < need):
+                    self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
         return ops.gemm(dy2d, w2d, a_kmajor=True, b_kmajor=False, M=T, N=N, K=K, lda=dy2d.stride(0),
                         ldb=w2d.stride(0), out_dtype=self.dtype, split_k=split, workspace=self._ws, **kw)
 

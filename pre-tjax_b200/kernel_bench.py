@@ -127,10 +127,10 @@ def main():
             ("gemm fwd ffn2       +bias+dropout+residual", lambda: ops.gemm(x_f, w2, bias=b_d, epilogue=lib.EPI_DROPOUT_RESID, aux=y_d, dropout_args=drop), 2 * T * F * D),
             ("gemm fwd lm-head    [T,768]x[50257,768]^T +bias", lambda: ops.gemm(x_d, w_emb, bias=b_v, out=logits, N=V, ldc=Vp), 2 * T * V * D),
             ("gemm dgrad ffn2     dy W2, *gelu'(pre)", lambda: ops.gemm(y_d, w2, a_kmajor=True, b_kmajor=False, M=T, N=F, K=D, epilogue=lib.EPI_GELU_BWD, aux=y_f), 2 * T * F * D),
-            ("gemm dgrad ffn1     dh W1", lambda: ops.gemm(y_f, w1, a_kmajor=True, b_kmajor=False, M=T, N=D, K=F), 2 * T * F * D),
+            ("gemm dgrad ffn1     dh W1 (last round of tiles split over K, as in the step)", lambda: step._dgrad(y_f, w1), 2 * T * F * D),
             ("gemm dgrad out-proj dy Wo", lambda: ops.gemm(y_d, w_o, a_kmajor=True, b_kmajor=False, M=T, N=D, K=D), 2 * T * D * D),
-            ("gemm dgrad qkv      dqkv Wqkv", lambda: ops.gemm(y_qkv, w_qkv, a_kmajor=True, b_kmajor=False, M=T, N=D, K=3 * D), 2 * T * 3 * D * D),
-            ("gemm dgrad lm-head  dlogits Wemb (K split as in the step)", lambda: step._dgrad(logits, w_emb, cols=V), 2 * T * V * D),
+            ("gemm dgrad qkv      dqkv Wqkv (last round split over K)", lambda: step._dgrad(y_qkv, w_qkv), 2 * T * 3 * D * D),
+            ("gemm dgrad lm-head  dlogits Wemb (last round split over K)", lambda: step._dgrad(logits, w_emb, cols=V), 2 * T * V * D),
         ]
         step = ptj.gpt2.Gpt2Step(ptj.PRESETS["gpt2-small"])
         g_w2, g_w1, g_wo, g_wqkv, g_emb = (torch.empty(*s, device=dev) for s in ((D, F), (F, D), (D, D), (3 * D, D), (V, D)))

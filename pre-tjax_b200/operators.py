@@ -253,13 +253,13 @@ def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None
 
 
 def gemm_grouped2(problems, K, *, a_kmajor=True, b_kmajor=True):
-    """Two products in one launch through ptj_gemm_grouped2. problems: two dicts with a, b, out (float32 [M, N]), lda,
+    """Two products in one launch through ptj_gemm_grouped2. problems: two dicts with a, b, out (float32 or bf16 [M, N]), lda,
     ldb, and optionally accumulate, split_k, workspace. Returns False (nothing launched) when the library says the
     pair does not qualify; the caller then issues two gemm() calls."""
     descs = []
     for pr in problems:
         a, b, out = pr["a"], pr["b"], pr["out"]
-        if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or out.dtype != torch.float32:
+        if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
             return False
         M, N = out.shape
         split = int(pr.get("split_k", 1))
@@ -267,7 +267,7 @@ def gemm_grouped2(problems, K, *, a_kmajor=True, b_kmajor=True):
         if split > 1 and (ws is None or ws.numel() < split * M * N):
             ws = torch.empty(split * M * N, device=a.device, dtype=torch.float32)
             pr["workspace"] = ws
-        descs.append(_lib.GemmProblem(_ptr(a), _ptr(b), _ptr(out), M, N, pr["lda"], pr["ldb"], out.stride(0),
+        descs.append(_lib.GemmProblem(_ptr(a), _ptr(b), _ptr(out), M, N, pr["lda"], pr["ldb"], out.stride(0), _dt(out),
                                       _lib.EPI_ACCUM if pr.get("accumulate") else _lib.EPI_NONE, split, _ptr(ws),
                                       0 if ws is None else ws.numel()))
     prof = GEMM_PROFILE
@@ -282,7 +282,7 @@ def gemm_grouped2(problems, K, *, a_kmajor=True, b_kmajor=True):
     if prof is not None:
         e1.record()
         flops = sum(2.0 * d.M * d.N * K for d in descs)
-        nbytes = sum(float(2 * (d.M * K + d.N * K) + d.M * d.N * 4) for d in descs)
+        nbytes = sum(float(2 * (d.M * K + d.N * K) + d.M * d.N * (2 if d.out_dtype == _lib.PTJ_BF16 else 4)) for d in descs)
         prof.append((e0, e1, flops, ("grouped", descs[0].M, descs[0].N, descs[1].M, descs[1].N, K), nbytes))
     return True
 

@@ -236,3 +236,28 @@ def test_grouped_launch_refuses_small_products(ops):
     pr = dict(a=a, b=b, out=out, lda=256, ldb=256)
     assert ops.gemm_grouped2([dict(pr), dict(pr)], 256) is False
     assert float(out.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("T,N,K", [(8192, 768, 3072), (8192, 768, 2304), (5000, 776, 2048)])
+def test_input_gradient_with_the_last_round_of_tiles_split_over_k(T, N, K):
+    """Gpt2Step._dgrad hands a product whose last round of 256 x 256 tiles is mostly empty to the two-product launch:
+    head rows as they were, the remaining rows split over K. Head rows equal the plain launch bit for bit, the rest
+    within rounding of it (another summation order), everything within tolerance of the float64 product."""
+    gpt2, ops = pkg("gpt2"), pkg("operators")
+    step = gpt2.Gpt2Step(gpt2.GPT2Config(vocab=512, dim=128, layers=1, heads=2, ffn=256, seq=128, dropout=0.0))
+    dy, w = rnd(T, K, seed=61, scale=0.1), rnd(K, N, seed=62)  # dx = dy w, w read MN-major
+    ref = dy.double() @ w.double()
+    tail = gpt2.tail_split_for(T, N, K)
+    got = step._dgrad(dy.cuda(), w.cuda())
+    no_fault(ops)
+    plain = ops.gemm(dy.cuda(), w.cuda(), a_kmajor=True, b_kmajor=False, M=T, N=N, K=K)
+    assert rel_err(got, ref) < TOL
+    if tail is None:
+        assert torch.equal(got, plain)
+    else:
+        head = tail[0]
+        assert 0 < head < T
+        assert torch.equal(got[:head], plain[:head])
+        assert rel_err(got[head:], plain[head:]) < 1e-2
+    step.tail_split = False
+    assert torch.equal(step._dgrad(dy.cuda(), w.cuda()), plain)
