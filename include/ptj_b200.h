@@ -214,6 +214,18 @@ int ptj_gemm(const void* a, const void* b, void* c, const float* bias, const voi
              int b_kmajor, int in_dtype, int out_dtype, int epilogue, const ptj_dropout_args* dropout,
              int split_k, float* workspace, size_t workspace_floats, void* stream);
 
+/* split_k = PTJ_SPLIT_TAIL lets ptj_gemm even out a bad last round of tiles: a bf16 product on the 256 x 256-tile
+ * thread-block-pair kernel whose tile count leaves most of the GPU idle in its last round (96 tiles on 74 pairs) runs
+ * as head rows that fill whole rounds plus, in the same launch, the remaining rows split over K; a finishing kernel
+ * sums those parts in a fixed order and applies the epilogue. Epilogues PTJ_EPI_NONE (no bias) and
+ * PTJ_EPI_DROPOUT_RESID (K-major operands, 16-byte aligned bf16 rows); anything else, or a workspace smaller than
+ * ptj_gemm_tail_split_floats(M, N, K) floats, runs unsplit. Head rows are bit-identical to the unsplit product, the
+ * rest differs by the summation order. ptj_gemm_tail_split_rows: the first row of the split range (0: no split for
+ * this shape). */
+#define PTJ_SPLIT_TAIL (-1)
+size_t ptj_gemm_tail_split_floats(int64_t M, int64_t N, int64_t K);
+int64_t ptj_gemm_tail_split_rows(int64_t M, int64_t N, int64_t K);
+
 /* Two products C_i[M_i, N_i] = op(A_i) op(B_i) (i = 0, 1) in ONE launch: bf16 operands, float32 or bf16 outputs, the
  * same K and the same operand layouts for both, epilogue PTJ_EPI_NONE or (float32 output) PTJ_EPI_ACCUM each, optional
  * K split each (own workspace of split_k * M * N floats). The two may also be row ranges of ONE product, the second

@@ -63,6 +63,8 @@ _SIGNATURES = {
     "ptj_colsum": (c_int, [_P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P]),
     "ptj_gemm": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
                          c_int, c_int, c_int, POINTER(DropoutArgs), c_int, _P, c_size_t, _P]),
+    "ptj_gemm_tail_split_floats": (c_size_t, [c_int64, c_int64, c_int64]),
+    "ptj_gemm_tail_split_rows": (c_int64, [c_int64, c_int64, c_int64]),
     "ptj_gemm_grouped2": (c_int, [POINTER(GemmProblem), POINTER(GemmProblem), c_int64, c_int, c_int, _P]),
     "ptj_attn_keep_bits_bytes": (c_size_t, [POINTER(AttnShape), c_int]),
     "ptj_attn_keep_bits": (c_int, [_P, POINTER(AttnShape), c_float, c_uint64, c_uint32, c_int, _P]),

@@ -613,8 +613,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       const int64_t row0 = static_cast<int64_t>(m_blk) * 2 * BM + static_cast<int64_t>(rank) * BM + quarter * 32;
       const int64_t row = row0 + lane;
-      if (SIDE) {
+      if (SIDE && (!GROUPED || q.tma_side)) {
         // the side input of this warp's first block of the tile, requested before the accumulator is even complete
+        // (a second product that is split over K leaves its epilogue to the finishing kernel: nothing to fetch)
         const int64_t nf = static_cast<int64_t>(n_blk) * BN + sub * 32;
         if (row0 < q.M && nf < q.N) side_prefetch_issue(sp, &smaps.s, row0, nf, lane);
       }
@@ -792,6 +793,57 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& sm,
   return PTJ_OK;
 }
 
+// Sum of the K-split partial tiles (fixed order) followed by the FULL epilogue of the product: one thread per row and
+// group of eight columns. Used for the row range that a product's mostly-empty last round of tiles is turned into.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const float* __restrict__ ws, const EpilogueParams ep, int split_k) {
+  grid_dep_sync();
+  const uint64_t seed = ep.mode == PTJ_EPI_DROPOUT_RESID ? resolve_seed(ep.seed) : 0ull;
+  const int64_t groups = (ep.N + 7) / 8, total = ep.M * groups;
+  const bool vec = (ep.N & 3) == 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / groups, n0 = (i - m * groups) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < split_k; ++k) {
+      const float* src = ws + (static_cast<int64_t>(k) * ep.M + m) * ep.N + n0;
+      if (vec && n0 + 8 <= ep.N) {
+        const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (n0 + j < ep.N) acc[j] += src[j];
+      }
+    }
+    epilogue_row_segment<TOut, 8>(ep, m, n0, acc, seed);
+  }
+}
+
+// A product whose last round of 256 x 256 tiles would leave most of the 74 thread-block pairs idle (96 tiles: 74 + 22):
+// head rows that fill whole rounds, and the K parts for the remaining rows so that they fill one more round of short
+// work items. parts == 0: no split (the product does not go to the pair kernel, or its last round is >= 60 % full).
+struct TailPlan { int64_t head_rows; int parts; };
+TailPlan tail_split_plan(int64_t M, int64_t N, int64_t K) {
+  TailPlan none{0, 0};
+  if (M < 256 || N < 256 || K < 2048) return none;
+  const int64_t pairs = kNumSMs / 2;
+  const int64_t num_m = ceil_div(M, 256), num_n = ceil_div(N, 256), tiles = num_m * num_n;
+  const int64_t full = tiles / pairs, rest = tiles % pairs;
+  if (full < 1 || rest == 0 || rest > 44) return none;
+  const int64_t head_mb = full * pairs / num_n, tail_tiles = (num_m - head_mb) * num_n;
+  if (head_mb < 1 || tail_tiles < 1) return none;
+  int64_t parts = (2 * pairs + tail_tiles) / (2 * tail_tiles);  // pairs / tail_tiles, rounded
+  if (parts > 8) parts = 8;
+  if (parts > K / 64 / 4) parts = K / 64 / 4;
+  if (parts < 2) return none;
+  return TailPlan{head_mb * 256, static_cast<int>(parts)};
+}
+
 // sums the K-split partial tiles in a fixed order (no-op when split_k == 1)
 int finish_split_k(float* workspace, void* c, const float* bias, int64_t M, int64_t N, int64_t ldc, int split_k,
                    int epilogue, int out_dtype, cudaStream_t st) {
@@ -895,6 +947,7 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   if ((epilogue == PTJ_EPI_GELU_BWD || epilogue == PTJ_EPI_DROPOUT_RESID) && aux == nullptr) return PTJ_ERR_BAD_SHAPE;
   if (epilogue == PTJ_EPI_DROPOUT_RESID && dropout == nullptr) return PTJ_ERR_BAD_SHAPE;
   if (epilogue == PTJ_EPI_ACCUM && out_dtype != PTJ_F32) return PTJ_ERR_UNSUPPORTED;
+  const bool tail_requested = split_k == PTJ_SPLIT_TAIL;
   if (split_k < 1) split_k = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -979,6 +1032,49 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
     p.num_n = static_cast<int>(ceil_div(N, 256));
     CUtensorMap ta, tb;
     if (!make_pair_operand_maps(&ta, &tb, a, b, M, N, K, lda, ldb, a_kmajor != 0, b_kmajor != 0)) return PTJ_ERR_LAUNCH;
+    // PTJ_SPLIT_TAIL: the rows of a mostly-empty last round of tiles become a second product of the same launch,
+    // split over K; their epilogue runs in the finishing kernel
+    const TailPlan tp = tail_requested ? tail_split_plan(M, N, K) : TailPlan{0, 0};
+    const bool tail_epilogue_ok = (epilogue == PTJ_EPI_NONE && bias == nullptr) ||
+                                  (epilogue == PTJ_EPI_DROPOUT_RESID && p.tma_side && a_kmajor && b_kmajor);
+    if (tp.parts >= 2 && tail_epilogue_ok && workspace != nullptr && aligned16(workspace) &&
+        workspace_floats >= static_cast<size_t>(tp.parts) * (M - tp.head_rows) * N) {
+      const int64_t head = tp.head_rows, tail = M - head;
+      GemmParams ph = p, pt = p;
+      ph.M = ph.ep.M = head;
+      ph.num_m = static_cast<int>(head / 256);
+      pt.M = pt.ep.M = tail;
+      pt.num_m = static_cast<int>(ceil_div(tail, 2 * BM));
+      pt.split_k = tp.parts;
+      pt.workspace = workspace;
+      pt.tma_store = pt.tma_side = 0;
+      pt.ep.c = static_cast<char*>(c) + head * ldc * osz;
+      if (aux != nullptr) pt.ep.aux = static_cast<const char*>(aux) + head * ldc * osz;
+      pt.ep.mask_row0 = head;
+      pt.ep.vec_ok = ep.vec_ok;
+      const char* a_tail = static_cast<const char*>(a) + (a_kmajor ? head * lda : head) * 2;
+      CUtensorMap ta_t, tb_t;
+      if (!make_pair_operand_maps(&ta_t, &tb_t, a_tail, b, tail, N, K, lda, ldb, a_kmajor != 0, b_kmajor != 0))
+        return PTJ_ERR_LAUNCH;
+      int grc;
+      if (ph.tma_side)
+        grc = launch_tc_pair<256, true, true, true, true>(ta, tb, smaps, ph, st, &ta_t, &tb_t, &pt);
+      else
+        grc = a_kmajor ? (b_kmajor ? launch_tc_pair<256, true, true, false, true>(ta, tb, smaps, ph, st, &ta_t, &tb_t, &pt)
+                                   : launch_tc_pair<256, true, false, false, true>(ta, tb, smaps, ph, st, &ta_t, &tb_t, &pt))
+                       : (b_kmajor ? launch_tc_pair<256, false, true, false, true>(ta, tb, smaps, ph, st, &ta_t, &tb_t, &pt)
+                                   : launch_tc_pair<256, false, false, false, true>(ta, tb, smaps, ph, st, &ta_t, &tb_t, &pt));
+      if (grc != PTJ_OK) return grc;
+      const int64_t threads = tail * ceil_div(N, 8);
+      int64_t blocks = ceil_div(threads, 256);
+      if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+      if (p.out_bf16)
+        launch_k(splitk_finish_kernel<__nv_bfloat16>, static_cast<int>(blocks), 256, 0, st, workspace, pt.ep, tp.parts);
+      else
+        launch_k(splitk_finish_kernel<float>, static_cast<int>(blocks), 256, 0, st, workspace, pt.ep, tp.parts);
+      PTJ_CHECK_LAUNCH();
+      return PTJ_OK;
+    }
     int prc;
     if (p.tma_side)  // (A is K-major whenever tma_side is set)
       prc = b_kmajor ? launch_tc_pair<256, true, true, true>(ta, tb, smaps, p, st)
@@ -1034,6 +1130,18 @@ extern "C" int ptj_gemm(const void* a, const void* b, void* c, const float* bias
   if (rc != PTJ_OK) return rc;
 
   return finish_split_k(workspace, c, bias, M, N, ldc, split_k, epilogue, out_dtype, st);
+}
+
+extern "C" size_t ptj_gemm_tail_split_floats(int64_t M, int64_t N, int64_t K) {
+  if (M < 1 || N < 1 || K < 1) return 0;
+  const TailPlan tp = tail_split_plan(M, N, K);
+  return tp.parts >= 2 ? static_cast<size_t>(tp.parts) * (M - tp.head_rows) * N : 0;
+}
+
+extern "C" int64_t ptj_gemm_tail_split_rows(int64_t M, int64_t N, int64_t K) {
+  if (M < 1 || N < 1 || K < 1) return 0;
+  const TailPlan tp = tail_split_plan(M, N, K);
+  return tp.parts >= 2 ? tp.head_rows : 0;
 }
 
 // ---- two products in one launch -----------------------------------------------------------------------------------

@@ -21,6 +21,7 @@ struct EpilogueParams {
   int train;
   uint64_t seed;
   uint32_t stream_id;
+  int64_t mask_row0;     // row of the logical [M, N] matrix that row 0 of c is (non-zero when c is a row range of it)
 };
 
 template <typename TOut, int CNT>
@@ -134,7 +135,7 @@ __device__ __forceinline__ void epilogue_post(const EpilogueParams& ep, int64_t 
     for (int j = 0; j < CNT; ++j) acc[j] += a[j];
   } else if (ep.mode == PTJ_EPI_DROPOUT_RESID) {
     // mask indexed by the logical element position m * N + n (the stream ptj_dropout uses on a contiguous [M, N])
-    const uint64_t base = static_cast<uint64_t>(m) * static_cast<uint64_t>(ep.N) + static_cast<uint64_t>(n0);
+    const uint64_t base = static_cast<uint64_t>(m + ep.mask_row0) * static_cast<uint64_t>(ep.N) + static_cast<uint64_t>(n0);
     if (!ep.train) {
 #pragma unroll
       for (int j = 0; j < CNT; ++j) acc[j] = fmaf(acc[j], ep.eval_scale, a[j]);

@@ -143,25 +143,12 @@ def split_k_for(M: int, N: int, K: int) -> int:
 
 
 def tail_split_for(M: int, N: int, K: int):
-    """For a product on the 256 x 256-tile thread-block-pair kernel whose last round of tiles would leave most of the 74
-    pairs idle (96 tiles: 74 + 22): (rows of the head part, K parts of the rest), so that head tiles fill whole rounds
-    and the remaining rows, split over K, fill one more round of short work items. None when the product does not go
-    to that kernel or its last round is at least 60 % full."""
-    if M < 256 or N < 256 or K < 2048:
-        return None
-    num_m, num_n = -(-M // 256), -(-N // 256)
-    tiles = num_m * num_n
-    full, rest = divmod(tiles, 74)
-    if full < 1 or rest == 0 or rest > 44:
-        return None
-    head_mb = (full * 74) // num_n
-    tail_tiles = (num_m - head_mb) * num_n
-    if head_mb < 1 or tail_tiles < 1:
-        return None
-    parts = min(8, int(74 / tail_tiles + 0.5), (K // 64) // 4)
-    if parts < 2:
-        return None
-    return head_mb * 256, parts
+    """(first row of the range that is split over K, floats of workspace) when ptj_gemm's PTJ_SPLIT_TAIL changes how a
+    bf16 product of this shape runs (its last round of 256 x 256 tiles would leave most thread-block pairs idle: 96
+    tiles on 74 pairs), else None."""
+    lib = _lib.lib()
+    n = lib.ptj_gemm_tail_split_floats(M, N, K)
+    return (int(lib.ptj_gemm_tail_split_rows(M, N, K)), int(n)) if n else None
 
 
 class Gpt2Step:
@@ -198,6 +185,11 @@ class Gpt2Step:
         ops.gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, M=M, N=N, K=T, lda=dy2d.stride(0), ldb=x2d.stride(0),
                  out=out.view(M, N), epilogue=_lib.EPI_ACCUM if accumulate else _lib.EPI_NONE, split_k=split,
                  workspace=self._ws)
+
+    def _workspace(self, floats: int):
+        if self._ws is None or self._ws.numel() < floats:
+            self._ws = torch.empty(floats, device="cuda", dtype=torch.float32)
+        return self._ws
 
     def _wgrad2(self, first, second):
         """Two weight gradients (dy, x, out) in ONE launch of the thread-block-pair kernel when both qualify: their
@@ -246,23 +238,11 @@ class Gpt2Step:
         if dy2d.dtype == torch.bfloat16 and not kw:
             tail = tail_split_for(T, N, K) if self.tail_split else None
             if tail is not None:
-                # the rows of the last, mostly empty round of tiles as a second product, split over K, in the same launch
-                head_rows, parts = tail
-                out = torch.empty((T, N), device=dy2d.device, dtype=self.dtype)
-                need = parts * (T - head_rows) * N
-                if self._ws is None or self._ws.numel() < need:
-                    self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
-                ld = dy2d.stride(0)
-                probs = [dict(a=dy2d[:head_rows], b=w2d, out=out[:head_rows], lda=ld, ldb=w2d.stride(0)),
-                         dict(a=dy2d[head_rows:], b=w2d, out=out[head_rows:], lda=ld, ldb=w2d.stride(0), split_k=parts,
-                              workspace=self._ws)]
-                if ops.gemm_grouped2(probs, K, a_kmajor=True, b_kmajor=False):
-                    return out
-            if K >= 16384:
+                split = ops.SPLIT_TAIL  # the rows of the last, mostly empty round of tiles are split over K
+                self._workspace(tail[1])
+            elif K >= 16384:
                 split = split_k_for(T, N, K)
-                need = split * T * N
-                if split > 1 and (self._ws is None or self._ws.numel() < need):
-                    self._ws = torch.empty(need, device=dy2d.device, dtype=torch.float32)
+                self._workspace(split * T * N)
         return ops.gemm(dy2d, w2d, a_kmajor=True, b_kmajor=False, M=T, N=N, K=K, lda=dy2d.stride(0),
                         ldb=w2d.stride(0), out_dtype=self.dtype, split_k=split, workspace=self._ws, **kw)
 
@@ -297,8 +277,10 @@ class Gpt2Step:
             a["ln2"] = ops.t_layernorm_fwd_t((g("g2"), g("b2")), a["x_mid"])
             a["h_pre"] = torch.empty((T, cfg.ffn), device=x.device, dtype=self.dtype)
             a["h_act"] = ops.gemm(a["ln2"], g("w1"), bias=g("b1f"), epilogue=_lib.EPI_GELU, aux_out=a["h_pre"])
+            tail = tail_split_for(T, D, cfg.ffn) if (self.tail_split and self.dtype == torch.bfloat16) else None
             x = ops.gemm(a["h_act"], g("w2"), bias=g("b2f"), epilogue=_lib.EPI_DROPOUT_RESID, aux=a["x_mid"],
-                         dropout_args=(p, train, s_res2, 0))
+                         dropout_args=(p, train, s_res2, 0), split_k=ops.SPLIT_TAIL if tail else 1,
+                         workspace=self._workspace(tail[1]) if tail else None)
             acts["layers"].append(a)
         acts["x_last"] = x
         acts["x_f"] = ops.t_layernorm_fwd_t((w["g_f"], w["b_f"]), x)

@@ -206,6 +206,9 @@ def t_log_softmax_bkwd2_t(dloss_dx: torch.Tensor, x: torch.Tensor) -> torch.Tens
     return dx.reshape(dloss_dx.shape)
 
 
+SPLIT_TAIL = -1  # ptj_gemm's split_k value "split the rows of a mostly-empty last round of tiles over K"
+
+
 # ---- GEMM -----------------------------------------------------------------------------------------------------------
 def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None, ldb=None, out=None, out_dtype=None,
          ldc=None, bias=None, epilogue=_lib.EPI_NONE, aux=None, aux_out=None, dropout_args=None, split_k=1,
@@ -224,12 +227,14 @@ def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None
         out = torch.empty((M, N), device=a.device, dtype=out_dtype)
     ldc = out.stride(0) if ldc is None else ldc
     ws_n = 0
-    if split_k > 1:
+    if split_k > 1 or split_k == SPLIT_TAIL:
         if a.dtype != torch.bfloat16:
             split_k = 1
         else:
-            ws_n = split_k * M * N
-            if workspace is None or workspace.numel() < ws_n:
+            ws_n = split_k * M * N if split_k > 1 else _lib.lib().ptj_gemm_tail_split_floats(M, N, K)
+            if ws_n == 0:
+                split_k = 1  # this shape has no bad last round
+            elif workspace is None or workspace.numel() < ws_n:
                 workspace = torch.empty(ws_n, device=a.device, dtype=torch.float32)
     dargs = None
     if dropout_args is not None:
@@ -242,7 +247,7 @@ def gemm(a, b, *, a_kmajor=True, b_kmajor=True, M=None, N=None, K=None, lda=None
     _lib.check(
         _lib.lib().ptj_gemm(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(aux), _ptr(aux_out), M, N, K, lda, ldb, ldc,
                             int(a_kmajor), int(b_kmajor), _dt(a), _dt(out), epilogue, dargs, split_k, _ptr(workspace),
-                            ws_n, _stream()),
+                            0 if workspace is None else workspace.numel(), _stream()),
         "ptj_gemm")
     if prof is not None:
         e1.record()

@@ -247,7 +247,7 @@ def test_input_gradient_with_the_last_round_of_tiles_split_over_k(T, N, K):
     step = gpt2.Gpt2Step(gpt2.GPT2Config(vocab=512, dim=128, layers=1, heads=2, ffn=256, seq=128, dropout=0.0))
     dy, w = rnd(T, K, seed=61, scale=0.1), rnd(K, N, seed=62)  # dx = dy w, w read MN-major
     ref = dy.double() @ w.double()
-    tail = gpt2.tail_split_for(T, N, K)
+    tail = gpt2.tail_split_for(T, N, K)  # (first split row, workspace floats) or None
     got = step._dgrad(dy.cuda(), w.cuda())
     no_fault(ops)
     plain = ops.gemm(dy.cuda(), w.cuda(), a_kmajor=True, b_kmajor=False, M=T, N=N, K=K)
@@ -261,3 +261,31 @@ def test_input_gradient_with_the_last_round_of_tiles_split_over_k(T, N, K):
         assert rel_err(got[head:], plain[head:]) < 1e-2
     step.tail_split = False
     assert torch.equal(step._dgrad(dy.cuda(), w.cuda()), plain)
+
+
+@pytest.mark.parametrize("train", [True, False])
+def test_dropout_residual_product_with_the_last_round_split_over_k(ops, train):
+    """FFN-2 forward at GPT-2 small size (96 tiles of 256 x 256) with PTJ_SPLIT_TAIL: bias + dropout + residual of the
+    split rows are applied by the finishing kernel with the mask of their position in the whole matrix. Head rows
+    equal the unsplit launch bit for bit; everything matches the float64 product with the host mask."""
+    lib = pkg("_lib")
+    M, N, K, p_drop, seed = 8192, 768, 3072, 0.3, 99
+    A, B = rnd(M, K, seed=71, scale=0.1), rnd(N, K, seed=72)
+    bias, res = torch.randn(N, generator=torch.Generator().manual_seed(3)), rnd(M, N, seed=73)
+    head = int(lib.lib().ptj_gemm_tail_split_rows(M, N, K))
+    assert 0 < head < M
+    kw = dict(bias=bias.cuda(), epilogue=lib.EPI_DROPOUT_RESID, aux=res.cuda(), dropout_args=(p_drop, train, seed, 2))
+    plain = ops.gemm(A.cuda(), B.cuda(), **kw)
+    got = ops.gemm(A.cuda(), B.cuda(), split_k=ops.SPLIT_TAIL, **kw)
+    no_fault(ops)
+    acc = A.double() @ B.double().t() + bias.double()
+    if train:
+        keep = torch.from_numpy(philox.keep_mask(seed, 2, M * N, p_drop)).view(M, N)
+        ref = res.double() + acc * keep
+    else:
+        ref = res.double() + acc * (1 - p_drop)
+    assert rel_err(got, ref) < TOL and rel_err(plain, ref) < TOL
+    assert torch.equal(got[:head], plain[:head])
+    assert rel_err(got[head:], plain[head:]) < 1e-2
+    if train:  # the same elements are dropped (where the product is dropped the output IS the residual)
+        assert torch.equal(got == res.cuda(), plain == res.cuda())
