@@ -74,21 +74,22 @@ pos_bwd_kernel(const T* __restrict__ dy, float* __restrict__ d_w_pos, int64_t ba
   }
 }
 
-// Adds rows pos_s[0 .. n) of dy (masked, scaled) into acc: warp w takes rows w, w + 8, ...; lanes run across the
-// features, 8 per vector = one Philox call. Several rows per step: their loads are independent (kept as raw 16-byte
+// Adds rows pos_s[first], pos_s[first + step], ... (< n) of dy (masked, scaled) into acc; lanes run across the
+// features, 8 per vector = one Philox call. A block's 8 warps share a batch with (first, step) = (warp, 8); a warp that
+// owns a whole run passes (0, 1). Several rows per step: their loads are independent (kept as raw 16-byte
 // pieces until they are added, in row order, so the sums do not depend on the grouping).
 template <typename T, int NV>
 __device__ __forceinline__ void add_rows(const T* __restrict__ dy, const int32_t* pos_s, int n, int dim, int nvec,
                                      bool masked, float k_all, uint64_t seed, uint32_t stream_id, uint32_t thr,
-                                     float (&acc)[NV][8], int lane, int warp) {
+                                     float (&acc)[NV][8], int lane, int first, int step) {
   constexpr int U = sizeof(T) == 2 ? 4 : 2;    // rows per step
   constexpr int PV = sizeof(T) == 2 ? 1 : 2;   // 16-byte pieces per 8-element vector
-  for (int r0 = warp; r0 < n; r0 += 8 * U) {
+  for (int r0 = first; r0 < n; r0 += step * U) {
     uint4 raw[U][NV][PV];
     int64_t rows_u[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int r = r0 + 8 * u;
+      const int r = r0 + step * u;
       rows_u[u] = r < n ? static_cast<int64_t>(pos_s[r]) * dim : -1;
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
@@ -134,14 +135,18 @@ __device__ __forceinline__ void add_rows(const T* __restrict__ dy, const int32_t
   }
 }
 
-constexpr int kHeavyRun = 128;
+constexpr int kHeavyRun = 32;
 constexpr int kHeavyCluster = 8;
 
 // Gradient w.r.t. the embedding table (model_triton.py:183-185, 205-213). Token positions arrive stably sorted by
-// token id; the thread block that lands on the first position of a run of equal ids sums the whole run: the run is
-// fetched in batches of 256 positions, warp w takes rows w, w+8, ... of a batch (lanes across the features, 8 per
-// vector = one Philox call), and the 8 per-warp partial rows are added in warp order at the end. One block, fixed
-// order, no atomics => every table row is reproducible. Frequent tokens (a Zipf head) make runs of ~1000 rows.
+// token id, so the rows of one table row form a run of equal ids. A block looks at kChunk consecutive sorted positions:
+// 64 threads mark the run heads among them (both neighbours' ids are two dependent loads, taken for all positions at
+// once rather than by one block per position), and each of the 8 warps then sums whole runs on its own - lanes across
+// the features, 8 per vector = one Philox call, four rows in flight, rows added in order - and adds the result onto
+// the table row. One warp, fixed order, no atomics => every table row is reproducible. Runs longer than kHeavyRun rows
+// (a Zipf head makes runs of ~1000) are left to the cluster kernel below.
+constexpr int kChunk = 64;
+
 template <typename T, int NV>
 __global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
 embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, const int32_t* __restrict__ sorted_pos,
@@ -149,59 +154,73 @@ embed_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids, cons
                  uint32_t thr, float eval_scale, int train, uint64_t seed, uint32_t stream_id) {
   grid_dep_sync();
   seed = resolve_seed(seed);
-  extern __shared__ float part[];  // [8][dim]
-  __shared__ int32_t pos_s[256];
+  __shared__ uint32_t head_mask[kChunk / 32];
+  __shared__ int32_t pos_w[8][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool masked = train && thr != 0u;
   const float k_all = train ? 1.f : eval_scale;
   const int nvec = dim / 8;  // dim % 8 == 0 is checked on the host
-  for (int64_t j = blockIdx.x; j < tokens; j += gridDim.x) {
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kChunk;
+  if (warp < kChunk / 32) {
+    const int64_t j = base + threadIdx.x;
+    bool head = false;
+    if (j < tokens) {
+      const int32_t id = ids[sorted_pos[j]];
+      head = (j == 0 || ids[sorted_pos[j - 1]] != id) && id >= 0 && id < vocab &&
+             !(j + kHeavyRun < tokens && ids[sorted_pos[j + kHeavyRun]] == id);  // (long runs: the cluster kernel)
+    }
+    const uint32_t m = __ballot_sync(0xffffffffu, head);
+    if (lane == 0) head_mask[warp] = m;
+  }
+  __syncthreads();
+  const uint32_t m0 = head_mask[0], m1 = head_mask[1];
+  const int n0 = __popc(m0), nheads = n0 + __popc(m1);
+  int32_t* my_pos = pos_w[warp];
+  for (int h = warp; h < nheads; h += 8) {
+    const int off = h < n0 ? static_cast<int>(__fns(m0, 0, h + 1)) : 32 + static_cast<int>(__fns(m1, 0, h - n0 + 1));
+    const int64_t j = base + off;
     const int32_t id = ids[sorted_pos[j]];
-    if (j > 0 && ids[sorted_pos[j - 1]] == id) continue;  // not the head of a run (uniform over the block)
-    if (id < 0 || id >= vocab) continue;
-    // runs longer than kHeavyRun rows are summed by a cluster of thread blocks (embed_bwd_heavy_kernel)
-    if (j + kHeavyRun < tokens && ids[sorted_pos[j + kHeavyRun]] == id) continue;
     float acc[NV][8];
 #pragma unroll
     for (int i = 0; i < NV; ++i)
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
-    for (int64_t base = j;; base += 256) {
-      const int64_t q = base + threadIdx.x;
+    for (int64_t w0 = j;; w0 += 32) {  // the run, 32 positions at a time (matches are a prefix of each window)
+      const int64_t q = w0 + lane;
       int32_t pos = -1;
       if (q < tokens) {
         pos = sorted_pos[q];
         if (ids[pos] != id) pos = -1;
       }
-      __syncthreads();  // previous batch fully consumed
-      pos_s[threadIdx.x] = pos;
-      const int n = __syncthreads_count(pos >= 0);  // matches are a prefix of the batch (ids are sorted)
-      add_rows<T, NV>(dy, pos_s, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, warp);
-      if (n < 256) break;
+      __syncwarp();  // the previous window has been consumed
+      my_pos[lane] = pos;
+      const int n = __popc(__ballot_sync(0xffffffffu, pos >= 0));
+      __syncwarp();
+      add_rows<T, NV>(dy, my_pos, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, 0, 1);
+      if (n < 32) break;
     }
-    __syncthreads();
+    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
       if (v < nvec) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) part[warp * dim + v * 8 + e] = acc[i][e];
+        float4* o4 = reinterpret_cast<float4*>(out + v * 8);
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (accumulate) {
+          a = o4[0];
+          b = o4[1];
+        }
+        a.x += acc[i][0] * scale; a.y += acc[i][1] * scale; a.z += acc[i][2] * scale; a.w += acc[i][3] * scale;
+        b.x += acc[i][4] * scale; b.y += acc[i][5] * scale; b.z += acc[i][6] * scale; b.w += acc[i][7] * scale;
+        o4[0] = a;
+        o4[1] = b;
       }
     }
-    __syncthreads();
-    float* out = d_w_emb + static_cast<int64_t>(id) * dim;
-    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < 8; ++w) s += part[w * dim + c];
-      out[c] = (accumulate ? out[c] : 0.f) + s * scale;
-    }
-    __syncthreads();
   }
 }
 
 // The long runs (a Zipf head: the most frequent token of a GPT-2 batch of 8192 tokens occurs about 1 100 times) would
-// each keep one block busy for 100 us while the rest of the GPU idles. Here a cluster of kHeavyCluster blocks shares
+// each keep one warp busy for 100 us and more while the rest of the GPU idles. Here a cluster of kHeavyCluster blocks shares
 // one run: block r of the cluster sums the r-th slice of the run's rows, the slices' sums meet in block 0 through
 // distributed shared memory and are added in slice order (fixed order, no atomics => reproducible).
 // Work assignment without any helper tensor: cluster k looks at sorted position a = k * kHeavyRun. A run longer than
@@ -255,7 +274,7 @@ embed_bwd_heavy_kernel(const T* __restrict__ dy, const int32_t* __restrict__ ids
     pos_s[tid] = q < s1 ? sorted_pos[q] : -1;
     __syncthreads();
     const int n = static_cast<int>(s1 - base < 256 ? s1 - base : 256);
-    add_rows<T, NV>(dy, pos_s, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, warp);
+    add_rows<T, NV>(dy, pos_s, n, dim, nvec, masked, k_all, seed, stream_id, thr, acc, lane, warp, 8);
   }
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -461,13 +480,10 @@ template <typename T>
 int launch_embed_bwd(const void* dy, const int32_t* ids, const int32_t* sorted_pos, float* d_w_emb, int64_t tokens,
                      int dim, int64_t vocab, float scale, uint32_t thr, float eval_scale, int train, uint64_t seed,
                      uint32_t stream_id, int grid, cudaStream_t st) {
-  const size_t smem = static_cast<size_t>(8) * dim * sizeof(float);
   const int nv = (dim / 8 + 31) / 32;
 #define PTJ_EMB(NV)                                                                                              \
   {                                                                                                              \
-    if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(embed_bwd_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    launch_k(embed_bwd_kernel<T, NV>, grid, 256, smem, st, static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, tokens, \
+    launch_k(embed_bwd_kernel<T, NV>, grid, 256, 0, st, static_cast<const T*>(dy), ids, sorted_pos, d_w_emb, 1, tokens, \
                                                      dim, vocab, scale, thr, eval_scale, train, seed, stream_id); \
   }
   if (nv <= 1) PTJ_EMB(1) else if (nv <= 2) PTJ_EMB(2) else if (nv <= 4) PTJ_EMB(4) else if (nv <= 8) PTJ_EMB(8) else PTJ_EMB(16)
@@ -549,7 +565,8 @@ extern "C" int ptj_embed_bwd(const void* dy, const int32_t* ids, const int32_t* 
     launch_k(zero_kernel, flat_grid(vocab * dim, 256 * 4), 256, 0, st, d_w_emb, vocab * dim);
     PTJ_CHECK_LAUNCH();
   }
-  const int grid_e = flat_grid(tokens, 1);  // one block per sorted position (only run heads do work)
+  if (!aligned16(d_w_emb)) return PTJ_ERR_MISALIGNED;
+  const int grid_e = static_cast<int>(ceil_div(tokens, kChunk));  // one block per kChunk sorted positions
   if (!aligned16(d_w_pos)) return PTJ_ERR_MISALIGNED;
   const int grid_p = flat_grid(seq * dim / 8, 256);
   if (dtype == PTJ_F32) {

@@ -336,13 +336,14 @@ def test_embedding_forward_backward(ops, dtype, tol):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)])
 def test_embedding_backward_long_runs(ops, dtype, tol):
-    """Tokens that occur more than 128 times in a batch are summed by a cluster of thread blocks (slices of the run
-    meet through distributed shared memory): run lengths on both sides of that limit and of the 256-position batch,
+    """Tokens that occur more than 32 times in a batch are summed by a cluster of thread blocks (slices of the run
+    meet through distributed shared memory): run lengths on both sides of that limit, of the 64-position chunk a block
+    scans for run heads and of the 256-position batch,
     one run that starts at sorted position 0 and one that ends at the last position, dropout on, against a float64
     scatter; two calls agree bit for bit."""
     B, S, D, V, p, seed = 4, 1024, 64, 300, 0.1, 5
     g = torch.Generator().manual_seed(1)
-    counts = {1: 1500, 9: 128, 11: 129, 17: 257, 21: 600, 299: 200}
+    counts = {1: 1500, 5: 32, 6: 33, 9: 64, 11: 65, 17: 257, 21: 600, 299: 200}
     flat = [t for t, n in counts.items() for _ in range(n)]
     rest = B * S - len(flat)
     flat += torch.randint(30, 290, (rest,), generator=g).tolist()
