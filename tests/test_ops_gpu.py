@@ -382,13 +382,15 @@ def test_colsum_and_sumsq(ops, rows, cols):
 @pytest.mark.parametrize("dim", [200, 512, 768, 1016, 1280, 1536, 1792, 2048])
 @pytest.mark.parametrize("rows", [5, 1237])
 def test_layernorm_backward_bf16_rows_over_several_warps(dim, rows):
-    """The bf16 backward spreads a row over ceil(dim / 256) warps: every warp count, rows that do not divide over
+    """The bf16 kernels (forward and backward) spread a row over ceil(dim / 256) warps: every warp count, rows that do not divide over
     the blocks and row groups, all outputs against the oracle, and the two reduced forms (parameter gradients only;
     dx without parameter gradients) bit for bit against the full call."""
     ops = pkg("operators")
     x, dy, res = (rnd(rows, dim, seed=s).bfloat16() for s in (1, 2, 5))
     x = (x.float() * 0.5 + 3.0).bfloat16()  # a mean well away from zero
     gamma = 1 + 0.2 * rnd(dim, seed=3)
+    beta = 0.3 * rnd(dim, seed=4)
+    check(ops.t_layernorm_fwd_t((gpu(gamma), gpu(beta)), gpu(x)), orc.layernorm(gamma, beta, x.float()), BF16_TOL)
     dx, dg, db = ops.layernorm_bwd(gpu(dy), (gpu(gamma), None), gpu(x), dx_add=gpu(res))
     odx, odg, odb = orc.layernorm_bwd(dy.float(), gamma, x.float())
     check(dx, odx + res.float(), BF16_TOL)
