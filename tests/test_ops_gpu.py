@@ -382,7 +382,7 @@ def test_colsum_and_sumsq(ops, rows, cols):
 @pytest.mark.parametrize("dim", [200, 512, 768, 1016, 1280, 1536, 1792, 2048])
 @pytest.mark.parametrize("rows", [5, 1237])
 def test_layernorm_backward_bf16_rows_over_several_warps(dim, rows):
-    """The bf16 kernels (forward and backward) spread a row over ceil(dim / 256) warps: every warp count, rows that do not divide over
+    """The bf16 backward spreads a row over ceil(dim / 256) warps (the forward is checked on the same shapes): every warp count, rows that do not divide over
     the blocks and row groups, all outputs against the oracle, and the two reduced forms (parameter gradients only;
     dx without parameter gradients) bit for bit against the full call."""
     ops = pkg("operators")
