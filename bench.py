@@ -45,6 +45,8 @@ NCU_GEMM_TRAFFIC = {
     (8192, 3072, 768, True, False): (89.8e6, "gemm_tc_kernel_ffn1_fwd_ffn2_dgrad_counters.md"),   # dy W2 x gelu'
     (3072, 768, 8192, False, False): (68.1e6, "gemm_tc_pair_kernel_wgrad_dgrad_ffn1_counters.md"),  # FFN-1 weight gradient
     (8192, 768, 3072, True, False): (58.8e6, "gemm_tc_pair_kernel_wgrad_dgrad_ffn1_counters.md"),   # dh W1
+    # the two FFN weight gradients in one launch
+    ("grouped", 768, 3072, 3072, 768, 8192): (130.7e6, "gemm_tc_pair_kernel_wgrad_dgrad_ffn1_counters.md"),
 }
 
 
