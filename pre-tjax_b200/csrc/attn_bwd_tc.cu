@@ -38,7 +38,7 @@ constexpr int kOffQG = 4 * kTileBytes;                     // per stage: Q then 
 constexpr int kOffW = kOffQG + kQGStages * 2 * kTileBytes; // per group: one [128][128] bf16 tile, Pd then dS
 constexpr int kOffBars = kOffW + 4 * kTileBytes;
 constexpr int kNumBars = 32;
-constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 1024;
+constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 4 * 32 + 1024;  // (+ 32 last-tile entries, VARLEN)
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColDQ = 256, kColDV = 384, kColDK = 448;
 
@@ -49,9 +49,13 @@ struct Sched {
 
 // Position in the stream of (item, query tile) pairs of one thread block; every role walks the same stream.
 // Items are ordered heaviest first (KV tile 0 has the most query tiles) and dealt in boustrophedon order.
+// last_tile (VARLEN): per round of this block, the last query tile whose rows reach into the item's KV tile (later
+// query tiles mask all of its keys: they are skipped); nullptr = every item runs to the last query tile.
+constexpr int kMaxRoundsTabled = 32;
 struct Cursor {
-  int n, ord, kt, bh, i, g;
+  int n, ord, kt, bh, i, i1, g;
   bool valid;
+  const int* last_tile;
   __device__ __forceinline__ void next_item(const Sched& s) {
     valid = false;
     while (++n < s.rounds) {
@@ -61,21 +65,23 @@ struct Cursor {
         kt = s.BH == 1 ? sp : static_cast<int>(__umulhi(static_cast<uint32_t>(sp), s.bh_magic));  // sp / BH
         bh = sp - kt * s.BH;
         i = kt;
+        i1 = last_tile != nullptr ? last_tile[n] : s.nq - 1;
         ++ord;
         valid = true;
         return;
       }
     }
   }
-  __device__ __forceinline__ void init(const Sched& s) {
-    n = -1; ord = -1; g = 0; kt = 0; bh = 0; i = 0;
+  __device__ __forceinline__ void init(const Sched& s, const int* last = nullptr) {
+    n = -1; ord = -1; g = 0; kt = 0; bh = 0; i = 0; i1 = 0;
+    last_tile = last;
     next_item(s);
   }
   __device__ __forceinline__ bool first(const Sched&) const { return i == kt; }
-  __device__ __forceinline__ bool last(const Sched& s) const { return i == s.nq - 1; }
+  __device__ __forceinline__ bool last(const Sched&) const { return i == i1; }
   __device__ __forceinline__ void advance(const Sched& s) {
     ++g;
-    if (i == s.nq - 1) next_item(s); else ++i;
+    if (i == i1) next_item(s); else ++i;
   }
 };
 
@@ -113,7 +119,8 @@ attn_bwd_prep_kernel(const RowView d_o, const RowView o_view, const float* __res
 // bytes per store): float4 index ((bh * ntri + qt (qt + 1) / 2 + kt) * 16 + c4) * 128 + row. One thread sums one
 // float4 over kt; consecutive threads take consecutive rows.
 __global__ void __launch_bounds__(256)
-attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, int H, int nq, int64_t total_vec) {
+attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, const int32_t* __restrict__ kstart, int S, int H,
+                      int nq, int64_t total_vec) {
   grid_dep_sync();
   const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (v >= total_vec) return;
@@ -127,7 +134,14 @@ attn_dq_reduce_kernel(const float* __restrict__ part, const RowView dq, int S, i
   const float4* src = reinterpret_cast<const float4*>(part) +
                       ((bh * ntri + static_cast<int64_t>(qt) * (qt + 1) / 2) * (DH / 4) + c4) * T + row;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int kt = 0; kt <= qt; ++kt) {
+  // packed / padded batches: shares of KV tiles before the row's first key were either skipped by the main kernel (not
+  // written) or are exact zeros; a row without keys sums nothing
+  int kt0 = 0;
+  if (kstart != nullptr) {
+    const int k = __ldg(kstart + (bh / H) * S + q);
+    kt0 = k > q ? qt + 1 : max(k, 0) / T;
+  }
+  for (int kt = kt0; kt <= qt; ++kt) {
     const float4 t = __ldcs(src + static_cast<int64_t>(kt) * T * (DH / 4));
     acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
   }
@@ -230,6 +244,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* rk_s = tmem_slot + 2;  // Philox round keys
+  int* last_tab = reinterpret_cast<int*>(rk_s + 20);  // [kMaxRoundsTabled] last query tile of this block's items (VARLEN)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const AbortCtx ctx{abort_flag, p.fault};
@@ -263,6 +278,34 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (tid == 0) philox_round_keys(p.dr.seed, rk_s);
     __syncthreads();
   }
+  // VARLEN: query tiles none of whose rows reach into the item's KV tile are skipped. Warp w looks at the item of round
+  // w, w + 12, ...: the last query tile with a row whose first key lies in or before the KV tile (the diagonal tile is
+  // always visited).
+  const int* last_tile = nullptr;
+  if (VARLEN && sched.rounds <= kMaxRoundsTabled) {
+    for (int n = warp; n < sched.rounds; n += kThreads / 32) {
+      const int pos = (n & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+      const int sp = n * static_cast<int>(gridDim.x) + pos;
+      int last = 0;
+      if (sp < sched.total) {
+        const int kt = sp / sched.BH, bh = sp - kt * sched.BH;
+        const int32_t* ks = p.kstart + static_cast<int64_t>(bh / p.H) * p.S;
+        const int kv_end = kt * T + T;  // keys of the tile are < kv_end
+        last = kt;
+        for (int i = kt + 1; i < sched.nq; ++i) {
+          bool reach = false;
+          for (int r = lane; r < T; r += 32) {
+            const int row = i * T + r, k = __ldg(ks + row);
+            reach = reach || (k <= row && k < kv_end);  // the row has keys and its first one is in or before the tile
+          }
+          if (__any_sync(0xffffffffu, reach)) last = i;
+        }
+      }
+      if (lane == 0) last_tab[n] = last;
+    }
+    __syncthreads();
+    last_tile = last_tab;
+  }
   constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);  // Q K^T and dO V^T
   constexpr uint32_t idesc_t = idesc_bf16_f32(T, DH, true, true);   // Pd^T dO and dS^T Q
   constexpr uint32_t idesc_q = idesc_bf16_f32(T, DH, false, true);  // dS K
@@ -289,8 +332,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       Cursor ci, ct;  // items (K_j, V_j) and tiles (Q_i, dO_i) are two independent sequences
-      ci.init(sched);
-      ct.init(sched);
+      ci.init(sched, last_tile);
+      ct.init(sched, last_tile);
       long long t_idle = clock64();
       while (ci.valid || ct.valid) {
         bool progress = false;
@@ -322,8 +365,8 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ---------------------------------------------------------------- MMA issuer: S = Q K^T, then dP = dO V^T over it
     // (all lanes walk the streams so that addresses and descriptors stay warp-uniform; an elected lane issues)
     Cursor cs, cd;
-    cs.init(sched);
-    cd.init(sched);
+    cs.init(sched, last_tile);
+    cd.init(sched, last_tile);
     long long t_idle = clock64();
     while (cs.valid || cd.valid) {
       bool progress = false;
@@ -365,7 +408,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   } else if (warp == 2) {
     // ---------------------------------------------------------------- MMA issuer: dV += Pd^T dO (stream order)
     Cursor c;
-    c.init(sched);
+    c.init(sched, last_tile);
     bool ok = true;
     while (c.valid && ok) {
       const int x = c.g & 1, st = c.g % kQGStages;
@@ -388,7 +431,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ---------------------------------------------------------------- MMA issuer: dK += dS^T Q (stream order) and the
     // tile's dQ share dS K_j; both read dS, so one warp issues them back to back
     Cursor c;
-    c.init(sched);
+    c.init(sched, last_tile);
     bool ok = true;
     while (c.valid && ok) {
       const int x = c.g & 1, st = c.g % kQGStages;
@@ -433,7 +476,7 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int ntri = p.nq * (p.nq + 1) / 2;
 
     Cursor c;
-    c.init(sched);
+    c.init(sched, last_tile);
     bool ok = true;
     int64_t pend_part = -1;  // workspace tile that takes the dQ share still sitting in tensor memory
     int pend_g = 0;
@@ -499,11 +542,13 @@ attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         if (VARLEN) {  // keys before the row's document
           const int rel = __ldg(p.kstart + static_cast<int64_t>(c.bh / p.H) * p.S + q_row) - c.kt * T;
+          if (__any_sync(0xffffffffu, rel > 0)) {  // (most tiles hold no document boundary for any row of the warp)
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc)
+            for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+              for (int i = 0; i < 32; ++i)
+                if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+          }
         }
         const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(-lse, -lse);
         uint32_t pk[T / 2];
@@ -668,7 +713,7 @@ int attn_bwd_tc(const void* d_o, const void* q, const void* k, const void* v, co
   PTJ_CHECK_LAUNCH();
   const int64_t total_vec = rows * (DH / 4);
   launch_k(attn_dq_reduce_kernel, static_cast<unsigned>((total_vec + 255) / 256), 256, 0, st, part, make_view(dq, dsh.q_strides),
-                                                                                        p.S, p.H, p.nq, total_vec);
+                                                                                        row_kstart, p.S, p.H, p.nq, total_vec);
   PTJ_CHECK_LAUNCH();
   return PTJ_OK;
 }

@@ -32,7 +32,7 @@ constexpr int kOffP = kOffV + kVStages * kTileBytes;     // P[2 groups][2 sub-ti
 constexpr int kOffDump = kOffP + 4 * kTileBytes;          // float[64 + 3][128]: hand-over of one group's state
 constexpr int kOffBars = kOffDump + (DH + 3) * T * 4;
 constexpr int kNumBars = 4 + 2 * kKStages + 2 * kVStages + 2 * kSBufs + 6 + 2;
-constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 1024;
+constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16 + 80 + 4 * 32 + 1024;  // (+ 32 first-tile entries, VARLEN)
 constexpr int kTmemCols = 512;
 
 struct Sched {
@@ -41,9 +41,13 @@ struct Sched {
 };
 
 // Position in the stream of (item, kv tile) pairs of one thread block; every role walks the same stream.
+// first_tile (VARLEN): per round of this block, the first KV tile its item needs (keys before the first key of every
+// row of the query tile are masked anyway: those tiles are skipped); nullptr = every item starts at tile 0.
+constexpr int kMaxRoundsTabled = 32;
 struct Cursor {
-  int n, ord, qt, bh, j, g;
+  int n, ord, qt, bh, j, j0, g;
   bool valid;
+  const int* first_tile;
   __device__ __forceinline__ void next_item(const Sched& s) {
     valid = false;
     while (++n < s.rounds) {
@@ -53,15 +57,17 @@ struct Cursor {
         const int t = s.BH == 1 ? sp : static_cast<int>(__umulhi(static_cast<uint32_t>(sp), s.bh_magic));  // sp / BH
         qt = s.nq - 1 - t;
         bh = sp - t * s.BH;
-        j = 0;
+        j0 = first_tile != nullptr ? first_tile[n] : 0;
+        j = j0;
         ++ord;
         valid = true;
         return;
       }
     }
   }
-  __device__ __forceinline__ void init(const Sched& s) {
-    n = -1; ord = -1; g = 0; qt = 0; bh = 0; j = 0;
+  __device__ __forceinline__ void init(const Sched& s, const int* first = nullptr) {
+    n = -1; ord = -1; g = 0; qt = 0; bh = 0; j = 0; j0 = 0;
+    first_tile = first;
     next_item(s);
   }
   __device__ __forceinline__ void advance(const Sched& s) {
@@ -104,6 +110,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dump_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* rk_s = tmem_slot + 2;  // Philox round keys (MODE 1)
+  int* first_tab = reinterpret_cast<int*>(rk_s + 20);  // [kMaxRoundsTabled] first KV tile of this block's items (VARLEN)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const AbortCtx ctx{abort_flag, p.fault};
@@ -137,6 +144,32 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (tid == 0) philox_round_keys(p.dr.seed, rk_s);
     __syncthreads();
   }
+  // VARLEN: whole KV tiles before the first key of every row of a query tile are skipped. Warp w looks at the item of
+  // round w, w + 12, ...: the smallest first key over the tile's rows that have keys at all (none: only the diagonal
+  // tile is visited, it masks everything).
+  const int* first_tile = nullptr;
+  if (VARLEN && sched.rounds <= kMaxRoundsTabled) {
+    for (int n = warp; n < sched.rounds; n += kThreads / 32) {
+      const int pos = (n & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+      const int sp = n * static_cast<int>(gridDim.x) + pos;
+      int first = 0;
+      if (sp < sched.total) {
+        const int t = sp / sched.BH;
+        const int qt = sched.nq - 1 - t, bh = sp - t * sched.BH;
+        const int32_t* ks = p.kstart + static_cast<int64_t>(bh / p.H) * p.S + static_cast<int64_t>(qt) * T;
+        int lo = 0x7fffffff;
+        for (int r = lane; r < T; r += 32) {
+          const int k = __ldg(ks + r);
+          if (k <= qt * T + r) lo = min(lo, k);  // (k > row: the row has no keys)
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo);
+        first = lo == 0x7fffffff ? qt : min(max(lo, 0) / T, qt);
+      }
+      if (lane == 0) first_tab[n] = first;
+    }
+    __syncthreads();
+    first_tile = first_tab;
+  }
 
   // the copy / MMA warps hand most of their registers to the softmax warps (whole groups of four warps switch together)
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -146,8 +179,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // free slot is fetched next, so the K tiles run as far ahead as their ring allows.
     if (lane == 0) {
       Cursor ck, cv;
-      ck.init(sched);
-      cv.init(sched);
+      ck.init(sched, first_tile);
+      cv.init(sched, first_tile);
       bool q_done = false;  // Q of ck's item has been requested
       long long t_idle = clock64();
       while (ck.valid || cv.valid) {
@@ -155,14 +188,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (ck.valid) {
           const int b = ck.bh / p.H, h = ck.bh % p.H;
           const int qb = ck.ord & 1;
-          if (ck.j == 0 && !q_done && mbar_try_wait(&q_empty[qb], ((ck.ord >> 1) & 1) ^ 1u)) {
+          if (ck.j == ck.j0 && !q_done && mbar_try_wait(&q_empty[qb], ((ck.ord >> 1) & 1) ^ 1u)) {
             mbar_expect_tx(&q_full[qb], kTileBytes);
             tma_load_4d(q_s + qb * kTileBytes, &tm_q, &q_full[qb], 0, ck.qt * T, h, b);
             q_done = true;
             progress = true;
           }
           const int st = ck.g % kKStages;
-          if ((ck.j > 0 || q_done) && mbar_try_wait(&k_empty[st], ((ck.g / kKStages) & 1) ^ 1u)) {
+          if ((ck.j > ck.j0 || q_done) && mbar_try_wait(&k_empty[st], ((ck.g / kKStages) & 1) ^ 1u)) {
             mbar_expect_tx(&k_full[st], kTileBytes);
             tma_load_4d(k_s + st * kTileBytes, &tm_k, &k_full[st], 0, ck.j * T, h, b);
             ck.advance(sched);
@@ -196,14 +229,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // every lane walks the stream and waits (addresses and descriptors stay warp-uniform); an elected lane issues
     constexpr uint32_t idesc_s = idesc_bf16_f32(T, T, false, false);
     Cursor a;
-    a.init(sched);
+    a.init(sched, first_tile);
     bool ok = true;
     while (a.valid && ok) {
       const int st = a.g % kKStages;
       const int qb = a.ord & 1;
       const int sb = a.g % kSBufs;
       bool w = true;
-      if (a.j == 0) w = mbar_wait(&q_full[qb], (a.ord >> 1) & 1, ctx, 0x1201u);
+      if (a.j == a.j0) w = mbar_wait(&q_full[qb], (a.ord >> 1) & 1, ctx, 0x1201u);
       if (w) w = mbar_wait(&k_full[st], (a.g / kKStages) & 1, ctx, 0x1202u);
       if (w) w = mbar_wait(&s_free[sb], ((a.g / kSBufs) & 1) ^ 1u, ctx, 0x1203u);  // tile g - 3 has been read out
       ok = __all_sync(0xffffffffu, w);
@@ -230,13 +263,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     constexpr uint32_t idesc_o = idesc_bf16_f32(T, DH, false, true);
     const int grp = warp - 2;
     Cursor b;
-    b.init(sched);
+    b.init(sched, first_tile);
     bool ok = true;
     uint32_t items = 0;  // items this group has taken part in
     while (b.valid && ok) {
       if ((b.g & 1) == grp) {
         const int st = b.g % kVStages;
-        const bool first = b.j <= 1;  // the group's first tile of this item: start a fresh accumulator ...
+        const bool first = b.j - b.j0 <= 1;  // the group's first tile of this item: start a fresh accumulator ...
         bool w = mbar_wait(&p_ready[grp], (b.g >> 1) & 1, ctx, 0x1204u) &&
                  mbar_wait(&v_full[st], (b.g / kVStages) & 1, ctx, 0x1205u);
         if (first) {  // ... once the group has read the previous item's result out of it
@@ -275,7 +308,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t thr_hi = p.dr.thr16 << 16;
 
     Cursor c;
-    c.init(sched);
+    c.init(sched, first_tile);
     bool ok = true;
     float m_ref = 0.f, l = 0.f;  // reference exponent (log2 domain) and sum of 2^(s - m_ref) of this group's tiles
     float m_true = 0.f;          // true running row maximum (log2 domain), only reported
@@ -293,7 +326,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     while (c.valid && ok) {
       const bool mine = (c.g & 1) == grp;
       const int64_t q_row = static_cast<int64_t>(c.qt) * T + row;
-      if (c.j == 0) have = false;
+      if (c.j == c.j0) have = false;
       if (mine) {
         const int sb = c.g % kSBufs;
         // dropout random words of this thread's row of the tile: independent of the scores, so they are drawn one
@@ -329,11 +362,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         if (VARLEN) {  // keys before the row's document: columns below rel (any tile may hold a boundary)
           const int rel = __ldg(p.kstart + static_cast<int64_t>(c.bh / p.H) * p.S + q_row) - c.j * T;
+          if (__any_sync(0xffffffffu, rel > 0)) {  // (most tiles hold no document boundary for any row of the warp)
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc)
+            for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+              for (int i = 0; i < 32; ++i)
+                if (cc * 32 + i < rel) s[cc][i] = -INFINITY;
+          }
         }
         float mp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains of three-input maxima
 #pragma unroll
@@ -435,7 +470,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           __syncwarp();
           if (lane == 0) mbar_arrive(&o_free[grp]);  // the next item may overwrite the accumulator
         }
-        if (c.qt > 0) {
+        if (c.qt > c.j0) {  // (an item of a single tile has nothing to merge)
           if (!mine) {
             ok = mbar_wait(dump_free, (nd & 1) ^ 1u, ctx, 0x1304u);
             ok = __all_sync(0xffffffffu, ok);

@@ -165,6 +165,12 @@ def main():
         run("attention keep flags of one call (Philox, 16-bit lanes)", lambda: ops.attn_keep_bits(q, k, v, o4, 5, p=0.1, bits=bits))
         run("attention fwd  dropout 0.1, keep flags given", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits), flops=fl_attn)
         run("attention bwd  dropout 0.1, keep flags given", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1, keep_bits=bits), flops=2.5 * fl_attn)
+        # packed batch: every row holds eight documents of 128 tokens (tiles before a document's first key are skipped)
+        ks_packed = ops.row_kstart_from_lengths([[128] * (S // 128)] * B, S)
+        ks_one = ops.row_kstart_from_lengths([[S]] * B, S)
+        run("attention fwd  packed, 8 documents of 128 per row, keep flags given", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits, row_kstart=ks_packed))
+        run("attention bwd  packed, 8 documents of 128 per row, keep flags given", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.1, keep_bits=bits, row_kstart=ks_packed))
+        run("attention fwd  one document per row through the packed path", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.1, keep_bits=bits, row_kstart=ks_one))
         run("attention fwd  no dropout", lambda: ops.attn_fwd(q, k, v, o4, True, 5, p=0.0), flops=fl_attn)
         run("attention bwd  no dropout", lambda: ops.attn_bwd(do4, q, k, v, o4, m, l, dq, dk, dv, True, 5, p=0.0), flops=2.5 * fl_attn)
 
