@@ -137,6 +137,45 @@ def test_attention_with_document_masks(dtype, d_head, S, lens, p):
         ops.DROPOUT_RATE = 0.1
 
 
+def test_tile_skipping_over_long_rows_and_several_items_per_block():
+    """S = 1024 (eight tiles per row) with documents that start on and off tile boundaries, one row that is a single
+    document, a padding tail that covers whole tiles, and more (row, head, tile) items than the GPU has SMs, so that
+    blocks walk several items and both kernels' skip tables have more than one entry. Forward and backward against
+    the oracle run with the dense mask, keep flags handed in (p = 0.1) and none (p = 0)."""
+    ops = pkg("operators")
+    S, H, dh = 1024, 4, 64
+    lens = [[128] * 8, [1024], [100, 156, 256, 300, 212], [640], [513, 511], [1, 127, 129, 255, 257, 255]]
+    B = len(lens)
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(B, H, 3, S, dh, generator=g).bfloat16()
+    mask = collator_mask(lens, S)
+    live = non_pad_rows(mask)[:, None, :, None]
+    d_o = (torch.randn(B, H, S, dh, generator=g) * live).bfloat16()
+    q, k, v = (qkv[:, :, c].float() for c in range(3))
+    am = mask.unsqueeze(1)
+    for p, seed in ((0.0, 3), (0.1, 4)):
+        ops.DROPOUT_RATE = p
+        try:
+            out, acts = ops.t_scaled_dot_prod_attn_fwd3_t(qkv.cuda(), mask.cuda(), True, seed)
+            dq, dk, dv = ops.t_scaled_dot_prod_attn_bkwd3_t(d_o.cuda(), acts, qkv.cuda(), mask.cuda(), True, seed)
+            torch.cuda.synchronize()
+            assert ops.last_kernel_fault() == 0
+            drop = torch.from_numpy(philox.keep_mask(seed, 0, B * H * S * S, p)).view(B, H, S, S) if p > 0 else None
+            o_ref, _ = orc.causal_attention(q, k, v, p, True, drop, am)
+            rq, rk, rv = orc.causal_attention_bwd(d_o.float(), q, k, v, p, True, drop, am)
+            assert rel_err(out.cpu().float() * live, o_ref * live) < 2e-2
+            assert float((out.cpu().float() * ~live).abs().max()) == 0.0
+            for name, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+                assert torch.isfinite(a).all(), name
+                assert rel_err(a, b) < 2e-2, f"{name} (p = {p}): {rel_err(a, b):.3e}"
+            # a second call gives the same bits (tile streams and reductions are fixed)
+            out2, acts2 = ops.t_scaled_dot_prod_attn_fwd3_t(qkv.cuda(), mask.cuda(), True, seed)
+            dq2, dk2, dv2 = ops.t_scaled_dot_prod_attn_bkwd3_t(d_o.cuda(), acts2, qkv.cuda(), mask.cuda(), True, seed)
+            assert torch.equal(out, out2) and torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+        finally:
+            ops.DROPOUT_RATE = 0.1
+
+
 def test_packed_batch_bf16_model_against_oracle():
     """A small model on the tensor-core path (d_head 64, S 256) with packed rows and a padding tail, dropout 0.1 at
     all four sites: loss and every gradient against the fp32 oracle run with the dense mask."""
